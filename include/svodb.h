@@ -1,0 +1,236 @@
+/* svodb — C ABI of the B200 (sm_100a) replacement for svod's `tk` encoder hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers / sizes / POD structs,
+ * launches on the caller's CUDA stream and returns an `int` status
+ * (SVODB_OK = 0). The caller owns all device memory: inputs, outputs and any
+ * workspace. Nothing here allocates device memory unless its comment says so.
+ *
+ * The op-level functions mirror `svod_tk::ops` (tk/src/ops/mod.rs:30-38): same
+ * operand meaning, same validation order and the same error classes
+ * (`ops::Error`, tk/src/ops/mod.rs:132-159). Where the reference would take its
+ * "graph" path for lack of a tile kernel (f32 operands, odd shapes), this
+ * library runs an exact generic CUDA kernel instead; `svodb_last_chosen` reports
+ * which ran, as `ops::chosen()` does (tk/src/ops/mod.rs:83-118).
+ *
+ * The device-level functions (`svodb_module_*`, `svodb_program_launch`,
+ * `svodb_graph_*`, `svodb_alloc`...) mirror the `device` crate seam a Rust host
+ * binds: `Program::execute` (device/src/device.rs:42-121), `CudaProgram::load`
+ * (device/src/cuda/program.rs:116-219), `Graph::replay` (device/src/device.rs:144-171),
+ * the allocator (device/src/cuda/allocator.rs).
+ */
+#ifndef SVODB_H_
+#define SVODB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: `ops::Error` variants (tk/src/ops/mod.rs:132-159) ---- */
+enum {
+  SVODB_OK = 0,
+  SVODB_ERR_SHAPE = 1,      /* Error::Shape */
+  SVODB_ERR_DTYPE = 2,      /* Error::Dtype */
+  SVODB_ERR_HEADS = 3,      /* Error::Heads */
+  SVODB_ERR_GRAPH = 4,      /* Error::Graph: what the graph op would reject */
+  SVODB_ERR_LAUNCH = 5,     /* Error::Launch: CUDA launch / driver failure */
+  SVODB_ERR_UNREALIZED = 6, /* Error::Unrealized: null data pointer */
+  SVODB_ERR_ALIAS = 7,      /* launch::aliasing (tk/src/launch.rs:227-246) */
+  SVODB_ERR_TIMEOUT = 8,    /* a bounded device-side wait ran out */
+  SVODB_ERR_POISONED = 9,   /* a sticky CUDA error latched (device/src/cuda/sys.rs:78-96) */
+  SVODB_ERR_WORKSPACE = 10, /* workspace missing or too small */
+  SVODB_ERR_UNSUPPORTED = 11
+};
+
+/* ---- element types (dtype/src: Float32, Float16, BFloat16, Int32, Int64, Bool) ---- */
+enum { SVODB_F32 = 0, SVODB_F16 = 1, SVODB_BF16 = 2, SVODB_I32 = 3, SVODB_I64 = 4, SVODB_U8 = 5 };
+
+/* ---- `kernels::Act` (tk/src/kernels/mod.rs:272-280); GELU_TANH is the extra
+ * `Tensor::gelu` form (tensor/src/activation.rs:198-230) ---- */
+enum { SVODB_ACT_NONE = 0, SVODB_ACT_GELU = 1, SVODB_ACT_SILU = 2, SVODB_ACT_GELU_TANH = 3 };
+
+#define SVODB_MAX_RANK 5
+
+/* A realized, dense device tensor: `stride` in elements, innermost stride 1. */
+typedef struct svodb_tensor {
+  void* data;
+  int32_t dtype;
+  int32_t rank;
+  int64_t shape[SVODB_MAX_RANK];
+  int64_t stride[SVODB_MAX_RANK];
+} svodb_tensor;
+
+/* ---- library / device ---------------------------------------------------- */
+
+/* Library version string. */
+const char* svodb_version(void);
+
+/* Thread-local message of the last failing call on this thread
+ * (the `Display` text of `ops::Error`). */
+const char* svodb_last_error(void);
+
+/* `ops::supported(&DeviceSpec)` (tk/src/ops/mod.rs:161-166): 1 when CUDA device
+ * `device` has the tcgen05 kernels (compute capability 10.x), else 0. */
+int svodb_supported(int device);
+
+/* `ops::chosen()` (tk/src/ops/mod.rs:101-118): what the last op on this thread
+ * ran, e.g. "linear: kernel gemm {bm:128,bn:256,bk:64,stages:4}" or
+ * "attention: graph dtype" (generic kernel and why). */
+const char* svodb_last_chosen(void);
+
+/* Reads and clears the device status word bounded waits report into
+ * (0 = ok). Synchronises `stream`. Returns SVODB_ERR_TIMEOUT when a wait ran
+ * out since the last call. */
+int svodb_device_status(void* stream);
+
+/* ---- op layer: `svod_tk::ops` --------------------------------------------- */
+
+/* `ops::Linear` + `ops::Rotary` (tk/src/ops/linear.rs:24-56). */
+typedef struct svodb_linear_opts {
+  const svodb_tensor* bias;     /* [N] ([2N] gated) or NULL */
+  int32_t act;                  /* SVODB_ACT_* */
+  int32_t gated;                /* w is [2N,K], gate rows over up rows */
+  const svodb_tensor* residual; /* [lead..., N] or NULL, added last */
+  int32_t has_scale;
+  float scale;                  /* multiplies the activated value before the residual */
+  const svodb_tensor* rope_cos; /* [1,T,1,head_dim/2] or NULL */
+  const svodb_tensor* rope_sin;
+  int32_t rope_heads;
+  int32_t rope_head_dim;
+  int64_t into_at;              /* y is channels [at, at+N) of a wider buffer: pass
+                                   `y` as that view (data offset, wide row stride) */
+} svodb_linear_opts;
+
+/* `ops::linear(x, w, opts)` (tk/src/ops/linear.rs:63-191):
+ * y[lead..., N] = scale*act(x[lead..., K] . w[N,K]^T + bias) + residual. */
+int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linear_opts* opts, svodb_tensor* y,
+                 void* stream);
+
+/* `ops::Attn` (tk/src/ops/attention.rs:59-86) flattened. */
+typedef struct svodb_attn_opts {
+  int32_t causal;
+  const svodb_tensor* key_lens; /* KeyMask::Lens: [B] i32/i64, or NULL */
+  const svodb_tensor* key_mask; /* KeyMask::Bool: [B,Tk] u8/i32 (nonzero = attended), or NULL */
+  int32_t has_window;
+  int64_t window_left, window_right;
+  int32_t has_chunk;            /* `Chunk{size,left,right}` */
+  int64_t chunk_size, chunk_left /* -1 = every earlier chunk */, chunk_right;
+  const svodb_tensor* seg_start; /* [B,T] i32 or NULL */
+  int32_t splits;               /* 0 = library's choice; >1 needs `workspace` */
+  int32_t has_scale;
+  float scale;                  /* default 1/sqrt(D) */
+  const svodb_tensor* bias;     /* [B|1,H,T,Tk] in the stream dtype, or NULL */
+  svodb_tensor* lse;            /* optional out: [B,H,T] f32, ln-sum-exp of the masked scaled scores */
+  void* workspace;              /* device scratch for key splits (f32 partials) */
+  size_t workspace_bytes;
+} svodb_attn_opts;
+
+/* Bytes of `workspace` a split attention of this shape needs
+ * (`o_part`, `m_part`, `l_part`: tk/src/ops/attention.rs:285-292). */
+size_t svodb_attention_workspace_bytes(int64_t batch, int64_t t, int64_t heads, int64_t d, int32_t splits);
+
+/* `ops::attention(q,k,v,opts)` (tk/src/ops/attention.rs:100-102):
+ * q [B,T,H,D], k,v [B,Tk,Hkv,D] sequence-major -> o [B,T,H,D]. */
+int svodb_attention(const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v, const svodb_attn_opts* opts,
+                    svodb_tensor* o, void* stream);
+
+/* `ops::attention_packed(qkv, heads, kv_heads, opts)` (tk/src/ops/attention.rs:107-122):
+ * qkv [B,T,(H+2Hkv)*D] read in place -> o [B,T,H,D]. */
+int svodb_attention_packed(const svodb_tensor* qkv, int32_t heads, int32_t kv_heads, const svodb_attn_opts* opts,
+                           svodb_tensor* o, void* stream);
+
+/* `kernels::attention::combine` (tk/src/kernels/attention.rs:984-1014): merges
+ * f32 partials o_part [S,B,T,H,D], m_part/l_part [S,B,T,H] (m in log2 units). */
+int svodb_combine_splits(const svodb_tensor* o_part, const svodb_tensor* m_part, const svodb_tensor* l_part,
+                         svodb_tensor* o, void* stream);
+
+/* `ops::Qkv` (tk/src/ops/heads.rs:18-32). */
+typedef struct svodb_qkv_opts {
+  int32_t heads, kv_heads, head_dim;
+  const svodb_tensor* q_norm; /* [head_dim] or NULL */
+  const svodb_tensor* k_norm;
+  double eps;
+  const svodb_tensor* rope_cos; /* [1|B, T, 1, head_dim/2] or NULL */
+  const svodb_tensor* rope_sin;
+} svodb_qkv_opts;
+
+/* `ops::heads(qkv, opts)` (tk/src/ops/heads.rs:37-102). */
+int svodb_heads(const svodb_tensor* qkv, const svodb_qkv_opts* opts, svodb_tensor* q, svodb_tensor* k,
+                svodb_tensor* v, void* stream);
+
+/* `ops::layer_norm` / `add_layer_norm` / `rms_norm` / `add_rms_norm`
+ * (tk/src/ops/norm.rs:17-41). `b` may be NULL. The fused forms write
+ * `sum = round(x + residual)` and normalise the rounded sum. */
+int svodb_layer_norm(const svodb_tensor* x, const svodb_tensor* w, const svodb_tensor* b, double eps,
+                     svodb_tensor* out, void* stream);
+int svodb_add_layer_norm(const svodb_tensor* x, const svodb_tensor* residual, const svodb_tensor* w,
+                         const svodb_tensor* b, double eps, svodb_tensor* sum, svodb_tensor* out, void* stream);
+int svodb_rms_norm(const svodb_tensor* x, const svodb_tensor* w, double eps, svodb_tensor* out, void* stream);
+int svodb_add_rms_norm(const svodb_tensor* x, const svodb_tensor* residual, const svodb_tensor* w, double eps,
+                       svodb_tensor* sum, svodb_tensor* out, void* stream);
+
+/* ---- glue the encoder callers need around the ops -------------------------- */
+
+/* Token embedding lookup `out[b,t,:] = table[ids[b,t],:]`
+ * (`Embedding::forward`, lowered as a gather: tensor/src/transformer.rs:33-64).
+ * XLM-R form adds position and token-type rows: ids i32/i64 [B,T];
+ * `pos_table`/`type_row` may be NULL; position ids follow
+ * model/src/xlm_roberta/position_ids.rs:27-32 when `pad_id >= 0`. */
+int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+                const svodb_tensor* type_row, int64_t pad_id, svodb_tensor* out, void* stream);
+
+/* `encoder_head::pool` + `lp_normalize` (model/src/encoder_head.rs:280-286;
+ * tensor/src/nn/norm.rs:205-213) and Qwen3's last-token gather
+ * (model/src/qwen3/model.rs:77-99): hidden [B,L,D] -> out [B,D] f32 rows of an
+ * `out` that may be a slice of a wider gather buffer.
+ * mode 0 = CLS, 1 = masked mean (mask [B,L] u8/i32), 2 = last token (lengths [B] i32). */
+int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
+               svodb_tensor* out, void* stream);
+
+/* RoPE tables `Tensor::rope_table` (tensor/src/transformer.rs:130-164): angles
+ * and cos/sin in f32, cast last; positions [P] i32 (NULL = 0..P-1);
+ * cos,sin [P, head_dim/2]. */
+int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,
+                     svodb_tensor* sin, void* stream);
+
+/* ---- device seam: what the `device` crate binds ----------------------------- */
+
+typedef struct svodb_program svodb_program;
+typedef struct svodb_graph svodb_graph;
+
+/* One kernel parameter: `AbiParamDescriptor{slot,kind}` (device/src/device.rs:366-381). */
+typedef struct svodb_abi_param {
+  int32_t slot;
+  int32_t kind; /* 0 = Storage (8-byte device pointer), 1 = Scalar (4-byte i32) */
+} svodb_abi_param;
+
+/* `CudaProgram::load` (device/src/cuda/program.rs:116-219): loads a cubin or PTX
+ * image, resolves `entry`. */
+int svodb_module_load(const void* image, size_t bytes, const char* entry, const svodb_abi_param* params, int32_t n,
+                      svodb_program** out);
+/* `Program::execute` (device/src/device.rs:42-66): kernarg = pointers then i32
+ * scalars in ascending slot order (device/src/cuda/program.rs:1-5,264-274). */
+int svodb_program_launch(svodb_program* p, void* stream, void* const* bufs, int32_t n_bufs, const int32_t* vals,
+                         int32_t n_vals, const uint32_t grid[3], const uint32_t block[3], uint32_t dyn_smem);
+int svodb_program_free(svodb_program* p);
+
+/* `CudaGraph::capture` / `Graph::replay` (device/src/cuda/graph.rs:127-173,375-391),
+ * stream-capture based. */
+int svodb_graph_begin(void* stream);
+int svodb_graph_end(void* stream, svodb_graph** out);
+int svodb_graph_replay(svodb_graph* g, void* stream);
+int svodb_graph_free(svodb_graph* g);
+
+/* `Allocator` (device/src/cuda/allocator.rs): kind 0 = device, 1 = pinned host. */
+int svodb_alloc(size_t bytes, int32_t kind, void** out);
+int svodb_free(void* ptr, int32_t kind);
+int svodb_copy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int svodb_copy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int svodb_stream_sync(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVODB_H_ */

@@ -1,0 +1,145 @@
+"""ctypes binding of `libsvodb.so` (the C ABI declared in include/svodb.h).
+
+The library is the product path. There is no CPU or PyTorch fallback: if the
+shared library is missing, loading raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libsvodb.so"
+
+MAX_RANK = 5
+
+# status codes of include/svodb.h
+OK, ERR_SHAPE, ERR_DTYPE, ERR_HEADS, ERR_GRAPH, ERR_LAUNCH, ERR_UNREALIZED, ERR_ALIAS, ERR_TIMEOUT, \
+    ERR_POISONED, ERR_WORKSPACE, ERR_UNSUPPORTED = range(12)
+
+F32, F16, BF16, I32, I64, U8 = range(6)
+
+
+class Tensor(C.Structure):
+    _fields_ = [
+        ("data", C.c_void_p),
+        ("dtype", C.c_int32),
+        ("rank", C.c_int32),
+        ("shape", C.c_int64 * MAX_RANK),
+        ("stride", C.c_int64 * MAX_RANK),
+    ]
+
+
+TensorP = C.POINTER(Tensor)
+
+
+class LinearOpts(C.Structure):
+    _fields_ = [
+        ("bias", TensorP),
+        ("act", C.c_int32),
+        ("gated", C.c_int32),
+        ("residual", TensorP),
+        ("has_scale", C.c_int32),
+        ("scale", C.c_float),
+        ("rope_cos", TensorP),
+        ("rope_sin", TensorP),
+        ("rope_heads", C.c_int32),
+        ("rope_head_dim", C.c_int32),
+        ("into_at", C.c_int64),
+    ]
+
+
+class AttnOpts(C.Structure):
+    _fields_ = [
+        ("causal", C.c_int32),
+        ("key_lens", TensorP),
+        ("key_mask", TensorP),
+        ("has_window", C.c_int32),
+        ("window_left", C.c_int64),
+        ("window_right", C.c_int64),
+        ("has_chunk", C.c_int32),
+        ("chunk_size", C.c_int64),
+        ("chunk_left", C.c_int64),
+        ("chunk_right", C.c_int64),
+        ("seg_start", TensorP),
+        ("splits", C.c_int32),
+        ("has_scale", C.c_int32),
+        ("scale", C.c_float),
+        ("bias", TensorP),
+        ("lse", TensorP),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class QkvOpts(C.Structure):
+    _fields_ = [
+        ("heads", C.c_int32),
+        ("kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("q_norm", TensorP),
+        ("k_norm", TensorP),
+        ("eps", C.c_double),
+        ("rope_cos", TensorP),
+        ("rope_sin", TensorP),
+    ]
+
+
+class AbiParam(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("kind", C.c_int32)]
+
+
+# Every symbol include/svodb.h declares: (name, restype, argtypes).
+SYMBOLS = [
+    ("svodb_version", C.c_char_p, []),
+    ("svodb_last_error", C.c_char_p, []),
+    ("svodb_supported", C.c_int, [C.c_int]),
+    ("svodb_last_chosen", C.c_char_p, []),
+    ("svodb_device_status", C.c_int, [C.c_void_p]),
+    ("svodb_linear", C.c_int, [TensorP, TensorP, C.POINTER(LinearOpts), TensorP, C.c_void_p]),
+    ("svodb_attention_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    ("svodb_attention", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
+    ("svodb_attention_packed", C.c_int, [TensorP, C.c_int32, C.c_int32, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
+    ("svodb_combine_splits", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_void_p]),
+    ("svodb_heads", C.c_int, [TensorP, C.POINTER(QkvOpts), TensorP, TensorP, TensorP, C.c_void_p]),
+    ("svodb_layer_norm", C.c_int, [TensorP, TensorP, TensorP, C.c_double, TensorP, C.c_void_p]),
+    ("svodb_add_layer_norm", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_double, TensorP, TensorP, C.c_void_p]),
+    ("svodb_rms_norm", C.c_int, [TensorP, TensorP, C.c_double, TensorP, C.c_void_p]),
+    ("svodb_add_rms_norm", C.c_int, [TensorP, TensorP, TensorP, C.c_double, TensorP, TensorP, C.c_void_p]),
+    ("svodb_embed", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_int64, TensorP, C.c_void_p]),
+    ("svodb_pool", C.c_int, [TensorP, TensorP, C.c_int32, C.c_int32, TensorP, C.c_void_p]),
+    ("svodb_rope_table", C.c_int, [C.c_double, TensorP, C.c_int32, TensorP, TensorP, C.c_void_p]),
+    ("svodb_module_load", C.c_int,
+     [C.c_void_p, C.c_size_t, C.c_char_p, C.POINTER(AbiParam), C.c_int32, C.POINTER(C.c_void_p)]),
+    ("svodb_program_launch", C.c_int,
+     [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.POINTER(C.c_int32), C.c_int32,
+      C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32]),
+    ("svodb_program_free", C.c_int, [C.c_void_p]),
+    ("svodb_graph_begin", C.c_int, [C.c_void_p]),
+    ("svodb_graph_end", C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    ("svodb_graph_replay", C.c_int, [C.c_void_p, C.c_void_p]),
+    ("svodb_graph_free", C.c_int, [C.c_void_p]),
+    ("svodb_alloc", C.c_int, [C.c_size_t, C.c_int32, C.POINTER(C.c_void_p)]),
+    ("svodb_free", C.c_int, [C.c_void_p, C.c_int32]),
+    ("svodb_copy_h2d", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("svodb_copy_d2h", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("svodb_stream_sync", C.c_int, [C.c_void_p]),
+]
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once and types every entry point."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m svod_b200.build` "
+                "(there is no CPU or PyTorch fallback for these ops)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, res, args in SYMBOLS:
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib

@@ -1,0 +1,995 @@
+// The C ABI: validation in the order and with the error classes of svod's
+// `tk::ops` (tk/src/ops/{linear,attention,heads,norm}.rs), kernel-vs-generic
+// dispatch (the reference's kernel-vs-graph `Plan`, tk/src/ops/shape.rs:92-231),
+// the `chosen()` report, and the device seam (module load / launch, graph
+// capture / replay, allocator).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "kernels.h"
+#include "svodb.h"
+
+using namespace svodb;
+
+namespace {
+
+thread_local char g_error[512] = "";
+thread_local char g_chosen[256] = "";
+bool g_poisoned = false;
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void chose_kernel(const char* op, const char* family, const char* cfg) {
+  snprintf(g_chosen, sizeof g_chosen, "%s: kernel %s %s", op, family, cfg);
+}
+void chose_graph(const char* op, const char* why) { snprintf(g_chosen, sizeof g_chosen, "%s: graph %s", op, why); }
+
+// Sticky CUDA errors poison the device: every later call fails fast
+// (device/src/cuda/sys.rs:78-96).
+bool sticky(cudaError_t e) {
+  switch (e) {
+    case cudaErrorIllegalAddress:
+    case cudaErrorLaunchFailure:
+    case cudaErrorIllegalInstruction:
+    case cudaErrorMisalignedAddress:
+    case cudaErrorHardwareStackError:
+    case cudaErrorInvalidAddressSpace:
+    case cudaErrorInvalidPc:
+    case cudaErrorAssert:
+    case cudaErrorECCUncorrectable:
+      return true;
+    default:
+      return false;
+  }
+}
+
+int check_launch(const char* op) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return SVODB_OK;
+  if (sticky(e)) g_poisoned = true;
+  return fail(SVODB_ERR_LAUNCH, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+#define GUARD(op)                                                                       \
+  do {                                                                                  \
+    if (g_poisoned) return fail(SVODB_ERR_POISONED, "%s: the device is poisoned", op); \
+  } while (0)
+
+bool is_float(int dt) { return dt == SVODB_F32 || dt == SVODB_F16 || dt == SVODB_BF16; }
+bool is_half(int dt) { return dt == SVODB_F16 || dt == SVODB_BF16; }
+const char* dtype_name(int dt) {
+  static const char* names[] = {"Float32", "Float16", "BFloat16", "Int32", "Int64", "UInt8"};
+  return dt >= 0 && dt <= 5 ? names[dt] : "?";
+}
+size_t esize(int dt) {
+  switch (dt) {
+    case SVODB_F32: case SVODB_I32: return 4;
+    case SVODB_I64: return 8;
+    case SVODB_U8: return 1;
+    default: return 2;
+  }
+}
+
+void fmt_shape(const svodb_tensor* t, char* buf, size_t n) {
+  size_t at = (size_t)snprintf(buf, n, "[");
+  for (int i = 0; i < t->rank && at < n; ++i)
+    at += (size_t)snprintf(buf + at, n - at, i ? ", %lld" : "%lld", (long long)t->shape[i]);
+  if (at < n) snprintf(buf + at, n - at, "]");
+}
+
+int shape_err(const char* op, const char* operand, const svodb_tensor* got, const char* expected) {
+  char buf[128];
+  fmt_shape(got, buf, sizeof buf);
+  return fail(SVODB_ERR_SHAPE, "%s: %s has shape %s, expected %s", op, operand, buf, expected);
+}
+int dtype_err(const char* op, const char* operand, int got, int want) {
+  return fail(SVODB_ERR_DTYPE, "%s: %s is %s, the input is %s", op, operand, dtype_name(got), dtype_name(want));
+}
+
+int64_t numel(const svodb_tensor* t) {
+  int64_t n = 1;
+  for (int i = 0; i < t->rank; ++i) n *= t->shape[i];
+  return n;
+}
+
+// Dense row-major in every dim but an optionally wider stride of dim `rank-2`
+// (a channel window of a wider buffer).
+bool rows_dense(const svodb_tensor* t) {
+  if (t->rank == 0) return true;
+  if (t->stride[t->rank - 1] != 1) return false;
+  if (t->rank == 1) return true;
+  int64_t ld = t->stride[t->rank - 2];
+  if (ld < t->shape[t->rank - 1]) return false;
+  int64_t expect = ld * t->shape[t->rank - 2];
+  for (int i = t->rank - 3; i >= 0; --i) {
+    if (t->stride[i] != expect) return false;
+    expect *= t->shape[i];
+  }
+  return true;
+}
+bool contiguous(const svodb_tensor* t) {
+  int64_t expect = 1;
+  for (int i = t->rank - 1; i >= 0; --i) {
+    if (t->shape[i] != 1 && t->stride[i] != expect) return false;
+    expect *= t->shape[i];
+  }
+  return true;
+}
+
+int realized(const char* op, const char* operand, const svodb_tensor* t) {
+  if (t == nullptr) return fail(SVODB_ERR_UNREALIZED, "%s: %s is missing", op, operand);
+  if (t->rank < 0 || t->rank > SVODB_MAX_RANK) return shape_err(op, operand, t, "rank <= 5");
+  if (t->data == nullptr && numel(t) != 0)
+    return fail(SVODB_ERR_UNREALIZED, "%s: %s is not a realized buffer", op, operand);
+  return SVODB_OK;
+}
+
+// `launch::aliasing` (tk/src/launch.rs:227-246): a written parameter may not
+// share storage with another parameter.
+struct Span {
+  const char* lo;
+  const char* hi;
+};
+Span span_of(const svodb_tensor* t) {
+  int64_t last = 0;
+  for (int i = 0; i < t->rank; ++i)
+    if (t->shape[i] > 0) last += (t->shape[i] - 1) * t->stride[i];
+  const char* lo = (const char*)t->data;
+  return Span{lo, lo + (size_t)(last + 1) * esize(t->dtype)};
+}
+int no_alias(const char* op, const svodb_tensor* out, std::initializer_list<const svodb_tensor*> others) {
+  if (out == nullptr || out->data == nullptr) return SVODB_OK;
+  Span o = span_of(out);
+  for (const svodb_tensor* t : others) {
+    if (t == nullptr || t->data == nullptr || t == out) continue;
+    Span s = span_of(t);
+    if (o.lo < s.hi && s.lo < o.hi) return fail(SVODB_ERR_ALIAS, "%s: an output shares storage with an input", op);
+  }
+  return SVODB_OK;
+}
+
+bool same_shape(const svodb_tensor* a, const svodb_tensor* b) {
+  if (a->rank != b->rank) return false;
+  for (int i = 0; i < a->rank; ++i)
+    if (a->shape[i] != b->shape[i]) return false;
+  return true;
+}
+
+#define TRY(expr)                  \
+  do {                             \
+    int rc_ = (expr);              \
+    if (rc_ != SVODB_OK) return rc_; \
+  } while (0)
+
+}  // namespace
+
+// The status word bounded device waits report into: a module-scope device
+// variable (one instance per device that loads the library), so the op layer
+// allocates nothing.
+__device__ uint32_t g_status_word = 0;
+
+namespace svodb {
+uint32_t* device_status_word() {
+  static std::mutex mu;
+  static std::vector<uint32_t*> words(64, nullptr);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 0 || dev >= (int)words.size()) return nullptr;
+  if (words[dev] == nullptr) {
+    void* w = nullptr;
+    if (cudaGetSymbolAddress(&w, g_status_word) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    words[dev] = (uint32_t*)w;
+  }
+  return words[dev];
+}
+}  // namespace svodb
+
+extern "C" {
+
+const char* svodb_version(void) { return "svodb 0.1 (sm_100a)"; }
+const char* svodb_last_error(void) { return g_error; }
+const char* svodb_last_chosen(void) { return g_chosen; }
+
+int svodb_supported(int device) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+int svodb_device_status(void* stream) {
+  GUARD("device_status");
+  uint32_t* w = device_status_word();
+  if (w == nullptr) return fail(SVODB_ERR_LAUNCH, "device_status: no status word");
+  uint32_t host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, w, sizeof host, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    if (sticky(e)) g_poisoned = true;
+    return fail(SVODB_ERR_LAUNCH, "device_status: %s", cudaGetErrorString(e));
+  }
+  if (host != 0) {
+    cudaMemsetAsync(w, 0, sizeof host, (cudaStream_t)stream);
+    cudaStreamSynchronize((cudaStream_t)stream);
+    return fail(SVODB_ERR_TIMEOUT, "a bounded device wait ran out (code %u)", host);
+  }
+  return SVODB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// linear
+// ---------------------------------------------------------------------------
+int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linear_opts* opts, svodb_tensor* y,
+                 void* stream) {
+  static const char* OP = "linear";
+  GUARD(OP);
+  svodb_linear_opts none{};
+  if (opts == nullptr) opts = &none;
+  TRY(realized(OP, "x", x));
+  TRY(realized(OP, "w", w));
+  TRY(realized(OP, "y", y));
+  if (x->rank < 1) return shape_err(OP, "x", x, "[..., K]");
+  const int64_t k = x->shape[x->rank - 1];
+  if (w->rank != 2 || w->shape[1] != k) return shape_err(OP, "w", w, "[N, K]");
+  if (!is_float(x->dtype)) return fail(SVODB_ERR_GRAPH, "%s: x is %s, not a float type", OP, dtype_name(x->dtype));
+  if (w->dtype != x->dtype) return dtype_err(OP, "w", w->dtype, x->dtype);
+  int64_t n = w->shape[0];
+  if (opts->gated) {
+    if (n % 2 != 0) return shape_err(OP, "w", w, "[2N, K]");
+    n /= 2;
+  }
+  if (opts->bias != nullptr) {
+    TRY(realized(OP, "bias", opts->bias));
+    if (opts->bias->rank != 1 || opts->bias->shape[0] != w->shape[0]) return shape_err(OP, "bias", opts->bias, "[N]");
+    if (opts->bias->dtype != x->dtype) return dtype_err(OP, "bias", opts->bias->dtype, x->dtype);
+  }
+  // out shape = lead..., N
+  if (y->rank != x->rank) return shape_err(OP, "y", y, "[lead..., N]");
+  for (int i = 0; i < x->rank - 1; ++i)
+    if (y->shape[i] != x->shape[i]) return shape_err(OP, "y", y, "[lead..., N]");
+  if (y->shape[y->rank - 1] != n) return shape_err(OP, "y", y, "[lead..., N]");
+  if (y->dtype != x->dtype) return dtype_err(OP, "y", y->dtype, x->dtype);
+  if (opts->residual != nullptr) {
+    TRY(realized(OP, "residual", opts->residual));
+    if (!same_shape(opts->residual, y)) return shape_err(OP, "residual", opts->residual, "[lead..., N]");
+    if (opts->residual->dtype != x->dtype) return dtype_err(OP, "residual", opts->residual->dtype, x->dtype);
+  }
+  const bool rope = opts->rope_cos != nullptr;
+  int64_t seq = 0;
+  if (rope) {
+    const int hd = opts->rope_head_dim, nh = opts->rope_heads;
+    if (x->rank != 3 || opts->gated) return shape_err(OP, "x", x, "[B, T, K] under a plain weight");
+    if (!(hd > 0 && hd % 2 == 0 && (int64_t)nh * hd <= n)) return shape_err(OP, "w", w, "[>= heads*head_dim, K] of even heads");
+    seq = x->shape[1];
+    const svodb_tensor* tabs[2] = {opts->rope_cos, opts->rope_sin};
+    const char* names[2] = {"cos", "sin"};
+    for (int i = 0; i < 2; ++i) {
+      TRY(realized(OP, names[i], tabs[i]));
+      const svodb_tensor* t = tabs[i];
+      const bool fits = t->rank == 4 && t->shape[0] == 1 && t->shape[1] == seq && t->shape[2] == 1 &&
+                        t->shape[3] == hd / 2 && contiguous(t);
+      if (!fits) return shape_err(OP, names[i], t, "[1, T, 1, head_dim/2]");
+    }
+  }
+  if (!rows_dense(x) || !rows_dense(y) || !contiguous(w) ||
+      (opts->residual != nullptr && !rows_dense(opts->residual)))
+    return fail(SVODB_ERR_GRAPH, "%s: operands must be dense rows (innermost stride 1)", OP);
+  TRY(no_alias(OP, y, {x, w, opts->bias, opts->residual, opts->rope_cos, opts->rope_sin}));
+
+  GemmArgs a{};
+  a.a = x->data;
+  a.w = w->data;
+  a.bias = opts->bias ? opts->bias->data : nullptr;
+  a.residual = opts->residual ? opts->residual->data : nullptr;
+  a.c = y->data;
+  a.k = (int)k;
+  a.n = (int)n;
+  a.m = k == 0 ? 0 : numel(x) / (k ? k : 1);
+  a.lda = x->rank >= 2 ? x->stride[x->rank - 2] : k;
+  a.ldw = k;
+  a.ldc = y->rank >= 2 ? y->stride[y->rank - 2] : n;
+  a.ldr = opts->residual ? (opts->residual->rank >= 2 ? opts->residual->stride[opts->residual->rank - 2] : n) : 0;
+  a.act = opts->act;
+  a.gated = opts->gated;
+  a.has_scale = opts->has_scale;
+  a.scale = opts->scale;
+  a.dtype = x->dtype;
+  a.status = device_status_word();
+  if (a.m == 0 || n == 0) {
+    chose_graph(OP, "shape");
+    return SVODB_OK;
+  }
+  // The tables ride the stream dtype or the rotation runs after a plain GEMM,
+  // and a turn runs alone after the bias (tk/src/ops/linear.rs:132-164).
+  bool rope_in_store = rope && opts->rope_cos->dtype == x->dtype && opts->rope_sin->dtype == x->dtype;
+  if (rope && !rope_in_store)
+    return dtype_err(OP, "cos", opts->rope_cos->dtype, x->dtype);
+  if (rope) {
+    a.rope_cos = opts->rope_cos->data;
+    a.rope_sin = opts->rope_sin->data;
+    a.rope_heads = opts->rope_heads;
+    a.rope_head_dim = opts->rope_head_dim;
+    a.rope_seq = seq;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  char cfg[128];
+  if (gemm_tc_covers(a)) {
+    int rc = launch_gemm_tc(a, s, cfg, sizeof cfg);
+    if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+    if (rc == 0) {
+      chose_kernel(OP, "gemm", cfg);
+      return check_launch(OP);
+    }
+  }
+  const char* why = !is_half(a.dtype) ? "dtype" : (n % 8 != 0 || k % 16 != 0) ? "shape" : "config";
+  launch_gemm_generic(a, s);
+  chose_graph(OP, why);
+  return check_launch(OP);
+}
+
+// ---------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------
+namespace {
+
+int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v, bool packed,
+           const svodb_attn_opts* opts, svodb_tensor* o, void* stream) {
+  svodb_attn_opts none{};
+  if (opts == nullptr) opts = &none;
+  if (q->rank != 4) return shape_err(OP, "q", q, "[B, T, H, D]");
+  if (!(k->rank == 4 && k->shape[0] == q->shape[0] && k->shape[3] == q->shape[3]))
+    return shape_err(OP, "k", k, "[B, Tk, H_kv, D]");
+  if (!same_shape(v, k)) return shape_err(OP, "v", v, "the shape of k");
+  if (!is_float(q->dtype)) return fail(SVODB_ERR_GRAPH, "%s: q is %s, not a float type", OP, dtype_name(q->dtype));
+  if (k->dtype != q->dtype) return dtype_err(OP, "k", k->dtype, q->dtype);
+  if (v->dtype != q->dtype) return dtype_err(OP, "v", v->dtype, q->dtype);
+  const int64_t B = q->shape[0], T = q->shape[1], H = q->shape[2], D = q->shape[3];
+  const int64_t Tk = k->shape[1], Hkv = k->shape[2];
+  if (!(Hkv > 0 && H % Hkv == 0))
+    return fail(SVODB_ERR_HEADS, "%s: %lld query heads are not a multiple of %lld key/value heads", OP, (long long)H,
+                (long long)Hkv);
+  if (opts->key_lens != nullptr && opts->key_mask != nullptr)
+    return fail(SVODB_ERR_GRAPH, "%s: key lengths and a key mask are alternatives (KeyMask)", OP);
+  if (opts->key_lens != nullptr) {
+    TRY(realized(OP, "key lens", opts->key_lens));
+    if (opts->key_lens->rank != 1 || opts->key_lens->shape[0] != B) return shape_err(OP, "key lens", opts->key_lens, "[B]");
+    if (opts->key_lens->dtype != SVODB_I32) return dtype_err(OP, "key lens", opts->key_lens->dtype, SVODB_I32);
+  }
+  if (opts->key_mask != nullptr) {
+    TRY(realized(OP, "key mask", opts->key_mask));
+    const svodb_tensor* m = opts->key_mask;
+    if (m->rank != 2 || m->shape[0] != B || m->shape[1] != Tk || !contiguous(m))
+      return shape_err(OP, "key mask", m, "[B, Tk]");
+    if (m->dtype != SVODB_U8 && m->dtype != SVODB_I32) return dtype_err(OP, "key mask", m->dtype, SVODB_U8);
+  }
+  if (opts->seg_start != nullptr) {
+    TRY(realized(OP, "seg start", opts->seg_start));
+    const svodb_tensor* sg = opts->seg_start;
+    if (sg->rank != 2 || sg->shape[0] != B || sg->shape[1] != T || !contiguous(sg))
+      return shape_err(OP, "seg start", sg, "[B, T]");
+    if (sg->dtype != SVODB_I32) return dtype_err(OP, "seg start", sg->dtype, SVODB_I32);
+  }
+  int bias_per_batch = 0;
+  if (opts->bias != nullptr) {
+    TRY(realized(OP, "bias", opts->bias));
+    const svodb_tensor* bs = opts->bias;
+    const bool fits = bs->rank == 4 && (bs->shape[0] == B || bs->shape[0] == 1) && bs->shape[1] == H &&
+                      bs->shape[2] == T && bs->shape[3] == Tk && contiguous(bs);
+    if (!fits) return shape_err(OP, "bias", bs, "[B | 1, H, T, Tk]");
+    if (bs->dtype != q->dtype) return dtype_err(OP, "bias", bs->dtype, q->dtype);
+    bias_per_batch = bs->shape[0] != 1 || B == 1;
+  }
+  if (!(o->rank == 4 && same_shape(o, q))) return shape_err(OP, "o", o, "[B, T, H, D]");
+  if (o->dtype != q->dtype) return dtype_err(OP, "o", o->dtype, q->dtype);
+  if (opts->lse != nullptr) {
+    TRY(realized(OP, "lse", opts->lse));
+    const svodb_tensor* l = opts->lse;
+    if (l->rank != 3 || l->shape[0] != B || l->shape[1] != H || l->shape[2] != T || !contiguous(l))
+      return shape_err(OP, "lse", l, "[B, H, T]");
+    if (l->dtype != SVODB_F32) return dtype_err(OP, "lse", l->dtype, SVODB_F32);
+  }
+  const svodb_tensor* all[4] = {q, k, v, o};
+  for (const svodb_tensor* t : all)
+    if (t->stride[3] != 1) return fail(SVODB_ERR_GRAPH, "%s: the head dim must be contiguous", OP);
+  if (packed) TRY(no_alias(OP, o, {q}));
+  else TRY(no_alias(OP, o, {q, k, v}));
+  if (opts->has_chunk && opts->chunk_size <= 0) return fail(SVODB_ERR_GRAPH, "%s: a chunk of size 0", OP);
+
+  AttnArgs a{};
+  a.q = q->data, a.k = k->data, a.v = v->data, a.o = o->data;
+  a.q_sb = q->stride[0], a.q_st = q->stride[1], a.q_sh = q->stride[2];
+  a.k_sb = k->stride[0], a.k_st = k->stride[1], a.k_sh = k->stride[2];
+  a.v_sb = v->stride[0], a.v_st = v->stride[1], a.v_sh = v->stride[2];
+  a.o_sb = o->stride[0], a.o_st = o->stride[1], a.o_sh = o->stride[2];
+  a.batch = B, a.t = T, a.tk = Tk;
+  a.heads = (int)H, a.kv_heads = (int)Hkv, a.d = (int)D;
+  a.dtype = q->dtype;
+  a.scale = opts->has_scale ? opts->scale : 1.0f / sqrtf((float)D);
+  a.causal = opts->causal;
+  a.key_lens = opts->key_lens ? (const int32_t*)opts->key_lens->data : nullptr;
+  a.key_mask = opts->key_mask ? opts->key_mask->data : nullptr;
+  a.key_mask_i32 = opts->key_mask ? opts->key_mask->dtype == SVODB_I32 : 0;
+  a.has_window = opts->has_window;
+  a.win_left = opts->window_left, a.win_right = opts->window_right;
+  a.has_chunk = opts->has_chunk;
+  a.chunk_size = opts->chunk_size, a.chunk_left = opts->chunk_left, a.chunk_right = opts->chunk_right;
+  a.seg_start = opts->seg_start ? (const int32_t*)opts->seg_start->data : nullptr;
+  a.bias = opts->bias ? opts->bias->data : nullptr;
+  a.bias_per_batch = bias_per_batch;
+  a.lse = opts->lse ? (float*)opts->lse->data : nullptr;
+  a.splits = opts->splits > 1 ? opts->splits : 1;
+  a.status = device_status_word();
+  a.packed = packed;
+  if (B * T * H == 0 || D == 0) {
+    chose_graph(OP, "shape");
+    return SVODB_OK;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (Tk == 0) {
+    // No key at all: every row attends to nothing (zeros), as the graph writes it.
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t t = 0; t < T; ++t)
+        cudaMemsetAsync((char*)o->data + (b * o->stride[0] + t * o->stride[1]) * esize(o->dtype), 0,
+                        (size_t)(H * D) * esize(o->dtype), s);
+    chose_graph(OP, "shape");
+    return check_launch(OP);
+  }
+  if (a.splits > 1) {
+    const int64_t tiles = (Tk + 31) / 32;
+    if (a.splits > tiles) a.splits = (int)tiles;  // capped at the key block count
+  }
+  if (a.splits > 1) {
+    const size_t need = svodb_attention_workspace_bytes(B, T, H, D, a.splits);
+    if (opts->workspace == nullptr || opts->workspace_bytes < need)
+      return fail(SVODB_ERR_WORKSPACE, "%s: %d key splits need %zu workspace bytes", OP, a.splits, need);
+    if (opts->lse != nullptr) return fail(SVODB_ERR_UNSUPPORTED, "%s: lse is not produced under key splits", OP);
+    const int64_t rows = B * T * H;
+    a.o_part = (float*)opts->workspace;
+    a.m_part = a.o_part + (size_t)a.splits * rows * D;
+    a.l_part = a.m_part + (size_t)a.splits * rows;
+    if (!(o->stride[2] == D && o->stride[1] == H * D && o->stride[0] == T * H * D))
+      return fail(SVODB_ERR_GRAPH, "%s: a split attention writes a contiguous output", OP);
+  }
+  char cfg[128];
+  if (attention_tc_covers(a)) {
+    int rc = launch_attention_tc(a, s, cfg, sizeof cfg);
+    if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+    if (rc == 0) {
+      chose_kernel(OP, packed ? "flash_attention_packed" : "flash_attention", cfg);
+      return check_launch(OP);
+    }
+  }
+  if (D > 256) return fail(SVODB_ERR_UNSUPPORTED, "%s: head dim %lld is above 256", OP, (long long)D);
+  const char* why = !is_half(a.dtype) ? "dtype" : "shape";
+  int rc = launch_attention_generic(a, s);
+  if (rc != 0) return fail(SVODB_ERR_LAUNCH, "%s: kernel attributes were rejected (%d)", OP, rc);
+  if (a.splits > 1) {
+    CombineArgs c{};
+    c.o_part = a.o_part, c.m_part = a.m_part, c.l_part = a.l_part;
+    c.o = o->data;
+    c.rows = B * T * H;
+    c.d = (int)D;
+    c.splits = a.splits;
+    c.dtype = a.dtype;
+    launch_combine(c, s);
+  }
+  chose_graph(OP, why);
+  return check_launch(OP);
+}
+
+}  // namespace
+
+size_t svodb_attention_workspace_bytes(int64_t batch, int64_t t, int64_t heads, int64_t d, int32_t splits) {
+  if (splits <= 1) return 0;
+  const size_t rows = (size_t)batch * (size_t)t * (size_t)heads;
+  return sizeof(float) * (size_t)splits * rows * ((size_t)d + 2);
+}
+
+int svodb_attention(const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v, const svodb_attn_opts* opts,
+                    svodb_tensor* o, void* stream) {
+  static const char* OP = "attention";
+  GUARD(OP);
+  TRY(realized(OP, "q", q));
+  TRY(realized(OP, "k", k));
+  TRY(realized(OP, "v", v));
+  TRY(realized(OP, "o", o));
+  return attend(OP, q, k, v, false, opts, o, stream);
+}
+
+int svodb_attention_packed(const svodb_tensor* qkv, int32_t heads, int32_t kv_heads, const svodb_attn_opts* opts,
+                           svodb_tensor* o, void* stream) {
+  static const char* OP = "attention";
+  GUARD(OP);
+  TRY(realized(OP, "qkv", qkv));
+  TRY(realized(OP, "o", o));
+  if (!(kv_heads > 0 && heads % kv_heads == 0))
+    return fail(SVODB_ERR_HEADS, "%s: %d query heads are not a multiple of %d key/value heads", OP, heads, kv_heads);
+  const int slots = heads + 2 * kv_heads;
+  if (qkv->rank != 3 || qkv->shape[2] <= 0 || qkv->shape[2] % slots != 0 || !contiguous(qkv))
+    return shape_err(OP, "qkv", qkv, "[B, T, slots*D]");
+  const int64_t d = qkv->shape[2] / slots;
+  const int64_t B = qkv->shape[0], T = qkv->shape[1], W = qkv->shape[2];
+  auto view = [&](int64_t head0, int64_t nheads) {
+    svodb_tensor t{};
+    t.data = (char*)qkv->data + (size_t)(head0 * d) * esize(qkv->dtype);
+    t.dtype = qkv->dtype;
+    t.rank = 4;
+    t.shape[0] = B, t.shape[1] = T, t.shape[2] = nheads, t.shape[3] = d;
+    t.stride[0] = T * W, t.stride[1] = W, t.stride[2] = d, t.stride[3] = 1;
+    return t;
+  };
+  svodb_tensor q = view(0, heads), k = view(heads, kv_heads), v = view(heads + kv_heads, kv_heads);
+  return attend(OP, &q, &k, &v, true, opts, o, stream);
+}
+
+int svodb_combine_splits(const svodb_tensor* o_part, const svodb_tensor* m_part, const svodb_tensor* l_part,
+                         svodb_tensor* o, void* stream) {
+  static const char* OP = "combine_splits";
+  GUARD(OP);
+  TRY(realized(OP, "o_part", o_part));
+  TRY(realized(OP, "m_part", m_part));
+  TRY(realized(OP, "l_part", l_part));
+  TRY(realized(OP, "o", o));
+  if (o_part->rank != 5 || !contiguous(o_part)) return shape_err(OP, "o_part", o_part, "[S, B, T, H, D]");
+  if (m_part->rank != 4 || !contiguous(m_part)) return shape_err(OP, "m_part", m_part, "[S, B, T, H]");
+  if (!same_shape(l_part, m_part) || !contiguous(l_part)) return shape_err(OP, "l_part", l_part, "[S, B, T, H]");
+  for (int i = 0; i < 4; ++i)
+    if (m_part->shape[i] != o_part->shape[i]) return shape_err(OP, "m_part", m_part, "[S, B, T, H]");
+  if (o->rank != 4 || !contiguous(o)) return shape_err(OP, "o", o, "[B, T, H, D]");
+  for (int i = 0; i < 4; ++i)
+    if (o->shape[i] != o_part->shape[i + 1]) return shape_err(OP, "o", o, "[B, T, H, D]");
+  if (o_part->dtype != SVODB_F32 || m_part->dtype != SVODB_F32 || l_part->dtype != SVODB_F32)
+    return dtype_err(OP, "partials", o_part->dtype, SVODB_F32);
+  if (!is_float(o->dtype)) return dtype_err(OP, "o", o->dtype, SVODB_BF16);
+  CombineArgs c{};
+  c.o_part = (const float*)o_part->data;
+  c.m_part = (const float*)m_part->data;
+  c.l_part = (const float*)l_part->data;
+  c.o = o->data;
+  c.rows = o->shape[0] * o->shape[1] * o->shape[2];
+  c.d = (int)o->shape[3];
+  c.splits = (int)o_part->shape[0];
+  c.dtype = o->dtype;
+  launch_combine(c, (cudaStream_t)stream);
+  chose_kernel(OP, "combine_splits", "{br:4}");
+  return check_launch(OP);
+}
+
+// ---------------------------------------------------------------------------
+// heads
+// ---------------------------------------------------------------------------
+int svodb_heads(const svodb_tensor* qkv, const svodb_qkv_opts* opts, svodb_tensor* q, svodb_tensor* k,
+                svodb_tensor* v, void* stream) {
+  static const char* OP = "heads";
+  GUARD(OP);
+  if (opts == nullptr) return fail(SVODB_ERR_GRAPH, "%s: options are required", OP);
+  TRY(realized(OP, "qkv", qkv));
+  TRY(realized(OP, "q", q));
+  TRY(realized(OP, "k", k));
+  TRY(realized(OP, "v", v));
+  const int H = opts->heads, Hkv = opts->kv_heads, d = opts->head_dim;
+  if (!(Hkv > 0 && H % Hkv == 0))
+    return fail(SVODB_ERR_HEADS, "%s: %d query heads are not a multiple of %d key/value heads", OP, H, Hkv);
+  const int slots = H + 2 * Hkv;
+  if (qkv->rank != 3 || qkv->shape[2] != (int64_t)slots * d || !contiguous(qkv))
+    return shape_err(OP, "qkv", qkv, "[B, T, slots*head_dim]");
+  if (!is_float(qkv->dtype)) return fail(SVODB_ERR_GRAPH, "%s: qkv is not a float type", OP);
+  const svodb_tensor* norms[2] = {opts->q_norm, opts->k_norm};
+  const char* nnames[2] = {"q norm", "k norm"};
+  for (int i = 0; i < 2; ++i) {
+    if (norms[i] == nullptr) continue;
+    TRY(realized(OP, nnames[i], norms[i]));
+    if (norms[i]->rank != 1 || norms[i]->shape[0] != d) return shape_err(OP, nnames[i], norms[i], "[head_dim]");
+    if (norms[i]->dtype != qkv->dtype) return dtype_err(OP, nnames[i], norms[i]->dtype, qkv->dtype);
+  }
+  const int64_t B = qkv->shape[0], T = qkv->shape[1];
+  int per_batch = 0;
+  if (opts->rope_cos != nullptr) {
+    if (d % 2 != 0) return shape_err(OP, "qkv", qkv, "an even head_dim under a rotation");
+    TRY(realized(OP, "cos", opts->rope_cos));
+    TRY(realized(OP, "sin", opts->rope_sin));
+    const svodb_tensor* c = opts->rope_cos;
+    const bool fits = c->rank == 4 && (c->shape[0] == 1 || c->shape[0] == B) && c->shape[1] == T &&
+                      c->shape[2] == 1 && c->shape[3] == d / 2 && contiguous(c);
+    if (!fits) return shape_err(OP, "cos", c, "[1 | B, T, 1, head_dim/2]");
+    if (!same_shape(opts->rope_sin, c) || !contiguous(opts->rope_sin)) return shape_err(OP, "sin", opts->rope_sin, "the shape of cos");
+    if (c->dtype != qkv->dtype) return dtype_err(OP, "cos", c->dtype, qkv->dtype);
+    if (opts->rope_sin->dtype != qkv->dtype) return dtype_err(OP, "sin", opts->rope_sin->dtype, qkv->dtype);
+    per_batch = c->shape[0] != 1;
+  }
+  auto out_ok = [&](const svodb_tensor* t, int heads) {
+    return t->rank == 4 && t->shape[0] == B && t->shape[1] == T && t->shape[2] == heads && t->shape[3] == d &&
+           contiguous(t) && t->dtype == qkv->dtype;
+  };
+  if (!out_ok(q, H)) return shape_err(OP, "q", q, "[B, T, heads, head_dim]");
+  if (!out_ok(k, Hkv)) return shape_err(OP, "k", k, "[B, T, kv_heads, head_dim]");
+  if (!out_ok(v, Hkv)) return shape_err(OP, "v", v, "[B, T, kv_heads, head_dim]");
+  TRY(no_alias(OP, q, {qkv, k, v}));
+  TRY(no_alias(OP, k, {qkv, v}));
+  TRY(no_alias(OP, v, {qkv}));
+  HeadsArgs a{};
+  a.qkv = qkv->data;
+  a.q_w = opts->q_norm ? opts->q_norm->data : nullptr;
+  a.k_w = opts->k_norm ? opts->k_norm->data : nullptr;
+  a.cos = opts->rope_cos ? opts->rope_cos->data : nullptr;
+  a.sin = opts->rope_sin ? opts->rope_sin->data : nullptr;
+  a.q = q->data, a.k = k->data, a.v = v->data;
+  a.batch = B, a.t = T;
+  a.heads = H, a.kv_heads = Hkv, a.d = d;
+  a.eps = (float)opts->eps;
+  a.per_batch_tables = per_batch;
+  a.dtype = qkv->dtype;
+  if (launch_heads(a, (cudaStream_t)stream)) chose_kernel(OP, "heads", "{lanes_per_head:d/16}");
+  else chose_graph(OP, is_half(a.dtype) ? "shape" : "dtype");
+  return check_launch(OP);
+}
+
+// ---------------------------------------------------------------------------
+// norms
+// ---------------------------------------------------------------------------
+namespace {
+int norm_op(const char* OP, int layer, const svodb_tensor* x, const svodb_tensor* residual, const svodb_tensor* w,
+            const svodb_tensor* b, double eps, svodb_tensor* sum, svodb_tensor* out, void* stream) {
+  GUARD(OP);
+  TRY(realized(OP, "x", x));
+  TRY(realized(OP, "w", w));
+  TRY(realized(OP, "out", out));
+  if (x->rank < 1) return shape_err(OP, "x", x, "[..., D]");
+  const int64_t d = x->shape[x->rank - 1];
+  if (!is_float(x->dtype)) return fail(SVODB_ERR_GRAPH, "%s: x is not a float type", OP);
+  if (w->rank != 1 || w->shape[0] != d) return shape_err(OP, "w", w, "[D]");
+  if (w->dtype != x->dtype) return dtype_err(OP, "w", w->dtype, x->dtype);
+  if (b != nullptr) {
+    TRY(realized(OP, "b", b));
+    if (b->rank != 1 || b->shape[0] != d) return shape_err(OP, "b", b, "[D]");
+    if (b->dtype != x->dtype) return dtype_err(OP, "b", b->dtype, x->dtype);
+  }
+  if (residual != nullptr) {
+    TRY(realized(OP, "residual", residual));
+    TRY(realized(OP, "sum", sum));
+    if (!same_shape(residual, x)) return shape_err(OP, "residual", residual, "the shape of x");
+    if (residual->dtype != x->dtype) return dtype_err(OP, "residual", residual->dtype, x->dtype);
+    if (!same_shape(sum, x) || !contiguous(sum) || sum->dtype != x->dtype) return shape_err(OP, "sum", sum, "the shape of x");
+    if (!contiguous(residual)) return fail(SVODB_ERR_GRAPH, "%s: residual must be contiguous", OP);
+  }
+  if (!same_shape(out, x) || out->dtype != x->dtype) return shape_err(OP, "out", out, "the shape of x");
+  if (!contiguous(x) || !contiguous(out)) return fail(SVODB_ERR_GRAPH, "%s: x and out must be contiguous", OP);
+  TRY(no_alias(OP, out, {x, residual, w, b, sum}));
+  if (sum != nullptr) TRY(no_alias(OP, sum, {x, residual, w, b}));
+  NormArgs a{};
+  a.x = x->data;
+  a.residual = residual ? residual->data : nullptr;
+  a.w = w->data;
+  a.b = b ? b->data : nullptr;
+  a.out = out->data;
+  a.sum = sum ? sum->data : nullptr;
+  a.d = (int)d;
+  a.rows = d == 0 ? 0 : numel(x) / d;
+  a.eps = (float)eps;
+  a.layer = layer;
+  a.dtype = x->dtype;
+  if (a.rows == 0) {
+    chose_graph(OP, "shape");
+    return SVODB_OK;
+  }
+  if (launch_norm(a, (cudaStream_t)stream)) chose_kernel(OP, OP, "{br:8}");
+  else chose_graph(OP, is_half(a.dtype) ? "shape" : "dtype");
+  return check_launch(OP);
+}
+}  // namespace
+
+int svodb_layer_norm(const svodb_tensor* x, const svodb_tensor* w, const svodb_tensor* b, double eps,
+                     svodb_tensor* out, void* stream) {
+  return norm_op("layer_norm", 1, x, nullptr, w, b, eps, nullptr, out, stream);
+}
+int svodb_add_layer_norm(const svodb_tensor* x, const svodb_tensor* residual, const svodb_tensor* w,
+                         const svodb_tensor* b, double eps, svodb_tensor* sum, svodb_tensor* out, void* stream) {
+  if (residual == nullptr) return fail(SVODB_ERR_UNREALIZED, "layer_norm: residual is missing");
+  return norm_op("layer_norm", 1, x, residual, w, b, eps, sum, out, stream);
+}
+int svodb_rms_norm(const svodb_tensor* x, const svodb_tensor* w, double eps, svodb_tensor* out, void* stream) {
+  return norm_op("rms_norm", 0, x, nullptr, w, nullptr, eps, nullptr, out, stream);
+}
+int svodb_add_rms_norm(const svodb_tensor* x, const svodb_tensor* residual, const svodb_tensor* w, double eps,
+                       svodb_tensor* sum, svodb_tensor* out, void* stream) {
+  if (residual == nullptr) return fail(SVODB_ERR_UNREALIZED, "rms_norm: residual is missing");
+  return norm_op("rms_norm", 0, x, residual, w, nullptr, eps, sum, out, stream);
+}
+
+// ---------------------------------------------------------------------------
+// glue
+// ---------------------------------------------------------------------------
+int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+                const svodb_tensor* type_row, int64_t pad_id, svodb_tensor* out, void* stream) {
+  static const char* OP = "embed";
+  GUARD(OP);
+  TRY(realized(OP, "ids", ids));
+  TRY(realized(OP, "table", table));
+  TRY(realized(OP, "out", out));
+  if (ids->rank != 2 || !contiguous(ids)) return shape_err(OP, "ids", ids, "[B, T]");
+  if (ids->dtype != SVODB_I32 && ids->dtype != SVODB_I64) return dtype_err(OP, "ids", ids->dtype, SVODB_I32);
+  if (table->rank != 2 || !contiguous(table)) return shape_err(OP, "table", table, "[V, D]");
+  if (!is_half(table->dtype)) return dtype_err(OP, "table", table->dtype, SVODB_BF16);
+  const int64_t d = table->shape[1];
+  if (d % 8 != 0) return shape_err(OP, "table", table, "[V, D] with D a multiple of 8");
+  if (out->rank != 3 || out->shape[0] != ids->shape[0] || out->shape[1] != ids->shape[1] || out->shape[2] != d ||
+      !contiguous(out) || out->dtype != table->dtype)
+    return shape_err(OP, "out", out, "[B, T, D]");
+  if (pos_table != nullptr) {
+    TRY(realized(OP, "pos_table", pos_table));
+    if (pos_table->rank != 2 || pos_table->shape[1] != d || !contiguous(pos_table) || pos_table->dtype != table->dtype)
+      return shape_err(OP, "pos_table", pos_table, "[P, D]");
+  }
+  if (type_row != nullptr) {
+    TRY(realized(OP, "type_row", type_row));
+    if (numel(type_row) < d || type_row->dtype != table->dtype) return shape_err(OP, "type_row", type_row, "[D]");
+  }
+  EmbedArgs a{};
+  a.ids = ids->data;
+  a.ids_i64 = ids->dtype == SVODB_I64;
+  a.table = table->data;
+  a.pos_table = pos_table ? pos_table->data : nullptr;
+  a.type_row = type_row ? type_row->data : nullptr;
+  a.pad_id = pad_id;
+  a.out = out->data;
+  a.batch = ids->shape[0], a.t = ids->shape[1];
+  a.d = (int)d;
+  a.vocab = table->shape[0];
+  a.max_pos = pos_table ? pos_table->shape[0] : 1;
+  a.dtype = table->dtype;
+  launch_embed(a, (cudaStream_t)stream);
+  return check_launch(OP);
+}
+
+int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
+               svodb_tensor* out, void* stream) {
+  static const char* OP = "pool";
+  GUARD(OP);
+  TRY(realized(OP, "hidden", hidden));
+  TRY(realized(OP, "out", out));
+  if (hidden->rank != 3 || !contiguous(hidden) || !is_float(hidden->dtype)) return shape_err(OP, "hidden", hidden, "[B, L, D]");
+  const int64_t B = hidden->shape[0], L = hidden->shape[1], D = hidden->shape[2];
+  if (out->rank != 2 || out->shape[0] != B || out->shape[1] != D || out->stride[1] != 1 || out->dtype != SVODB_F32)
+    return shape_err(OP, "out", out, "[B, D] f32");
+  if (mode < 0 || mode > 2) return fail(SVODB_ERR_GRAPH, "%s: mode %d", OP, mode);
+  const svodb_tensor* aux = mask_or_lengths;
+  if (mode == 1) {
+    TRY(realized(OP, "mask", aux));
+    if (aux->rank != 2 || aux->shape[0] != B || aux->shape[1] != L || !contiguous(aux)) return shape_err(OP, "mask", aux, "[B, L]");
+    if (aux->dtype != SVODB_U8 && aux->dtype != SVODB_I32) return dtype_err(OP, "mask", aux->dtype, SVODB_U8);
+  } else if (mode == 2) {
+    TRY(realized(OP, "lengths", aux));
+    if (aux->rank != 1 || aux->shape[0] != B) return shape_err(OP, "lengths", aux, "[B]");
+    if (aux->dtype != SVODB_I32) return dtype_err(OP, "lengths", aux->dtype, SVODB_I32);
+  }
+  if (L == 0) return shape_err(OP, "hidden", hidden, "[B, L >= 1, D]");
+  PoolArgs a{};
+  a.hidden = hidden->data;
+  a.aux = aux ? aux->data : nullptr;
+  a.aux_i32 = aux ? aux->dtype == SVODB_I32 : 0;
+  a.mode = mode;
+  a.normalize = normalize;
+  a.out = (float*)out->data;
+  a.out_row_stride = out->stride[0];
+  a.batch = B, a.l = L;
+  a.d = (int)D;
+  a.dtype = hidden->dtype;
+  launch_pool(a, (cudaStream_t)stream);
+  return check_launch(OP);
+}
+
+int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,
+                     svodb_tensor* sin, void* stream) {
+  static const char* OP = "rope_table";
+  GUARD(OP);
+  TRY(realized(OP, "cos", cos));
+  TRY(realized(OP, "sin", sin));
+  if (head_dim < 2 || head_dim % 2 != 0) return fail(SVODB_ERR_GRAPH, "%s: head_dim %d is not an even number >= 2", OP, head_dim);
+  if (cos->rank != 2 || cos->shape[1] != head_dim / 2 || !contiguous(cos) || !is_float(cos->dtype))
+    return shape_err(OP, "cos", cos, "[P, head_dim/2]");
+  if (!same_shape(sin, cos) || !contiguous(sin) || sin->dtype != cos->dtype) return shape_err(OP, "sin", sin, "the shape of cos");
+  const int32_t* pos = nullptr;
+  if (positions != nullptr) {
+    TRY(realized(OP, "positions", positions));
+    if (numel(positions) != cos->shape[0] || positions->dtype != SVODB_I32 || !contiguous(positions))
+      return shape_err(OP, "positions", positions, "[P] i32");
+    pos = (const int32_t*)positions->data;
+  }
+  launch_rope_table(theta, pos, cos->shape[0], head_dim, cos->data, sin->data, cos->dtype, (cudaStream_t)stream);
+  return check_launch(OP);
+}
+
+// ---------------------------------------------------------------------------
+// device seam
+// ---------------------------------------------------------------------------
+struct svodb_program {
+  CUmodule module;
+  CUfunction function;
+  std::vector<svodb_abi_param> params;
+};
+struct svodb_graph {
+  cudaGraph_t graph;
+  cudaGraphExec_t exec;
+};
+
+namespace {
+struct Driver {
+  CUresult (*module_load_data)(CUmodule*, const void*) = nullptr;
+  CUresult (*module_get_function)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*module_unload)(CUmodule) = nullptr;
+  CUresult (*launch_kernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                            void**, void**) = nullptr;
+  CUresult (*func_set_attribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  bool ok = false;
+};
+const Driver& driver() {
+  static Driver d;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    cudaFree(nullptr);  // make sure the primary context exists
+    auto get = [](const char* name, void** fn) {
+      cudaDriverEntryPointQueryResult q;
+      return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess;
+    };
+    d.ok = get("cuModuleLoadData", (void**)&d.module_load_data) &&
+           get("cuModuleGetFunction", (void**)&d.module_get_function) &&
+           get("cuModuleUnload", (void**)&d.module_unload) && get("cuLaunchKernel", (void**)&d.launch_kernel) &&
+           get("cuFuncSetAttribute", (void**)&d.func_set_attribute);
+  }
+  return d;
+}
+}  // namespace
+
+int svodb_module_load(const void* image, size_t bytes, const char* entry, const svodb_abi_param* params, int32_t n,
+                      svodb_program** out) {
+  static const char* OP = "module_load";
+  GUARD(OP);
+  (void)bytes;
+  if (image == nullptr || entry == nullptr || out == nullptr) return fail(SVODB_ERR_UNREALIZED, "%s: null argument", OP);
+  const Driver& d = driver();
+  if (!d.ok) return fail(SVODB_ERR_LAUNCH, "%s: the CUDA driver entry points are unavailable", OP);
+  svodb_program* p = new svodb_program();
+  CUresult r = d.module_load_data(&p->module, image);
+  if (r != CUDA_SUCCESS) {
+    delete p;
+    return fail(SVODB_ERR_LAUNCH, "%s: cuModuleLoadData failed (%d)", OP, (int)r);
+  }
+  r = d.module_get_function(&p->function, p->module, entry);
+  if (r != CUDA_SUCCESS) {
+    d.module_unload(p->module);
+    delete p;
+    return fail(SVODB_ERR_LAUNCH, "%s: no entry `%s` (%d)", OP, entry, (int)r);
+  }
+  for (int i = 0; i < n; ++i) p->params.push_back(params[i]);
+  *out = p;
+  return SVODB_OK;
+}
+
+int svodb_program_launch(svodb_program* p, void* stream, void* const* bufs, int32_t n_bufs, const int32_t* vals,
+                         int32_t n_vals, const uint32_t grid[3], const uint32_t block[3], uint32_t dyn_smem) {
+  static const char* OP = "program_launch";
+  GUARD(OP);
+  if (p == nullptr) return fail(SVODB_ERR_UNREALIZED, "%s: null program", OP);
+  const Driver& d = driver();
+  // The reference packs the kernarg blob as 8-byte pointers then 4-byte scalars
+  // in ascending slot order (device/src/cuda/program.rs:264-274); the same
+  // parameter order is handed to cuLaunchKernel by address here.
+  std::vector<void*> argv;
+  std::vector<void*> ptrs(bufs, bufs + n_bufs);
+  std::vector<int32_t> ints(vals, vals + n_vals);
+  for (int i = 0; i < n_bufs; ++i) argv.push_back(&ptrs[i]);
+  for (int i = 0; i < n_vals; ++i) argv.push_back(&ints[i]);
+  if (dyn_smem > 48 * 1024) d.func_set_attribute(p->function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)dyn_smem);
+  CUresult r = d.launch_kernel(p->function, grid[0], grid[1], grid[2], block[0], block[1], block[2], dyn_smem,
+                               (CUstream)stream, argv.data(), nullptr);
+  if (r != CUDA_SUCCESS) return fail(SVODB_ERR_LAUNCH, "%s: cuLaunchKernel failed (%d)", OP, (int)r);
+  return SVODB_OK;
+}
+
+int svodb_program_free(svodb_program* p) {
+  if (p == nullptr) return SVODB_OK;
+  const Driver& d = driver();
+  if (d.ok) d.module_unload(p->module);
+  delete p;
+  return SVODB_OK;
+}
+
+int svodb_graph_begin(void* stream) {
+  GUARD("graph_begin");
+  cudaError_t e = cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) return fail(SVODB_ERR_LAUNCH, "graph_begin: %s", cudaGetErrorString(e));
+  return SVODB_OK;
+}
+int svodb_graph_end(void* stream, svodb_graph** out) {
+  GUARD("graph_end");
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture((cudaStream_t)stream, &g);
+  if (e != cudaSuccess || g == nullptr) {
+    cudaGetLastError();
+    return fail(SVODB_ERR_LAUNCH, "graph_end: %s", cudaGetErrorString(e));
+  }
+  cudaGraphExec_t x = nullptr;
+  e = cudaGraphInstantiate(&x, g, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(g);
+    return fail(SVODB_ERR_LAUNCH, "graph_end: instantiate: %s", cudaGetErrorString(e));
+  }
+  *out = new svodb_graph{g, x};
+  return SVODB_OK;
+}
+int svodb_graph_replay(svodb_graph* g, void* stream) {
+  GUARD("graph_replay");
+  if (g == nullptr) return fail(SVODB_ERR_UNREALIZED, "graph_replay: null graph");
+  cudaError_t e = cudaGraphLaunch(g->exec, (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    if (sticky(e)) g_poisoned = true;
+    return fail(SVODB_ERR_LAUNCH, "graph_replay: %s", cudaGetErrorString(e));
+  }
+  return SVODB_OK;
+}
+int svodb_graph_free(svodb_graph* g) {
+  if (g == nullptr) return SVODB_OK;
+  cudaGraphExecDestroy(g->exec);
+  cudaGraphDestroy(g->graph);
+  delete g;
+  return SVODB_OK;
+}
+
+int svodb_alloc(size_t bytes, int32_t kind, void** out) {
+  GUARD("alloc");
+  if (out == nullptr) return fail(SVODB_ERR_UNREALIZED, "alloc: null out");
+  cudaError_t e = kind == 1 ? cudaMallocHost(out, bytes) : cudaMalloc(out, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SVODB_ERR_LAUNCH, "alloc: %s", cudaGetErrorString(e));
+  }
+  return SVODB_OK;
+}
+int svodb_free(void* ptr, int32_t kind) {
+  if (ptr == nullptr) return SVODB_OK;
+  cudaError_t e = kind == 1 ? cudaFreeHost(ptr) : cudaFree(ptr);
+  if (e != cudaSuccess) return fail(SVODB_ERR_LAUNCH, "free: %s", cudaGetErrorString(e));
+  return SVODB_OK;
+}
+int svodb_copy_h2d(void* dst, const void* src, size_t bytes, void* stream) {
+  GUARD("copy_h2d");
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(SVODB_ERR_LAUNCH, "copy_h2d: %s", cudaGetErrorString(e));
+  return SVODB_OK;
+}
+int svodb_copy_d2h(void* dst, const void* src, size_t bytes, void* stream) {
+  GUARD("copy_d2h");
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(SVODB_ERR_LAUNCH, "copy_d2h: %s", cudaGetErrorString(e));
+  return SVODB_OK;
+}
+int svodb_stream_sync(void* stream) {
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    if (sticky(e)) g_poisoned = true;
+    return fail(SVODB_ERR_LAUNCH, "stream_sync: %s", cudaGetErrorString(e));
+  }
+  return SVODB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,494 @@
+// tcgen05 GEMM with the fused epilogue of `ops::linear`:
+//   C[M,N] = scale * act(A[M,K] . W[N,K]^T + bias) (* up) -> RoPE turn -> + residual
+// (order of tk/src/kernels/gemm.rs:605-651; gated weights are `[2N,K]`, gate rows
+// over up rows, gemm.rs:21-23,547-559; in-store RoPE, gemm.rs:670-718).
+//
+// Blackwell design (one persistent CTA per SM, 320 threads):
+//   warp 0      TMA producer: A tile 128x64 and W tile BNx64 per k-block into a
+//               128B-swizzled shared-memory ring (non-multicast TMA, OOB rows and
+//               the K tail zero-filled by the hardware).
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma 128xBNx16
+//               (kind::f16, f32 accumulate) into one of two TMEM accumulators;
+//               tcgen05.commit releases ring slots and publishes the accumulator.
+//   warps 2..9  epilogue: tcgen05.ld 32 columns at a time (one output row per
+//               thread), bias / activation / gate / scale / RoPE / residual in
+//               f32, one rounding, 64-byte contiguous stores per row. The second
+//               accumulator lets the epilogue of tile i overlap the MMAs of i+1.
+// A gated tile loads gate rows and up rows into one BN-row B tile, so a single
+// MMA produces [gate | up] side by side in TMEM.
+//
+// Tiles are walked in groups of 8 tile-rows (the reference's TileOrder::DEFAULT,
+// gemm.rs:164,198-213) so concurrently running CTAs share W tiles in L2.
+//
+// Every mbarrier wait is bounded: on timeout the kernel records a status code,
+// drains and frees its TMEM.
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "svodb.h"
+#include "tensormap.h"
+
+namespace svodb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageBytes = (BM + BN) * BK * 2;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct Params {
+  int64_t m;
+  int n, k;
+  int tiles_m, tiles_n;
+  int out_bn;        // output columns per tile: BN, or BN/2 when gated
+  int gated;
+  int act;
+  int has_scale;
+  float scale;
+  const void* bias;
+  const void* residual;
+  void* c;
+  int64_t ldr, ldc;
+  const void* rope_cos;
+  const void* rope_sin;
+  int rope_width;     // heads * head_dim turned columns (0 = none)
+  int rope_head_dim;
+  int64_t rope_seq;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mt, int& nt) {
+  const int per_group = 8 * tiles_n;
+  const int group = t / per_group;
+  const int first = group * 8;
+  const int gsize = tiles_m - first < 8 ? tiles_m - first : 8;
+  const int r = t - group * per_group;
+  mt = first + r % gsize;
+  nt = r / gsize;
+}
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, bool ok, float (&f)[8]) {
+  if (ok) {
+    uint4 u = ldg128(p);
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 v = Elem<T>::unpack(uu[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+  }
+}
+
+__device__ __forceinline__ void act32(float (&x)[32], int act) {
+  switch (act) {
+    case kActGelu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = gelu_f(x[i]);
+      break;
+    case kActSilu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = silu_f(x[i]);
+      break;
+    case kActGeluTanh:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = gelu_tanh_f(x[i]);
+      break;
+    default: break;
+  }
+}
+
+// Loads 32 accumulator columns starting at `col` of this warp's lane quarter
+// and adds the bias of output columns `n_at ..`.
+template <typename T>
+__device__ __forceinline__ void acc32(uint32_t taddr, const T* bias, int n_at, int n_lim, float (&x)[32]) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
+  if (bias != nullptr) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      float b[8];
+      load8<T>(bias + n_at + v * 8, n_at + v * 8 < n_lim, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[v * 8 + i] += b[i];
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store32(const Params& p, int64_t row, bool row_ok, int n_at, float (&x)[32]) {
+  const T* res = (const T*)p.residual;
+  T* c = (T*)p.c;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const int n = n_at + v * 8;
+    const bool ok = row_ok && n < p.n;
+    if (res != nullptr) {
+      float r[8];
+      load8<T>(res + row * p.ldr + n, ok, r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[v * 8 + i] += r[i];
+    }
+    if (ok) {
+      stg128(c + row * p.ldc + n,
+             make_uint4(Elem<T>::pack(x[v * 8 + 0], x[v * 8 + 1]), Elem<T>::pack(x[v * 8 + 2], x[v * 8 + 3]),
+                        Elem<T>::pack(x[v * 8 + 4], x[v * 8 + 5]), Elem<T>::pack(x[v * 8 + 6], x[v * 8 + 7])));
+    }
+  }
+}
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                   const Params p) {
+  using C = Cfg<BN>;
+  constexpr int S = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // The swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * C::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + S;
+  uint64_t* acc_full = bars + 2 * S;
+  uint64_t* acc_empty = bars + 2 * S + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.k + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], kEpiWarps);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      uint32_t issued = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mt, nt;
+        tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
+        const int m0 = mt * BM;
+        const int n0 = nt * p.out_bn;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + (size_t)s * C::kStageBytes;
+          uint8_t* b_dst = a_dst + BM * BK * 2;
+          mbar_expect_tx(&full[s], (uint32_t)C::kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, m0);
+          if (p.gated) {
+            tma_load_2d(b_dst, &tmap_w, &full[s], kb * BK, n0);
+            tma_load_2d(b_dst + (BN / 2) * BK * 2, &tmap_w, &full[s], kb * BK, p.n + n0);
+          } else {
+            tma_load_2d(b_dst, &tmap_w, &full[s], kb * BK, n0);
+          }
+          ++issued;
+          if (++s == S) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Error path: let the copies already in flight land before the CTA's
+        // shared memory is released (bounded).
+        const uint32_t back = issued < (uint32_t)S ? issued : (uint32_t)S;
+        int ss = s;
+        uint32_t pp = ph;
+        for (uint32_t i = 0; i < back; ++i) {
+          if (--ss < 0) {
+            ss = S - 1;
+            pp ^= 1;
+          }
+          for (uint32_t it = 0; it < (1u << 16); ++it)
+            if (mbar_try_wait(&full[ss], pp)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(Elem<T>::kUmmaFormat, BM, BN, 0, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      int as = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[as], aph ^ 1, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::kStageBytes);
+          const uint32_t b_addr = a_addr + BM * BK * 2;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t a_desc = umma_desc_sw128(a_addr + k4 * 32, 16, 1024);
+            const uint64_t b_desc = umma_desc_sw128(b_addr + k4 * 32, 16, 1024);
+            umma_ss(d_tmem, a_desc, b_desc, idesc, (kb | k4) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+          if (++s == S) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[as]);
+        if (++as == 2) {
+          as = 0;
+          aph ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*(warp%4) ..
+    const int chalf = ew >> 2;     // which half of the tile's output columns
+    const T* bias = (const T*)p.bias;
+    int as = 0;
+    uint32_t aph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
+      const int64_t row = (int64_t)mt * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const int n0 = nt * p.out_bn;
+      if (!mbar_wait(&acc_full[as], aph, p.status)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
+      const int cols = p.out_bn / 2;  // output columns this warp covers
+      const int c_lo = chalf * cols;
+      if (p.rope_width > 0 && n0 + c_lo < p.rope_width) {
+        // In-store RoPE: whole heads, pairs (c, c + head_dim/2) from two chunks.
+        const int hd = p.rope_head_dim, half = hd / 2;
+        const T* cos = (const T*)p.rope_cos;
+        const T* sin = (const T*)p.rope_sin;
+        const int64_t pos = row_ok ? row % p.rope_seq : 0;
+        for (int h0 = c_lo; h0 < c_lo + cols; h0 += hd) {
+          const bool turned = n0 + h0 < p.rope_width;
+          for (int j = 0; j < half; j += 32) {
+            float x1[32], x2[32];
+            acc32<T>(t_acc + (uint32_t)(h0 + j), bias, n0 + h0 + j, p.n, x1);
+            acc32<T>(t_acc + (uint32_t)(h0 + half + j), bias, n0 + h0 + half + j, p.n, x2);
+            if (turned) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float cs[8], sn[8];
+                load8<T>(cos + pos * half + j + v * 8, true, cs);
+                load8<T>(sin + pos * half + j + v * 8, true, sn);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float a = x1[v * 8 + i], b = x2[v * 8 + i];
+                  x1[v * 8 + i] = a * cs[i] - b * sn[i];
+                  x2[v * 8 + i] = a * sn[i] + b * cs[i];
+                }
+              }
+            }
+            store32<T>(p, row, row_ok, n0 + h0 + j, x1);
+            store32<T>(p, row, row_ok, n0 + h0 + half + j, x2);
+          }
+        }
+      } else {
+        for (int c0 = c_lo; c0 < c_lo + cols; c0 += 32) {
+          float x[32];
+          acc32<T>(t_acc + (uint32_t)c0, bias, n0 + c0, p.n, x);
+          act32(x, p.act);
+          if (p.gated) {
+            float u[32];
+            acc32<T>(t_acc + (uint32_t)(BN / 2 + c0), bias != nullptr ? bias + p.n : nullptr, n0 + c0, p.n, u);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] *= u[i];
+          }
+          if (p.has_scale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] *= p.scale;
+          }
+          store32<T>(p, row, row_ok, n0 + c0, x);
+        }
+      }
+      // All of this warp's TMEM reads of the tile have completed (wait::ld in acc32).
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+      if (++as == 2) {
+        as = 0;
+        aph ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <typename T, int BN>
+int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg, size_t cfg_len) {
+  using C = Cfg<BN>;
+  Params p = p0;
+  p.out_bn = a.gated ? BN / 2 : BN;
+  p.tiles_m = (int)((a.m + BM - 1) / BM);
+  p.tiles_n = (a.n + p.out_bn - 1) / p.out_bn;
+  CUtensorMap ta, tw;
+  const int dt = a.dtype;
+  if (!make_tmap_2d(&ta, a.a, dt, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, BM)) return -1;
+  const uint64_t w_rows = (uint64_t)(a.gated ? 2 * a.n : a.n);
+  if (!make_tmap_2d(&tw, a.w, dt, (uint64_t)a.k, w_rows, (uint64_t)a.ldw, BK, a.gated ? BN / 2 : BN)) return -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)C::kSmemBytes) != cudaSuccess)
+      return -1;
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tc_kernel<T, BN><<<grid, kThreads, C::kSmemBytes, s>>>(ta, tw, p);
+  if (cfg != nullptr)
+    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d}", BM, BN, BK, C::kStages, a.gated, grid);
+  return 0;
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool gemm_tc_covers(const GemmArgs& a) {
+  // The reference's kernel gate (tk/src/ops/shape.rs:120-139): 16-bit operands,
+  // N a multiple of 8, K a multiple of 16. Plus what TMA and the 128-bit
+  // epilogue accesses need: 16-byte aligned bases and row strides.
+  if (a.dtype != SVODB_BF16 && a.dtype != SVODB_F16) return false;
+  if (a.n % 8 != 0 || a.k % 16 != 0 || a.m <= 0 || a.n <= 0 || a.k <= 0) return false;
+  if (a.m > 0x7fffffffLL) return false;
+  if (a.lda % 8 != 0 || a.ldw % 8 != 0 || a.ldc % 8 != 0) return false;
+  if (!aligned16(a.a) || !aligned16(a.w) || !aligned16(a.c)) return false;
+  if (a.bias != nullptr && !aligned16(a.bias)) return false;
+  if (a.residual != nullptr && (!aligned16(a.residual) || a.ldr % 8 != 0)) return false;
+  if (a.rope_cos != nullptr) {
+    // A tile turns whole heads: pairs must sit in two 32-column chunks of one
+    // warp's column range.
+    const int hd = a.rope_head_dim;
+    if (hd != 64 && hd != 128) return false;
+    if (a.gated || a.act != kActNone || a.residual != nullptr || a.has_scale) return false;
+    if (!aligned16(a.rope_cos) || !aligned16(a.rope_sin)) return false;
+  }
+  return true;
+}
+
+int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
+  if (!gemm_tc_covers(a)) return 1;
+  Params p{};
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.gated = a.gated;
+  p.act = a.act;
+  p.has_scale = a.has_scale;
+  p.scale = a.scale;
+  p.bias = a.bias;
+  p.residual = a.residual;
+  p.c = a.c;
+  p.ldr = a.ldr;
+  p.ldc = a.ldc;
+  p.rope_cos = a.rope_cos;
+  p.rope_sin = a.rope_sin;
+  p.rope_width = a.rope_cos != nullptr ? a.rope_heads * a.rope_head_dim : 0;
+  p.rope_head_dim = a.rope_head_dim;
+  p.rope_seq = a.rope_seq;
+  p.status = a.status;
+  const int sms = sm_count();
+  // Tile width: the widest MMA whose tile count still fills the SMs. A gated
+  // tile spends half its MMA width on the up rows; a turned tile must hold
+  // whole heads per epilogue warp (64 columns at least).
+  const int64_t tiles_m = (a.m + BM - 1) / BM;
+  auto tiles = [&](int bn) { return tiles_m * ((a.n + (a.gated ? bn / 2 : bn) - 1) / (a.gated ? bn / 2 : bn)); };
+  int bn = 256;
+  const int min_bn = a.gated ? 128 : (a.rope_cos != nullptr ? 2 * a.rope_head_dim : 64);
+  while (bn > min_bn && tiles(bn) < sms) bn /= 2;
+  if (bn < min_bn) bn = min_bn;
+  if (bn > 256) return 1;
+  int rc;
+  if (a.dtype == SVODB_BF16) {
+    rc = bn == 256 ? run<__nv_bfloat16, 256>(a, p, sms, s, cfg, cfg_len)
+       : bn == 128 ? run<__nv_bfloat16, 128>(a, p, sms, s, cfg, cfg_len)
+                   : run<__nv_bfloat16, 64>(a, p, sms, s, cfg, cfg_len);
+  } else {
+    rc = bn == 256 ? run<__half, 256>(a, p, sms, s, cfg, cfg_len)
+       : bn == 128 ? run<__half, 128>(a, p, sms, s, cfg, cfg_len)
+                   : run<__half, 64>(a, p, sms, s, cfg, cfg_len);
+  }
+  return rc;
+}
+
+}  // namespace svodb

@@ -1,0 +1,212 @@
+// Small kernels around the op layer that the encoder callers need: token
+// embedding lookup (with XLM-R position ids), pooling + L2 normalisation, and
+// RoPE tables. All HBM-bound or negligible; written for coalesced access.
+#include "common.cuh"
+#include "kernels.h"
+#include "svodb.h"
+
+namespace svodb {
+
+namespace {
+
+// out[b,t,:] = table[ids[b,t]] (+ pos_table[pos_id] + type_row), each add
+// rounded to the element type as the graph's 16-bit adds are
+// (model/src/xlm_roberta/embeddings.rs:53-63). Position ids:
+// `cumsum(ids != pad) * (ids != pad) + pad` (position_ids.rs:27-32).
+// One block per (batch row, group of kTok tokens).
+constexpr int kTok = 8;
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(256)
+    embed_kernel(const I* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ pos_table,
+                 const T* __restrict__ type_row, int64_t pad_id, T* __restrict__ out, int64_t t_len, int d,
+                 int64_t vocab, int64_t max_pos) {
+  __shared__ int red[8];
+  __shared__ int64_t tok_id[kTok];
+  __shared__ int64_t tok_pos[kTok];
+  const int64_t b = blockIdx.y;
+  const int64_t t0 = (int64_t)blockIdx.x * kTok;
+  const I* row = ids + b * t_len;
+  const int tid = threadIdx.x;
+  int before = 0;
+  if (pos_table != nullptr && pad_id >= 0) {
+    int cnt = 0;
+    for (int64_t i = tid; i < t0; i += 256) cnt += (int64_t)row[i] != pad_id;
+    cnt = (int)warp_sum((float)cnt);  // counts stay below 2^24: exact in f32
+    if ((tid & 31) == 0) red[tid >> 5] = cnt;
+    __syncthreads();
+    for (int i = 0; i < 8; ++i) before += red[i];
+  }
+  if (tid == 0) {
+    int run = before;
+    for (int j = 0; j < kTok; ++j) {
+      const int64_t t = t0 + j;
+      if (t >= t_len) break;
+      int64_t id = (int64_t)row[t];
+      const bool real = id != pad_id;
+      run += real ? 1 : 0;
+      tok_pos[j] = pad_id >= 0 ? (real ? run : 0) + pad_id : t;
+      tok_id[j] = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    }
+  }
+  __syncthreads();
+  const int vec = d / 8;
+  for (int j = 0; j < kTok; ++j) {
+    const int64_t t = t0 + j;
+    if (t >= t_len) break;
+    const T* src = table + tok_id[j] * d;
+    int64_t p = tok_pos[j];
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+    const T* psrc = pos_table != nullptr ? pos_table + p * d : nullptr;
+    T* dst = out + (b * t_len + t) * d;
+    for (int c = tid; c < vec; c += 256) {
+      uint4 u = ldg128(src + c * 8);
+      if (psrc != nullptr || type_row != nullptr) {
+        uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+        if (psrc != nullptr) {
+          uint4 pu = ldg128(psrc + c * 8);
+          const uint32_t pp[4] = {pu.x, pu.y, pu.z, pu.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 a = Elem<T>::unpack(uu[i]), q = Elem<T>::unpack(pp[i]);
+            uu[i] = Elem<T>::pack(a.x + q.x, a.y + q.y);
+          }
+        }
+        if (type_row != nullptr) {
+          uint4 tu = ldg128(type_row + c * 8);
+          const uint32_t tt[4] = {tu.x, tu.y, tu.z, tu.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 a = Elem<T>::unpack(uu[i]), q = Elem<T>::unpack(tt[i]);
+            uu[i] = Elem<T>::pack(a.x + q.x, a.y + q.y);
+          }
+        }
+        u = make_uint4(uu[0], uu[1], uu[2], uu[3]);
+      }
+      stg128(dst + c * 8, u);
+    }
+  }
+}
+
+// Pooling, pass 1: out[b, c] = pooled value in f32 (un-normalised).
+// grid (ceil(D/128), B), 256 threads: thread = (token lane 0..1, column 0..127).
+template <typename T>
+__global__ void __launch_bounds__(256)
+    pool_kernel(const T* __restrict__ hidden, const void* __restrict__ aux, int aux_i32, int mode,
+                float* __restrict__ out, int64_t out_row_stride, int64_t l_len, int d) {
+  __shared__ float part[2][128];
+  const int64_t b = blockIdx.y;
+  const int col = blockIdx.x * 128 + (threadIdx.x & 127);
+  const int tl = threadIdx.x >> 7;
+  const T* h = hidden + b * l_len * d;
+  float acc = 0.f, cnt = 0.f;
+  if (mode == 1) {
+    for (int64_t t = tl; t < l_len; t += 2) {
+      const int m = aux_i32 ? ((const int32_t*)aux)[b * l_len + t] : (int)((const uint8_t*)aux)[b * l_len + t];
+      if (m != 0) {
+        cnt += 1.f;
+        if (col < d) acc += Elem<T>::to_f(h[t * d + col]);
+      }
+    }
+  } else if (tl == 0 && col < d) {
+    int64_t t = 0;
+    if (mode == 2) {
+      t = (int64_t)((const int32_t*)aux)[b] - 1;
+      t = t < 0 ? 0 : (t > l_len - 1 ? l_len - 1 : t);
+    }
+    acc = Elem<T>::to_f(h[t * d + col]);
+  }
+  __shared__ float cnts[2];
+  part[tl][threadIdx.x & 127] = acc;
+  if ((threadIdx.x & 127) == 0) cnts[tl] = cnt;
+  __syncthreads();
+  if (tl == 0 && col < d) {
+    float v = part[0][threadIdx.x] + part[1][threadIdx.x];
+    if (mode == 1) v = v / fmaxf(cnts[0] + cnts[1], 1e-9f);
+    out[b * out_row_stride + col] = v;
+  }
+}
+
+// Pass 2: x / (||x||_2 + f32::MIN_POSITIVE) in place, one block per row.
+__global__ void __launch_bounds__(256) l2_kernel(float* __restrict__ out, int64_t out_row_stride, int d) {
+  __shared__ float red[8];
+  float* row = out + (int64_t)blockIdx.x * out_row_stride;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < d; i += 256) sq = fmaf(row[i], row[i], sq);
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = 1.0f / (sqrtf(tot) + 1.17549435e-38f);
+  for (int i = threadIdx.x; i < d; i += 256) row[i] *= inv;
+}
+
+// cos/sin of position * theta^(-2i/D), angles and functions in f32, cast last
+// (tensor/src/transformer.rs:130-164).
+template <typename T>
+__global__ void rope_table_kernel(float theta, const int32_t* __restrict__ positions, int64_t n_pos, int half,
+                                  float expo_step, T* __restrict__ cos, T* __restrict__ sin) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_pos * half) return;
+  const int64_t p = idx / half;
+  const int i = (int)(idx % half);
+  const float pos = positions != nullptr ? (float)positions[p] : (float)p;
+  const float inv_freq = powf(theta, (float)i * expo_step);
+  const float ang = pos * inv_freq;
+  cos[idx] = Elem<T>::from_f(cosf(ang));
+  sin[idx] = Elem<T>::from_f(sinf(ang));
+}
+
+}  // namespace
+
+void launch_embed(const EmbedArgs& a, cudaStream_t s) {
+  if (a.batch * a.t == 0) return;
+  dim3 grid((unsigned)((a.t + kTok - 1) / kTok), (unsigned)a.batch);
+#define SVODB_EMBED(T, I)                                                                                         \
+  embed_kernel<T, I><<<grid, 256, 0, s>>>((const I*)a.ids, (const T*)a.table, (const T*)a.pos_table,              \
+                                          (const T*)a.type_row, a.pad_id, (T*)a.out, a.t, a.d, a.vocab, a.max_pos)
+  if (a.dtype == SVODB_BF16) {
+    if (a.ids_i64) SVODB_EMBED(__nv_bfloat16, int64_t);
+    else SVODB_EMBED(__nv_bfloat16, int32_t);
+  } else {
+    if (a.ids_i64) SVODB_EMBED(__half, int64_t);
+    else SVODB_EMBED(__half, int32_t);
+  }
+#undef SVODB_EMBED
+}
+
+void launch_pool(const PoolArgs& a, cudaStream_t s) {
+  if (a.batch == 0) return;
+  dim3 grid((unsigned)((a.d + 127) / 128), (unsigned)a.batch);
+  if (a.dtype == SVODB_BF16)
+    pool_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
+                                                    a.out_row_stride, a.l, a.d);
+  else if (a.dtype == SVODB_F16)
+    pool_kernel<__half><<<grid, 256, 0, s>>>((const __half*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
+                                             a.out_row_stride, a.l, a.d);
+  else
+    pool_kernel<float><<<grid, 256, 0, s>>>((const float*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
+                                            a.out_row_stride, a.l, a.d);
+  if (a.normalize) l2_kernel<<<(unsigned)a.batch, 256, 0, s>>>(a.out, a.out_row_stride, a.d);
+}
+
+void launch_rope_table(double theta, const int32_t* positions, int64_t n_pos, int head_dim, void* cos, void* sin,
+                       int dtype, cudaStream_t s) {
+  const int half = head_dim / 2;
+  const int64_t n = n_pos * half;
+  if (n == 0) return;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  const float step = (float)(-2.0 / head_dim);
+  if (dtype == SVODB_BF16)
+    rope_table_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((float)theta, positions, n_pos, half, step,
+                                                            (__nv_bfloat16*)cos, (__nv_bfloat16*)sin);
+  else if (dtype == SVODB_F16)
+    rope_table_kernel<__half><<<blocks, 256, 0, s>>>((float)theta, positions, n_pos, half, step, (__half*)cos,
+                                                     (__half*)sin);
+  else
+    rope_table_kernel<float><<<blocks, 256, 0, s>>>((float)theta, positions, n_pos, half, step, (float*)cos,
+                                                    (float*)sin);
+}
+
+}  // namespace svodb

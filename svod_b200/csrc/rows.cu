@@ -1,0 +1,197 @@
+// LayerNorm / RMSNorm over the last dim, optionally after a residual add whose
+// rounded sum is written out and is what gets normalised.
+//
+// Semantics follow tk/src/kernels/rows.rs:41-115: f32 reductions, biased
+// variance from the centred values, `rsqrt(var + eps)`, weight (and bias) in
+// f32, one rounding at the store; the fused sum is rounded to the element type
+// first (rows.rs:77-85).
+//
+// HBM-bound: one warp per row, 128-bit loads/stores, the whole row held in
+// registers so x (and the residual) are read exactly once.
+#include "common.cuh"
+#include "kernels.h"
+#include "svodb.h"
+
+namespace svodb {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+// d = SPANS * 256: lane l owns elements [span*256 + l*8, +8).
+template <typename T, int SPANS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    norm_rows_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                     const T* __restrict__ b, T* __restrict__ out, T* __restrict__ sum, int64_t rows, float eps,
+                     int layer) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  constexpr int D = SPANS * 256;
+  const T* xr = x + row * D;
+  float v[SPANS][8];
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    const int off = s * 256 + lane * 8;
+    uint4 u = ldg128(xr + off);
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = Elem<T>::unpack(uu[i]);
+      v[s][2 * i] = f.x;
+      v[s][2 * i + 1] = f.y;
+    }
+    if (res != nullptr) {
+      uint4 r = ldg128(res + row * D + off);
+      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+      uint32_t packed[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = Elem<T>::unpack(rr[i]);
+        packed[i] = Elem<T>::pack(v[s][2 * i] + f.x, v[s][2 * i + 1] + f.y);
+        float2 g = Elem<T>::unpack(packed[i]);
+        v[s][2 * i] = g.x;
+        v[s][2 * i + 1] = g.y;
+      }
+      stg128(sum + row * D + off, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+    }
+  }
+  float mean = 0.f;
+  if (layer) {
+    float acc = 0.f;
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc += v[s][i];
+    mean = warp_sum(acc) * (1.0f / D);
+  }
+  float sq = 0.f;
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[s][i] -= mean;
+      sq = fmaf(v[s][i], v[s][i], sq);
+    }
+  const float inv = rsqrtf(warp_sum(sq) * (1.0f / D) + eps);
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    const int off = s * 256 + lane * 8;
+    uint4 wu = ldg128(w + off);
+    const uint32_t ww[4] = {wu.x, wu.y, wu.z, wu.w};
+    uint32_t bb[4] = {0, 0, 0, 0};
+    if (b != nullptr) {
+      uint4 bu = ldg128(b + off);
+      bb[0] = bu.x, bb[1] = bu.y, bb[2] = bu.z, bb[3] = bu.w;
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 wf = Elem<T>::unpack(ww[i]);
+      float2 bf = Elem<T>::unpack(bb[i]);
+      float y0 = v[s][2 * i] * inv * wf.x;
+      float y1 = v[s][2 * i + 1] * inv * wf.y;
+      if (b != nullptr) {
+        y0 += bf.x;
+        y1 += bf.y;
+      }
+      packed[i] = Elem<T>::pack(y0, y1);
+    }
+    stg128(out + row * D + off, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+  }
+}
+
+// Any d, any float type: one block per row, three passes served by L1/L2.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    norm_rows_generic_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                             const T* __restrict__ b, T* __restrict__ out, T* __restrict__ sum, int d, float eps,
+                             int layer) {
+  __shared__ float red[8];
+  __shared__ float bcast;
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * d;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  auto value = [&](int i) -> float {
+    float f = Elem<T>::to_f(xr[i]);
+    if (res != nullptr) f = Elem<T>::to_f(Elem<T>::from_f(f + Elem<T>::to_f(res[row * d + i])));
+    return f;
+  };
+  auto block_sum = [&](float v) -> float {
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+      float t = lane < 8 ? red[lane] : 0.f;
+      t = warp_sum(t);
+      if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    return bcast;
+  };
+  float acc = 0.f;
+  for (int i = tid; i < d; i += 256) {
+    float f = value(i);
+    if (res != nullptr) sum[row * d + i] = Elem<T>::from_f(f);
+    acc += f;
+  }
+  const float mean = layer ? block_sum(acc) / d : 0.f;
+  float sq = 0.f;
+  for (int i = tid; i < d; i += 256) {
+    float c = value(i) - mean;
+    sq = fmaf(c, c, sq);
+  }
+  const float inv = rsqrtf(block_sum(sq) / d + eps);
+  for (int i = tid; i < d; i += 256) {
+    float y = (value(i) - mean) * inv * Elem<T>::to_f(w[i]);
+    if (b != nullptr) y += Elem<T>::to_f(b[i]);
+    out[row * d + i] = Elem<T>::from_f(y);
+  }
+}
+
+template <typename T, int SPANS>
+void run_rows(const NormArgs& a, cudaStream_t s) {
+  const unsigned blocks = (unsigned)((a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  norm_rows_kernel<T, SPANS><<<blocks, kWarpsPerBlock * 32, 0, s>>>(
+      (const T*)a.x, (const T*)a.residual, (const T*)a.w, (const T*)a.b, (T*)a.out, (T*)a.sum, a.rows, a.eps, a.layer);
+}
+
+template <typename T>
+bool run_rows_dispatch(const NormArgs& a, cudaStream_t s) {
+  switch (a.d / 256) {
+    case 1: run_rows<T, 1>(a, s); return true;
+    case 2: run_rows<T, 2>(a, s); return true;
+    case 3: run_rows<T, 3>(a, s); return true;
+    case 4: run_rows<T, 4>(a, s); return true;
+    case 5: run_rows<T, 5>(a, s); return true;
+    case 6: run_rows<T, 6>(a, s); return true;
+    case 7: run_rows<T, 7>(a, s); return true;
+    case 8: run_rows<T, 8>(a, s); return true;
+    default: return false;
+  }
+}
+
+template <typename T>
+void run_generic(const NormArgs& a, cudaStream_t s) {
+  norm_rows_generic_kernel<T><<<(unsigned)a.rows, 256, 0, s>>>((const T*)a.x, (const T*)a.residual, (const T*)a.w,
+                                                                 (const T*)a.b, (T*)a.out, (T*)a.sum, a.d, a.eps,
+                                                                 a.layer);
+}
+
+}  // namespace
+
+int launch_norm(const NormArgs& a, cudaStream_t s) {
+  if (a.rows == 0) return 1;
+  // The warp-per-row kernel covers what the reference's kernel covers: 16-bit
+  // rows of 256..2048 elements in multiples of 256 (tk/src/ops/config/norm.rs:19-24).
+  const bool fits = a.d % 256 == 0 && a.d >= 256 && a.d <= 2048;
+  if (fits && a.dtype == SVODB_BF16 && run_rows_dispatch<__nv_bfloat16>(a, s)) return 1;
+  if (fits && a.dtype == SVODB_F16 && run_rows_dispatch<__half>(a, s)) return 1;
+  if (a.dtype == SVODB_BF16) run_generic<__nv_bfloat16>(a, s);
+  else if (a.dtype == SVODB_F16) run_generic<__half>(a, s);
+  else run_generic<float>(a, s);
+  return 0;
+}
+
+}  // namespace svodb
