@@ -322,9 +322,11 @@ def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=Non
         scale = float(np.float32(1.0 / math.sqrt(D)))
     else:
         scale = float(np.float32(scale))
-    kk = np.repeat(k, group, axis=2)
-    vv = np.repeat(v, group, axis=2)
-    s = np.einsum("bihd,bjhd->bhij", q, kk) * scale
+    # head-major views so the two contractions are batched BLAS matmuls
+    qh = q.transpose(0, 2, 1, 3)
+    kh = np.repeat(k, group, axis=2).transpose(0, 2, 1, 3)
+    vh = np.repeat(v, group, axis=2).transpose(0, 2, 1, 3)
+    s = np.matmul(qh, kh.transpose(0, 1, 3, 2)) * scale
     if bias is not None:
         s = s + np.asarray(bias, dtype=np.float64)
     i = np.arange(T).reshape(1, 1, T, 1)
@@ -353,7 +355,7 @@ def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=Non
         wts = np.exp(s - np.where(empty, 0.0, mx))
     wts = np.where(hidden, 0.0, wts)
     l = wts.sum(axis=-1, keepdims=True)
-    out = np.einsum("bhij,bjhd->bihd", wts / np.where(empty, 1.0, l), vv)
+    out = np.matmul(wts / np.where(empty, 1.0, l), vh).transpose(0, 2, 1, 3)
     out = round_to(dtype, out)
     if return_lse:
         with np.errstate(divide="ignore"):

@@ -396,6 +396,32 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       seg_me = p.seg_start[b * p.t + (row_ok ? row : i_last)];
       seg_last = p.seg_start[b * p.t + i_last];
     }
+    // Every mask but the bool key mask is an interval of keys per query row:
+    // this row sees keys [vis_lo, vis_hi) (and, under a general key mask, the set
+    // bits of the bitmask among them).
+    int64_t vis_lo64 = 0, vis_hi64 = ctx.len;
+    if (p.causal && row + 1 < vis_hi64) vis_hi64 = row + 1;
+    if (p.has_window) {
+      if (row - p.win_left > vis_lo64) vis_lo64 = row - p.win_left;
+      if (row + p.win_right + 1 < vis_hi64) vis_hi64 = row + p.win_right + 1;
+    }
+    if (p.has_chunk) {
+      const int64_t ci = row / p.chunk_size;
+      if ((ci + p.chunk_right + 1) * p.chunk_size < vis_hi64) vis_hi64 = (ci + p.chunk_right + 1) * p.chunk_size;
+      if (p.chunk_left >= 0 && (ci - p.chunk_left) * p.chunk_size > vis_lo64) vis_lo64 = (ci - p.chunk_left) * p.chunk_size;
+    }
+    if (p.seg_start != nullptr && seg_me > vis_lo64) vis_lo64 = seg_me;
+    const int vis_lo = (int)vis_lo64, vis_hi = (int)(vis_hi64 < vis_lo64 ? vis_lo64 : vis_hi64);
+    // Visibility of keys base .. base+31 as a bit word.
+    auto vis_word = [&](int base) -> uint32_t {
+      int a = vis_lo - base, bnd = vis_hi - base;
+      a = a < 0 ? 0 : a;
+      bnd = bnd > 32 ? 32 : bnd;
+      uint32_t w = 0;
+      if (bnd > a) w = (bnd == 32 ? 0xffffffffu : ((1u << bnd) - 1u)) & ~((1u << a) - 1u);
+      if (ctx.general_mask) w &= mask_bits[base >> 5];
+      return w;
+    };
     float m_run = -INFINITY;  // running maximum, scaled log2 units
     float l_run = 0.f;
     uint32_t s_phase = 0;
@@ -413,20 +439,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
       if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
 
-      auto hidden = [&](int64_t jj) -> bool {
-        if (jj >= ctx.len) return true;
-        if (p.causal && jj > row) return true;
-        if (p.has_window && (jj + p.win_left < row || jj > row + p.win_right)) return true;
-        if (p.has_chunk) {
-          const int64_t cj = jj / p.chunk_size, ci = row / p.chunk_size;
-          if (cj > ci + p.chunk_right) return true;
-          if (p.chunk_left >= 0 && cj + p.chunk_left < ci) return true;
-        }
-        if (ctx.general_mask && ((mask_bits[jj >> 5] >> (jj & 31)) & 1u) == 0) return true;
-        if (p.seg_start != nullptr && jj < seg_me) return true;
-        return false;
-      };
-
       // pass 1: row maximum of the visible raw scores
       float mx = -INFINITY;
 #pragma unroll 1
@@ -435,9 +447,9 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_ld32(s_tmem + c, sr);
         tmem_ld_wait();
         if (need_mask) {
+          const uint32_t vw = vis_word((int)j0 + c);
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (!hidden(j0 + c + e)) mx = fmaxf(mx, __uint_as_float(sr[e]));
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, (vw >> e) & 1u ? __uint_as_float(sr[e]) : -INFINITY);
         } else {
           float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
@@ -485,10 +497,11 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_ld_wait();
         float pv[32];
         if (need_mask) {
+          const uint32_t vw = vis_word((int)j0 + c);
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const float x = ex2_approx(fmaf(__uint_as_float(sr[e]), sl2, -m_use));
-            pv[e] = hidden(j0 + c + e) ? 0.f : x;
+            pv[e] = (vw >> e) & 1u ? x : 0.f;
           }
         } else {
 #pragma unroll

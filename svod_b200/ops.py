@@ -151,9 +151,16 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(rc: int):
+# Kernel launches issued through this module since import (an op that runs two
+# kernels, e.g. pooling + L2 or a split attention + merge, counts both).
+launches = 0
+
+
+def _check(rc: int, kernels: int = 1):
+    global launches
     if rc != L.OK:
         raise OpsError(rc, L.load().svodb_last_error().decode())
+    launches += kernels
 
 
 def supported(device=None) -> bool:
@@ -173,7 +180,7 @@ def chosen() -> Optional[str]:
 
 def device_status() -> None:
     """Raises if a bounded device-side wait ran out since the last check."""
-    _check(L.load().svodb_device_status(_stream()))
+    _check(L.load().svodb_device_status(_stream()), 0)
 
 
 # --------------------------------------------------------------------------- linear
@@ -280,6 +287,8 @@ def attention_packed(qkv: torch.Tensor, heads: int, kv_heads: int, opts: Optiona
     """`ops::attention_packed` (tk/src/ops/attention.rs:107-122): the kernel
     reads q, k and v in place from `qkv [B, T, (heads + 2 kv_heads) D]`."""
     opts = opts or Attn()
+    if kv_heads <= 0 or heads % kv_heads != 0:
+        raise OpsError(L.ERR_HEADS, f"attention: {heads} query heads are not a multiple of {kv_heads} key/value heads")
     slots = heads + 2 * kv_heads
     if qkv.dim() != 3 or slots <= 0 or qkv.shape[2] % slots != 0:
         raise OpsError(L.ERR_SHAPE, f"attention: qkv has shape {list(qkv.shape)}, expected [B, T, slots*D]")
@@ -380,7 +389,7 @@ def pool(hidden, aux=None, mode: int = POOL_CLS, normalize: bool = True, out=Non
     if aux is not None and aux.dtype not in (torch.bool, torch.uint8, torch.int32):
         aux = aux.to(torch.int32)
     a, b, c = _desc(hidden), _desc(aux), _desc(out)
-    _check(L.load().svodb_pool(_p(a), _p(b), int(mode), int(normalize), _p(c), _stream()))
+    _check(L.load().svodb_pool(_p(a), _p(b), int(mode), int(normalize), _p(c), _stream()), 2 if normalize else 1)
     return out
 
 

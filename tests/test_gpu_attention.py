@@ -1,0 +1,258 @@
+"""GPU parity of `ops.attention` / `attention_packed` against the oracle: the
+reference's kernel cases (tk/src/test/unit/attention.rs:349-455: LCG seed 5,
+key mask hiding (b+j)%5==2, segments of 40, max-abs 2e-2) and its op-level cases
+(tk/src/test/unit/ops.rs:436-470, 507-523, 1004-1024), through the C ABI."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import svod_oracle as O
+from svod_b200 import ops
+from tests.util import dev, host, max_abs, mean_rel
+
+pytestmark = pytest.mark.gpu
+
+SEGMENT = 40
+
+
+def recipe(B, T, Tk, H, Hkv, D, dt=O.BF16, seed=5):
+    g = O.Lcg(seed)
+    q = g.rounded(dt, B * T * H * D).reshape(B, T, H, D)
+    k = g.rounded(dt, B * Tk * Hkv * D).reshape(B, Tk, Hkv, D)
+    v = g.rounded(dt, B * Tk * Hkv * D).reshape(B, Tk, Hkv, D)
+    return q, k, v
+
+
+def run_case(q, k, v, dt, packed=False, lse=False, **kw):
+    B, T, H, D = q.shape
+    a = ops.Attn(want_lse=lse, causal=bool(kw.get("causal")), window=kw.get("window"), scale=kw.get("scale"),
+                 splits=kw.get("splits"))
+    okw = {key: kw[key] for key in ("causal", "window", "scale") if kw.get(key) is not None}
+    if "lens" in kw:
+        okw["key_lens"] = np.array(kw["lens"])
+        a.keys = ops.KeyMask.Lens(torch.tensor(kw["lens"], dtype=torch.int64).cuda())
+    if "mask" in kw:
+        okw["key_mask"] = kw["mask"]
+        a.keys = ops.KeyMask.Bool(torch.from_numpy(np.asarray(kw["mask"])).cuda())
+    if "seg" in kw:
+        okw["seg_start"] = kw["seg"]
+        a.seg_start = torch.from_numpy(np.asarray(kw["seg"], dtype=np.int64)).cuda()
+    if "chunk" in kw:
+        okw["chunk"] = kw["chunk"]
+        a.chunk = ops.Chunk(*kw["chunk"])
+    if "bias" in kw:
+        okw["bias"] = kw["bias"]
+        a.bias = dev(kw["bias"], dt)
+    want = O.attention(q, k, v, dtype=dt, return_lse=lse, **okw)
+    if packed:
+        qkv = np.concatenate([q.reshape(B, T, -1), k.reshape(B, T, -1), v.reshape(B, T, -1)], axis=-1)
+        got = ops.attention_packed(dev(qkv, dt), H, k.shape[2], a)
+    else:
+        got = ops.attention(dev(q, dt), dev(k, dt), dev(v, dt), a)
+    if lse:
+        return host(got[0]), host(got[1]), want[0], want[1]
+    return host(got), want
+
+
+def key_mask(B, Tk):
+    return np.array([[(b + j) % 5 != 2 for j in range(Tk)] for b in range(B)])
+
+
+def segments(B, T, seg=SEGMENT):
+    return np.array([[i - i % seg for i in range(T)] for _ in range(B)])
+
+
+KERNEL_CASES = [
+    # name, T, Tk, D, kwargs            (B = 2, H = Hkv = 2 as in the reference's `spec`)
+    ("one block", 64, 64, 64, {}),
+    ("three key blocks", 128, 192, 64, {}),
+    ("causal", 128, 128, 64, dict(causal=True)),
+    ("key lengths", 128, 128, 64, dict(lens=[100, 7])),
+    ("causal with lengths", 128, 128, 64, dict(causal=True, lens=[128, 50])),
+    ("window with lengths", 128, 128, 64, dict(window=(16, 8), lens=[128, 90])),
+    ("key mask", 128, 128, 64, dict(mask="km")),
+    ("causal segments", 128, 128, 64, dict(causal=True, seg="seg")),
+    ("chunks with lengths", 128, 128, 64, dict(chunk=(32, 1, 0), lens=[128, 90])),
+    ("chunks, every earlier one and one ahead, ragged", 100, 100, 64, dict(chunk=(32, None, 1))),
+    ("every mask", 128, 128, 64, dict(causal=True, window=(64, 64), lens=[128, 100], mask="km", seg="seg")),
+    ("a lane with no keys", 128, 128, 64, dict(lens=[100, 0])),
+    ("causal, a lane with no keys", 128, 128, 64, dict(causal=True, lens=[0, 50])),
+    ("a larger scale", 128, 128, 64, dict(causal=True, lens=[128, 50], scale=0.3)),
+    ("plain", 128, 128, 64, {}),
+    ("causal, 256 queries", 256, 256, 64, dict(causal=True)),
+    ("key lengths, 256 keys", 128, 256, 64, dict(lens=[200, 33])),
+    ("d 128, causal with lengths", 128, 128, 128, dict(causal=True, lens=[128, 64])),
+    ("bq 128, three stages", 256, 192, 64, dict(causal=True, lens=[192, 70])),
+    ("d 128, ragged", 200, 130, 128, dict(lens=[130, 99])),
+    ("d 128, bq 256, ragged", 600, 420, 128, dict(lens=[420, 299])),
+    ("key mask, ragged", 100, 100, 64, dict(mask="km")),
+    ("every mask, d 128", 128, 128, 128, dict(causal=True, window=(64, 64), lens=[128, 100], mask="km", seg="seg")),
+    ("wide core, d 128", 200, 300, 128, {}),
+    ("wide core, d 64, bq 256", 300, 300, 64, {}),
+    ("odd keys", 99, 99, 64, dict(lens=[99, 41])),
+]
+
+
+@pytest.mark.parametrize("name,T,Tk,D,kw", KERNEL_CASES, ids=[c[0] for c in KERNEL_CASES])
+def test_flash_attention_matches_a_direct_softmax(name, T, Tk, D, kw):
+    B, H = 2, 2
+    kw = dict(kw)
+    if kw.get("mask") == "km":
+        kw["mask"] = key_mask(B, Tk)
+    if kw.get("seg") == "seg":
+        kw["seg"] = segments(B, T)
+    if "lens" in kw and "mask" in kw:
+        # KeyMask is one or the other: fold the lengths into the bool mask
+        kw["mask"] = kw["mask"] & (np.arange(Tk)[None, :] < np.array(kw.pop("lens"))[:, None])
+    q, k, v = recipe(B, T, Tk, H, H, D)
+    got, want = run_case(q, k, v, O.BF16, **kw)
+    assert "kernel flash_attention" in ops.chosen()
+    assert not np.isnan(got).any()
+    assert max_abs(got, want) < 2e-2
+
+
+def test_a_fully_masked_batch_is_zeros():
+    B, T, D = 2, 128, 64
+    q, k, v = recipe(B, T, T, 2, 2, D)
+    m = key_mask(B, T)
+    m[1] = False
+    got, want = run_case(q, k, v, O.BF16, mask=m)
+    assert np.any(got[0] != 0) and np.all(got[1] == 0)
+    assert max_abs(got, want) < 2e-2
+
+
+OP_CASES = [
+    ("lens", 2, 100, 100, 4, 4, 64, O.BF16, dict(lens=[100, 61])),
+    ("causal T200", 2, 200, 200, 4, 4, 64, O.BF16, dict(causal=True)),
+    ("gqa 8/2", 2, 100, 100, 8, 2, 64, O.BF16, {}),
+    ("d128 gqa causal", 2, 100, 100, 8, 2, 128, O.BF16, dict(causal=True)),
+    ("cross 37x150", 2, 37, 150, 4, 4, 64, O.BF16, {}),
+    ("window (64,64) T300", 2, 300, 300, 4, 4, 64, O.BF16, dict(window=(64, 64))),
+    ("bool mask", 2, 100, 100, 4, 4, 64, O.BF16, dict(mask="km")),
+    ("segments of 30", 2, 100, 100, 4, 4, 64, O.BF16, dict(causal=True, seg=30)),
+    ("f16", 2, 100, 100, 4, 4, 64, O.F16, dict(lens=[100, 61])),
+    ("f16 d128 causal 700", 1, 700, 700, 4, 2, 128, O.F16, dict(causal=True)),
+]
+
+
+@pytest.mark.parametrize("name,B,T,Tk,H,Hkv,D,dt,kw", OP_CASES, ids=[c[0] for c in OP_CASES])
+def test_attention_op_matches_the_oracle(name, B, T, Tk, H, Hkv, D, dt, kw):
+    kw = dict(kw)
+    if kw.get("mask") == "km":
+        kw["mask"] = key_mask(B, Tk)
+    if "seg" in kw:
+        kw["seg"] = segments(B, T, kw["seg"])
+    rng = np.random.default_rng(11)
+    q = O.round_to(dt, rng.uniform(-1, 1, (B, T, H, D)))
+    k = O.round_to(dt, rng.uniform(-1, 1, (B, Tk, Hkv, D)))
+    v = O.round_to(dt, rng.uniform(-1, 1, (B, Tk, Hkv, D)))
+    got, want = run_case(q, k, v, dt, **kw)
+    assert "kernel flash_attention" in ops.chosen()
+    assert max_abs(got, want) < 2e-2
+
+
+@pytest.mark.parametrize("kw", [dict(window=(64, 64)), dict(mask="km"), dict(causal=True)])
+def test_packed_attention_is_bit_identical_to_the_split_operands(kw):
+    """`packed_attention_matches_the_split_kernel` (ops.rs:507-523)."""
+    kw = dict(kw)
+    B, T, H, D = 2, 300, 4, 64
+    if kw.get("mask") == "km":
+        kw["mask"] = key_mask(B, T)
+    q, k, v = recipe(B, T, T, H, H, D)
+    a, want = run_case(q, k, v, O.BF16, **kw)
+    b, _ = run_case(q, k, v, O.BF16, packed=True, **kw)
+    assert "flash_attention_packed" in ops.chosen()
+    assert np.array_equal(a, b)
+    assert max_abs(a, want) < 2e-2
+
+
+def test_config_1_f32_attention_with_key_lengths_output_and_logsumexp():
+    """f32, batch 2, 8 heads, seq 512, head_dim 64, N(0,1) from seed, key-padding
+    lengths uniform in [256, 512], scale 1/sqrt(64): output and log-sum-exp
+    within 1e-4 of the CPU oracle."""
+    rng = np.random.default_rng(1000)
+    B, T, H, D = 2, 512, 8, 64
+    q = O.round_to(O.F32, rng.standard_normal((B, T, H, D)))
+    k = O.round_to(O.F32, rng.standard_normal((B, T, H, D)))
+    v = O.round_to(O.F32, rng.standard_normal((B, T, H, D)))
+    lens = rng.integers(256, 513, B).tolist()
+    got, glse, want, wlse = run_case(q, k, v, O.F32, lse=True, lens=lens, scale=1.0 / math.sqrt(64))
+    assert ops.chosen() == "attention: graph dtype"
+    assert max_abs(got, want) < 1e-4
+    assert max_abs(glse, wlse) < 1e-4
+    # the same inputs rounded to bf16 run the tcgen05 kernel: 2e-2 / 5e-3
+    qb, kb, vb = (O.round_to(O.BF16, t) for t in (q, k, v))
+    got, glse, want, wlse = run_case(qb, kb, vb, O.BF16, lse=True, lens=lens)
+    assert "kernel flash_attention" in ops.chosen()
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+    assert max_abs(glse, wlse) < 2e-2
+
+
+GENERIC_CASES = [
+    ("d 48", 2, 96, 96, 2, 2, 48, O.BF16, dict(causal=True, seg=40)),
+    ("bias per batch", 2, 128, 128, 2, 2, 64, O.BF16, dict(bias=(2, 2, 128, 128))),
+    ("shared bias, ragged", 2, 100, 130, 2, 2, 64, O.BF16, dict(bias=(1, 2, 100, 130))),
+    ("bias with key lengths", 2, 99, 99, 2, 2, 64, O.BF16, dict(bias=(2, 2, 99, 99), lens=[99, 41])),
+    ("four splits", 1, 1, 200, 4, 4, 64, O.BF16, dict(lens=[70], splits=4)),
+    ("two splits, five queries, d128", 2, 5, 96, 2, 2, 128, O.BF16, dict(lens=[64, 96], splits=2)),
+    ("more splits than blocks", 2, 1, 64, 2, 2, 64, O.BF16, dict(lens=[64, 40], splits=4)),
+    ("splits, a lane with no keys", 2, 1, 200, 4, 4, 64, O.BF16, dict(lens=[0, 70], splits=4)),
+    ("negative scale", 2, 128, 128, 2, 2, 64, O.BF16, dict(causal=True, lens=[128, 50], scale=-0.1)),
+    ("f32 causal ragged gqa", 2, 100, 130, 4, 2, 48, O.F32, dict(causal=True)),
+]
+
+
+@pytest.mark.parametrize("name,B,T,Tk,H,Hkv,D,dt,kw", GENERIC_CASES, ids=[c[0] for c in GENERIC_CASES])
+def test_cases_outside_the_tile_kernel_run_the_exact_kernel(name, B, T, Tk, H, Hkv, D, dt, kw):
+    kw = dict(kw)
+    if "seg" in kw:
+        kw["seg"] = segments(B, T, kw["seg"])
+    q, k, v = recipe(B, T, Tk, H, Hkv, D, dt)
+    if "bias" in kw:
+        kw["bias"] = O.Lcg(99).rounded(dt, int(np.prod(kw["bias"])), lambda x: 2.0 * x).reshape(kw["bias"])
+    got, want = run_case(q, k, v, dt, **kw)
+    assert ops.chosen().startswith("attention: graph")
+    assert max_abs(got, want) < (1e-4 if dt == O.F32 else 2e-2)
+
+
+def test_combine_splits_merges_partial_states():
+    rng = np.random.default_rng(4)
+    S, B, T, H, D = 3, 2, 5, 2, 64
+    o = rng.standard_normal((S, B, T, H, D)).astype(np.float32)
+    m = (rng.standard_normal((S, B, T, H)) * 3).astype(np.float32)
+    l = rng.uniform(0.5, 4, (S, B, T, H)).astype(np.float32)
+    l[:, 1, 2] = 0.0
+    o[:, 1, 2] = 0.0
+    m[:, 1, 2] = -1e30
+    want = O.combine_splits(o, m, l, O.BF16)
+    got = ops.combine_splits(torch.from_numpy(o).cuda(), torch.from_numpy(m).cuda(), torch.from_numpy(l).cuda(),
+                             torch.bfloat16)
+    assert max_abs(host(got), want) < 2e-2
+    assert np.all(host(got)[1, 2] == 0)
+
+
+def test_full_size_attention_properties_at_seq_4096_d128():
+    """Size-independent checks at the headline shape (heads 16/8, seq 4096, d 128,
+    causal), batch 2: (1) v = ones gives ones on every row that sees a key;
+    (2) the first 256 queries equal attention over the first 256 keys alone;
+    (3) a replay is bit-identical; (4) sampled rows match an f32 softmax."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    B, T, H, Hkv, D = 2, 4096, 16, 8, 128
+    q = torch.randn(B, T, H, D, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+    a = ops.Attn(causal=True)
+    o = ops.attention(q, k, v, a)
+    assert "kernel flash_attention" in ops.chosen()
+    ones = ops.attention(q, k, torch.ones_like(v), a)
+    assert float((ones.float() - 1).abs().max()) < 1e-2
+    head = ops.attention(q[:, :256].contiguous(), k[:, :256].contiguous(), v[:, :256].contiguous(), a)
+    assert torch.equal(head, o[:, :256])
+    assert torch.equal(ops.attention(q, k, v, a), o)
+    for (b, h, i) in [(0, 0, 0), (1, 5, 1000), (0, 15, 4095), (1, 9, 2177)]:
+        kk, vv = k[b, :i + 1, h // 2].float(), v[b, :i + 1, h // 2].float()
+        s = (kk @ q[b, i, h].float()) / math.sqrt(D)
+        ref = torch.softmax(s, 0) @ vv
+        assert float((o[b, i, h].float() - ref).abs().max()) < 2e-2

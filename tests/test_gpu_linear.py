@@ -1,0 +1,146 @@
+"""GPU parity of `ops.linear` (tcgen05 GEMM + fused epilogue, and the generic
+path) against the oracle: the reference's epilogue recipe
+(tk/src/test/unit/rows.rs:77-145, seed 17, 64^3 and 256^3, rel 1.6e-2), its
+op-vs-graph cases (ops.rs:163-205, rel 2e-2) and the benchmark sweep shapes."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import svod_oracle as O
+from svod_b200 import ops
+from tests.test_oracle_pins import EPILOGUES, gemm_recipe
+from tests.util import dev, host, max_abs, mean_rel, rel_close
+
+pytestmark = pytest.mark.gpu
+
+
+def run_linear(x, w, dt, bias=None, act=0, gated=False, residual=None, scale=None, rope=None):
+    o = ops.Linear(bias=dev(bias, dt) if bias is not None else None, act=ops.Act(act), gated=gated,
+                   residual=dev(residual, dt) if residual is not None else None, scale=scale)
+    if rope is not None:
+        cos, sin, nh, hd = rope
+        T = x.shape[1]
+        o.rope = ops.Rotary(dev(cos, dt).view(1, T, 1, hd // 2), dev(sin, dt).view(1, T, 1, hd // 2), nh, hd)
+    return host(ops.linear(dev(x, dt), dev(w, dt), o))
+
+
+@pytest.mark.parametrize("size", [64, 256])
+@pytest.mark.parametrize("which", range(8))
+def test_epilogues_match_the_reference_recipe(size, which):
+    epi = EPILOGUES[which]
+    a, w, bias, res = gemm_recipe(size, size, size, epi)
+    want = O.linear(a, w, bias, epi.get("act", 0), epi.get("gated", False), res, epi.get("scale"), dtype=O.BF16)
+    got = run_linear(a, w, O.BF16, bias, epi.get("act", 0), epi.get("gated", False), res, epi.get("scale"))
+    assert "kernel gemm" in ops.chosen()
+    assert rel_close(got, want, 1.6e-2)
+
+
+OP_CASES = [
+    # (lead, n, k, dtype, bias, act, gated, residual)  -- tk/src/test/unit/ops.rs:163-171
+    ((37,), 96, 64, O.BF16, True, O.ACT_GELU, False, True),
+    ((3, 50), 96, 64, O.BF16, True, 0, False, False),
+    ((300,), 200, 48, O.BF16, False, O.ACT_SILU, False, False),
+    ((2048,), 512, 512, O.BF16, True, 0, False, True),
+    ((77,), 96, 128, O.BF16, True, O.ACT_SILU, True, False),
+    ((77,), 96, 128, O.BF16, False, O.ACT_GELU, True, True),
+    ((129,), 264, 80, O.F16, True, O.ACT_GELU, False, True),
+    ((1, 1), 8, 16, O.BF16, True, 0, False, False),
+    ((1000,), 1152, 768, O.BF16, False, O.ACT_GELU, True, True),
+]
+
+
+@pytest.mark.parametrize("lead,n,k,dt,bias,act,gated,residual", OP_CASES)
+def test_linear_matches_the_oracle(lead, n, k, dt, bias, act, gated, residual):
+    rng = np.random.default_rng(n * 7 + k)
+    halves = 2 if gated else 1
+    x = O.round_to(dt, rng.uniform(-1, 1, lead + (k,)))
+    w = O.round_to(dt, rng.uniform(-1, 1, (halves * n, k)) * 0.3)
+    b = O.round_to(dt, rng.uniform(-1, 1, halves * n)) if bias else None
+    r = O.round_to(dt, rng.uniform(-1, 1, lead + (n,))) if residual else None
+    want = O.linear(x, w, b, act, gated, r, dtype=dt)
+    got = run_linear(x, w, dt, b, act, gated, r)
+    assert "kernel gemm" in ops.chosen()
+    assert got.shape == want.shape
+    assert rel_close(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("dt,m,n,k", [(O.F32, 37, 96, 64), (O.BF16, 50, 100, 64), (O.BF16, 77, 96, 40), (O.F32, 5, 7, 3)])
+def test_shapes_and_dtypes_without_a_tile_kernel_take_the_generic_path(dt, m, n, k):
+    rng = np.random.default_rng(1)
+    x = O.round_to(dt, rng.standard_normal((m, k)))
+    w = O.round_to(dt, rng.standard_normal((2 * n, k)) * 0.2)
+    b = O.round_to(dt, rng.standard_normal(2 * n))
+    r = O.round_to(dt, rng.standard_normal((m, n)))
+    want = O.linear(x, w, b, O.ACT_SILU, True, r, 0.5, dtype=dt)
+    got = run_linear(x, w, dt, b, O.ACT_SILU, True, r, 0.5)
+    assert ops.chosen().startswith("linear: graph")
+    assert rel_close(got, want, 1e-4 if dt == O.F32 else 2e-2)
+
+
+@pytest.mark.parametrize("B,T,k,heads,hd,extra,bias", [(2, 200, 768, 24, 64, 768, False), (2, 37, 128, 4, 64, 64, True),
+                                                        (1, 130, 128, 2, 128, 256, False), (2, 50, 64, 2, 32, 16, False)])
+def test_rope_in_the_projection_store(B, T, k, heads, hd, extra, bias):
+    """`Rotary` (tk/src/ops/linear.rs:45-56): the first heads*hd columns turned
+    by position, the rest stored as they are. hd 32 has no turning tile and
+    takes the generic rotation."""
+    dt = O.BF16
+    rng = np.random.default_rng(T)
+    n = heads * hd + extra
+    x = O.round_to(dt, rng.standard_normal((B, T, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    b = O.round_to(dt, rng.standard_normal(n)) if bias else None
+    cos, sin = O.rope_table(10000.0, np.arange(T), hd, dt)
+    want = O.linear(x, w, b, rope=(cos, sin, heads, hd), dtype=dt)
+    got = run_linear(x, w, dt, b, rope=(cos, sin, heads, hd))
+    assert ("kernel gemm" in ops.chosen()) == (hd in (64, 128))
+    assert rel_close(got, want, 2e-2)
+
+
+def test_into_stores_a_channel_window():
+    """`into` (tk/src/ops/mod.rs:431-477): the output stored into channels
+    [at, at+N) of a wider buffer, the other channels untouched."""
+    dt = O.BF16
+    rng = np.random.default_rng(9)
+    x = O.round_to(dt, rng.standard_normal((70, 64)))
+    w = O.round_to(dt, rng.standard_normal((32, 64)) * 0.2)
+    wide = torch.full((70, 96), 3.0, dtype=torch.bfloat16, device="cuda")
+    out = ops.linear(dev(x, dt), dev(w, dt), ops.Linear(into=(wide, 32)))
+    assert out.data_ptr() == wide.data_ptr()
+    got = host(wide)
+    assert rel_close(got[:, 32:64], O.linear(x, w, dtype=dt), 2e-2)
+    assert np.all(got[:, :32] == 3.0) and np.all(got[:, 64:] == 3.0)
+
+
+@pytest.mark.parametrize("m", [512, 4096])
+@pytest.mark.parametrize("nk", [768, 1024])
+@pytest.mark.parametrize("epi", ["gelu_tanh", "swiglu"])
+def test_sweep_shapes_of_the_gemm_benchmark(m, nk, epi):
+    """The benchmark sweep's smaller shapes: bf16 N(0,0.02) inputs, bias, GELU
+    (tanh) and SwiGLU epilogues; max-abs 2e-2 / mean-rel 5e-3."""
+    dt = O.BF16
+    rng = np.random.default_rng(2000 + m + nk)
+    gated = epi == "swiglu"
+    x = O.round_to(dt, rng.standard_normal((m, nk)) * 0.02)
+    w = O.round_to(dt, rng.standard_normal(((2 if gated else 1) * nk, nk)) * 0.02)
+    b = O.round_to(dt, rng.standard_normal((2 if gated else 1) * nk) * 0.02)
+    act = O.ACT_SILU if gated else O.ACT_GELU_TANH
+    want = O.linear(x, w, b, act, gated, dtype=dt)
+    got = run_linear(x, w, dt, b, act, gated)
+    assert max_abs(got, want) <= 2e-2 and mean_rel(got, want) <= 5e-3
+
+
+def test_full_size_gemm_is_linear_in_its_input():
+    """Size-independent property at the sweep's largest shape (M 32768, N = K =
+    4096): with a power-of-two factor, linear(2x) == 2*linear(x) exactly and
+    a second run is bit-identical."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.randn(32768, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    w = (torch.randn(4096, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    y1 = ops.linear(x, w)
+    y2 = ops.linear(x * 2, w)
+    assert torch.equal(y2, y1 * 2)
+    assert torch.equal(ops.linear(x, w), y1)
+    # spot rows against an f32 product of the same inputs
+    rows = torch.tensor([0, 777, 32767], device="cuda")
+    ref = x[rows].float() @ w.float().t()
+    assert float((y1[rows].float() - ref).abs().max()) <= 2e-2
