@@ -403,6 +403,47 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def kernel_case(args):
+    """A small single-kernel case for profiler captures: a few launches of one
+    kernel at the workload's per-launch shape with a reduced batch (inputs above
+    the 126 MB L2, a few hundred MB on the device)."""
+    import torch
+    from svod_b200 import ops
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    B, T = args.case_batch, 4096
+    if args.kernel_case == "flash_attention":
+        q = torch.randn(B, T, 16, 128, generator=g, device="cuda").to(torch.bfloat16)
+        k = torch.randn(B, T, 8, 128, generator=g, device="cuda").to(torch.bfloat16)
+        v = torch.randn(B, T, 8, 128, generator=g, device="cuda").to(torch.bfloat16)
+        a = ops.Attn(causal=True)
+        fn = lambda: ops.attention(q, k, v, a)
+        flops = 4 * B * 16 * T * T * 128 / 2
+    elif args.kernel_case == "gemm":
+        M, N, K = B * T, 3072, 1024
+        x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+        w = (torch.randn(2 * N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        o = ops.Linear(act=ops.Act.SILU, gated=True)
+        fn = lambda: ops.linear(x, w, o)
+        flops = 2 * M * 2 * N * K
+    elif args.kernel_case == "rms_norm":
+        x = torch.randn(B * T * 4, 1024, generator=g, device="cuda").to(torch.bfloat16)
+        w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ops.rms_norm(x, w)
+        flops = 0
+    else:
+        qkv = torch.randn(B, T, 4096, generator=g, device="cuda").to(torch.bfloat16)
+        w = torch.ones(128, device="cuda", dtype=torch.bfloat16)
+        cos, sin = ops.rope_table(1e6, T, 128, torch.bfloat16)
+        o = ops.Qkv(16, 8, 128, w, w, 1e-6, (cos.view(1, T, 1, 64), sin.view(1, T, 1, 64)))
+        fn = lambda: ops.heads(qkv, o)
+        flops = 0
+    ms = time_kernel(fn, torch.cuda.current_stream(), 3)
+    ops.device_status()
+    print(json.dumps({"kernel_case": args.kernel_case, "batch": B, "ms": ms,
+                      "tflops": flops / ms / 1e9 if flops else None, "chosen": ops.chosen()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -411,7 +452,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b-embed", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "rms_norm", "heads"],
+                    help="run a few launches of one kernel on a small case (for profiler captures) and exit")
+    ap.add_argument("--case-batch", type=int, default=4)
     args = ap.parse_args()
+    if args.kernel_case:
+        return kernel_case(args)
     if args.impl == "reference":
         reference_arm(args)
     else:
