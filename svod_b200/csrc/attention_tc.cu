@@ -118,6 +118,12 @@ __device__ __forceinline__ Range tile_range(const FaParams& p, const Ctx& c, int
   return r;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -161,7 +167,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 4);  // one arrival per softmax warp
     }
     for (int i = 0; i < S; ++i) {
       mbar_init(&k_full[i], 1);
@@ -242,6 +248,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     u_lo = r1.lo, u_hi = r1.hi;
   }
 
+  // Register budget: the loader / MMA / mask warpgroup gives registers back so
+  // the two softmax warpgroups can hold a whole 128-column score row each.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     // ---------------- TMA loader ----------------
     if (lane == 0 && u_hi > u_lo) {
@@ -294,7 +304,9 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     if (lane == 0 && u_hi > u_lo) {
       constexpr uint32_t idesc_qk = umma_idesc(Elem<T>::kUmmaFormat, 128, kBKV, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(Elem<T>::kUmmaFormat, 128, D, 0, 1);
-      const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      const uint64_t q_desc0 = umma_desc_sw128(smem_u32(q_s), 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_s), 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_s), 128 * 128, 1024);
       bool ok = true;
       bool q_ready[2] = {false, false};
       bool pending[2] = {false, false};   // a P.V of the previous block is owed
@@ -332,13 +344,14 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + 256 + i * D;
             const uint32_t a_tmem = tmem_base + i * 128;
+            // V block: [keys][D] with 64-wide column boxes 16 KiB apart (LBO),
+            // 8-key groups 1 KiB apart (SBO); 16 keys per step = 2 KiB. Descriptors
+            // are formed per step from one base.
+            const uint64_t v_base = v_desc0 + (uint64_t)((s_prev * TB) >> 4);
+            const uint32_t first = o_started[i] ? 1u : 0u;
 #pragma unroll
-            for (int ks = 0; ks < kBKV / 16; ++ks) {
-              // V block: [keys][D] with 64-wide column boxes 16 KiB apart (LBO),
-              // 8-key groups 1 KiB apart (SBO); 16 keys per step = 2 KiB.
-              const uint64_t b_desc = umma_desc_sw128(v_addr + s_prev * TB + ks * 2048, 128 * 128, 1024);
-              umma_ts(d_tmem, a_tmem + ks * 8, b_desc, idesc_pv, (o_started[i] || ks != 0) ? 1u : 0u);
-            }
+            for (int ks = 0; ks < kBKV / 16; ++ks)
+              umma_ts(d_tmem, a_tmem + ks * 8, v_base + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (first | (uint32_t)ks) != 0 ? 1u : 0u);
             o_started[i] = true;
             pending[i] = false;
           }
@@ -352,12 +365,13 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
             }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + i * 128;
+            const uint64_t qa = q_desc0 + (uint64_t)((i * TB) >> 4);
+            const uint64_t kb = k_desc0 + (uint64_t)((s * TB) >> 4);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-              const uint32_t off = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-              const uint64_t a_desc = umma_desc_sw128(q_addr + i * TB + off, 16, 1024);
-              const uint64_t b_desc = umma_desc_sw128(k_addr + s * TB + off, 16, 1024);
-              umma_ss(d_tmem, a_desc, b_desc, idesc_qk, ks != 0 ? 1u : 0u);
+              // 16 columns = 32 bytes inside a 64-column box; boxes are 16 KiB apart
+              const uint64_t off = (uint64_t)((ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2);
+              umma_ss(d_tmem, qa + off, kb + off, idesc_qk, ks != 0 ? 1u : 0u);
             }
             tc_commit(&s_full[i]);
             pending[i] = true;
@@ -378,7 +392,9 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         }
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ---------------- softmax + epilogue ----------------
     const int i = (warp - 4) >> 2;                 // query tile
     const int quarter = warp & 3;                  // TMEM lane quarter
@@ -439,28 +455,40 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
       if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
 
-      // pass 1: row maximum of the visible raw scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kBKV; c += 32) {
-        uint32_t sr[32];
-        tmem_ld32(s_tmem + c, sr);
-        tmem_ld_wait();
-        if (need_mask) {
-          const uint32_t vw = vis_word((int)j0 + c);
+      // The whole 128-column score row of this thread is read once, with the
+      // four loads in flight together.
+      uint32_t sr[4][32];
+      tmem_ld32(s_tmem, sr[0]);
+      tmem_ld32(s_tmem + 32, sr[1]);
+      tmem_ld32(s_tmem + 64, sr[2]);
+      tmem_ld32(s_tmem + 96, sr[3]);
+      tmem_ld_wait();
+      if (need_mask) {
+        // Hidden scores become -inf: they drop out of the maximum and their
+        // probability is 2^(-inf) = 0 (the scale is positive on this path).
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, (vw >> e) & 1u ? __uint_as_float(sr[e]) : -INFINITY);
-        } else {
-          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t vw = vis_word((int)j0 + 32 * c);
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            m0 = fmaxf(m0, __uint_as_float(sr[e]));
-            m1 = fmaxf(m1, __uint_as_float(sr[e + 1]));
-            m2 = fmaxf(m2, __uint_as_float(sr[e + 2]));
-            m3 = fmaxf(m3, __uint_as_float(sr[e + 3]));
-          }
-          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+          for (int e = 0; e < 32; ++e)
+            if (((vw >> e) & 1u) == 0) sr[c][e] = 0xff800000u;
         }
+      }
+      // row maximum of the raw scores, two new values per instruction
+      float mx;
+      {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            m0 = max3(m0, __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+            m1 = max3(m1, __uint_as_float(sr[c][e + 2]), __uint_as_float(sr[c][e + 3]));
+            m2 = max3(m2, __uint_as_float(sr[c][e + 4]), __uint_as_float(sr[c][e + 5]));
+            m3 = max3(m3, __uint_as_float(sr[c][e + 6]), __uint_as_float(sr[c][e + 7]));
+          }
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
       const float mx_t = mx * sl2;  // scale > 0 on this path
       // Lazy rescale: adopt the new maximum only when it grew by more than 2^8.
@@ -488,41 +516,37 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       }
       m_run = m_new;
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
-      // pass 2: p = 2^(s*scale - m), row sum in f32, P rounded to the stream type
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kBKV; c += 32) {
-        uint32_t sr[32];
-        tmem_ld32(s_tmem + c, sr);
-        tmem_ld_wait();
-        float pv[32];
-        if (need_mask) {
-          const uint32_t vw = vis_word((int)j0 + c);
+      // p = 2^(s*scale - m) with the scale and the subtraction as packed f32x2
+      // FMAs; the row sum is taken from the f32 values, P is rounded to the
+      // stream type and written over S.
+      const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float x = ex2_approx(fmaf(__uint_as_float(sr[e]), sl2, -m_use));
-            pv[e] = (vw >> e) & 1u ? x : 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) pv[e] = ex2_approx(fmaf(__uint_as_float(sr[e]), sl2, -m_use));
-        }
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
-          l0 += pv[e];
-          l1 += pv[e + 1];
-          l2 += pv[e + 2];
-          l3 += pv[e + 3];
-          pk[e / 2] = Elem<T>::pack(pv[e], pv[e + 1]);
-          pk[e / 2 + 1] = Elem<T>::pack(pv[e + 2], pv[e + 3]);
+          float2 x0 = __ffma2_rn(make_float2(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1])), sl2_2, nm_2);
+          float2 x1 = __ffma2_rn(make_float2(__uint_as_float(sr[c][e + 2]), __uint_as_float(sr[c][e + 3])), sl2_2, nm_2);
+          x0.x = ex2_approx(x0.x);
+          x0.y = ex2_approx(x0.y);
+          x1.x = ex2_approx(x1.x);
+          x1.y = ex2_approx(x1.y);
+          la = __fadd2_rn(la, x0);
+          lb = __fadd2_rn(lb, x1);
+          pk[e / 2] = Elem<T>::pack(x0.x, x0.y);
+          pk[e / 2 + 1] = Elem<T>::pack(x1.x, x1.y);
         }
-        tmem_st16(s_tmem + c / 2, pk);
+        tmem_st16(s_tmem + 16 * c, pk);
       }
+      const float l0 = la.x + la.y, l1 = lb.x + lb.y, l2 = 0.f, l3 = 0.f;
       l_run += (l0 + l1) + (l2 + l3);
+      // Every lane's P stores have completed (wait::st is warp-wide); one lane
+      // per warp then publishes the tile to the MMA issuer.
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_full[i]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i]);
     }
     // ---- epilogue: O / l ----
     T* orow = (T*)p.o + b * p.o_sb + row * p.o_st + (int64_t)h * p.o_sh;
