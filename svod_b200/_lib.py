@@ -8,7 +8,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libsvodb.so"
+import os
+
+# SVODB_LIB_PATH selects another build of the library (e.g. one with debug probes).
+LIB_PATH = Path(os.environ.get("SVODB_LIB_PATH") or Path(__file__).resolve().parent / "lib" / "libsvodb.so")
 
 MAX_RANK = 5
 

@@ -45,7 +45,7 @@ namespace svodb {
 namespace {
 
 constexpr int kBQ = 128;   // rows per query tile (two tiles per CTA)
-constexpr int kBKV = 128;  // keys per block
+constexpr int kBKV = 64;   // keys per block
 constexpr int kThreadsFa = 384;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLn2F = 0.6931471805599453f;
@@ -54,10 +54,11 @@ constexpr int kMaxMaskWords = 2048;  // general key mask: up to 65536 keys
 
 template <int D>
 struct FaCfg {
-  static constexpr int kTileBytes = 128 * D * 2;  // one Q tile / one K block / one V block
-  static constexpr int kStages = D == 128 ? 2 : 4;
+  static constexpr int kQTileBytes = 128 * D * 2;   // one 128-row Q tile
+  static constexpr int kKvBytes = kBKV * D * 2;     // one K or V block
+  static constexpr int kStages = 4;
   static constexpr size_t kSmemBytes =
-      1024 + (size_t)(2 + 2 * kStages) * kTileBytes + (size_t)kMaxMaskWords * 4 + 512;
+      1024 + (size_t)2 * kQTileBytes + (size_t)2 * kStages * kKvBytes + (size_t)kMaxMaskWords * 4 + 512;
 };
 
 struct FaParams {
@@ -130,32 +131,52 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+#ifdef SVODB_TRACE
+// Timeline probe (debug builds only): clock() stamps of CTA (0,0,0).
+__device__ unsigned int g_trace[3 * 64 * 8];
+#define TRACE(role, iter, ev)                                                    \
+  do {                                                                           \
+    if (trace_on && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = (unsigned int)clock(); \
+  } while (0)
+#else
+#define TRACE(role, iter, ev) \
+  do {                        \
+  } while (0)
+#endif
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsFa, 1)
     attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
   using C = FaCfg<D>;
   constexpr int S = C::kStages;
-  constexpr int TB = C::kTileBytes;
+  constexpr int QB = C::kQTileBytes;   // one 128-row Q tile
+  constexpr int KB = C::kKvBytes;      // one 64-key K or V block
+  constexpr int KBOX = kBKV * 128;     // bytes of one 64-column box of a K/V block
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;                         // [2][TB]
-  uint8_t* k_s = q_s + 2 * TB;                 // [S][TB]
-  uint8_t* v_s = k_s + S * TB;                 // [S][TB]
-  uint32_t* mask_bits = reinterpret_cast<uint32_t*>(v_s + S * TB);  // [kMaxMaskWords]
+  uint8_t* q_s = smem;                         // [2][QB]
+  uint8_t* k_s = q_s + 2 * QB;                 // [S][KB]
+  uint8_t* v_s = k_s + S * KB;                 // [S][KB]
+  uint32_t* mask_bits = reinterpret_cast<uint32_t*>(v_s + S * KB);  // [kMaxMaskWords]
   uint64_t* bars = reinterpret_cast<uint64_t*>(mask_bits + kMaxMaskWords);
   uint64_t* q_full = bars;                     // [2]
   uint64_t* k_full = bars + 2;                 // [S]
   uint64_t* k_empty = k_full + S;
   uint64_t* v_full = k_empty + S;
   uint64_t* v_empty = v_full + S;
-  uint64_t* s_full = v_empty + S;              // [2]
-  uint64_t* p_full = s_full + 2;               // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2);
+  uint64_t* s_full = v_empty + S;              // [2 tiles][2 buffers]
+  uint64_t* p_full = s_full + 4;               // [2 tiles][2 buffers]
+  uint64_t* tail_done = p_full + 4;            // [2 tiles]: the last two P.V of a tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail_done + 2);
   int* scan = reinterpret_cast<int*>(tmem_slot + 1);  // [0] first zero, [1] last nonzero + 1
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef SVODB_TRACE
+  const bool trace_on = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
+                        (warp == 1 || warp == 3 || warp == 4 || warp == 8);
+#endif
   // Heavier (later, under a causal mask) query tiles are scheduled first.
   const int qt = p.n_qt - 1 - (int)blockIdx.x;
   const int h = blockIdx.y;
@@ -166,14 +187,17 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
+      mbar_init(&tail_done[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp
     }
     for (int i = 0; i < S; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);  // released by both tiles' issuers
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
     }
     scan[0] = 0x7fffffff;
     scan[1] = 0;
@@ -227,13 +251,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   }
   if (p.key_mask != nullptr) {
     const int first_zero = scan[0], last_set = scan[1];
-    if (first_zero >= last_set) {
-      // Set bits form a prefix [0, last_set).
-      if (last_set < ctx.len) ctx.len = last_set;
-    } else {
-      ctx.general_mask = 1;
-      if (last_set < ctx.len) ctx.len = last_set;
-    }
+    if (first_zero < last_set) ctx.general_mask = 1;  // not a prefix: consult the bitmask
+    if (last_set < ctx.len) ctx.len = last_set;
   }
   const Range r0 = tile_range(p, ctx, b, i0);
   const Range r1 = tile_range(p, ctx, b, i0 + kBQ);
@@ -248,151 +267,144 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     u_lo = r1.lo, u_hi = r1.hi;
   }
 
-  // Register budget: the loader / MMA / mask warpgroup gives registers back so
-  // the two softmax warpgroups can hold a whole 128-column score row each.
+  // Register budget: the loader / MMA / mask warpgroup gives registers back to
+  // the two softmax warpgroups.
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-  if (warp == 0) {
-    // ---------------- TMA loader ----------------
-    if (lane == 0 && u_hi > u_lo) {
-      for (int i = 0; i < 2; ++i) {
-        if (i == 0 ? live0 : live1) {
-          mbar_expect_tx(&q_full[i], TB);
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(q_s + i * TB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, h, (int)(i0 + i * kBQ), (int)b);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 0) {
+      // ---------------- TMA loader ----------------
+      if (lane == 0 && u_hi > u_lo) {
+        for (int i = 0; i < 2; ++i) {
+          if (i == 0 ? live0 : live1) {
+            mbar_expect_tx(&q_full[i], QB);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, h, (int)(i0 + i * kBQ),
+                          (int)b);
+          }
         }
-      }
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      int issued = 0;
-      for (int j = u_lo; j < u_hi; ++j) {
-        if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) {
-          ok = false;
-          break;
-        }
-        mbar_expect_tx(&k_full[s], TB);
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(k_s + s * TB + c * (128 * 128), &tmap_k, &k_full[s], c * 64, hk, j * kBKV, (int)b);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) {
-          ok = false;
-          // the K copy just issued is drained below
-          ++issued;
-          break;
-        }
-        mbar_expect_tx(&v_full[s], TB);
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(v_s + s * TB + c * (128 * 128), &tmap_v, &v_full[s], c * 64, hk, j * kBKV, (int)b);
-        ++issued;
-        if (++s == S) {
-          s = 0;
-          ph ^= 1;
-        }
-      }
-      if (!ok) {
-        // Error path: give copies in flight a bounded time to land.
-        for (uint32_t it = 0; it < (1u << 18); ++it) {
-          bool all = true;
-          for (int i = 0; i < S; ++i) all = all && mbar_try_wait(&k_full[i], ph) && mbar_try_wait(&v_full[i], ph);
-          if (all) break;
-        }
-        (void)issued;
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0 && u_hi > u_lo) {
-      constexpr uint32_t idesc_qk = umma_idesc(Elem<T>::kUmmaFormat, 128, kBKV, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc(Elem<T>::kUmmaFormat, 128, D, 0, 1);
-      const uint64_t q_desc0 = umma_desc_sw128(smem_u32(q_s), 16, 1024);
-      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_s), 16, 1024);
-      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_s), 128 * 128, 1024);
-      bool ok = true;
-      bool q_ready[2] = {false, false};
-      bool pending[2] = {false, false};   // a P.V of the previous block is owed
-      bool o_started[2] = {false, false};
-      uint32_t p_phase[2] = {0, 0};
-      int s = 0;            // ring slot of block j
-      uint32_t ph = 0;
-      int s_prev = 0;       // ring slot of block j-1
-      for (int j = u_lo; j <= u_hi && ok; ++j) {
-        const bool have_block = j < u_hi;
-        if (have_block) {
-          if (!mbar_wait(&k_full[s], ph, p.status)) {
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int j = u_lo; j < u_hi; ++j) {
+          if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) {
             ok = false;
             break;
           }
-        }
-        bool v_waited = false;
-        for (int i = 0; i < 2 && ok; ++i) {
-          const Range& r = i == 0 ? r0 : r1;
-          if (pending[i]) {
-            // O_i += P_i(j-1) . V(j-1)
-            if (!v_waited) {
-              // V of block j-1 sits in slot s_prev; its phase is that block's lap of the ring.
-              if (!mbar_wait(&v_full[s_prev], (uint32_t)(((j - 1 - u_lo) / S) & 1), p.status)) {
-                ok = false;
-                break;
-              }
-              v_waited = true;
-            }
-            if (!mbar_wait(&p_full[i], p_phase[i], p.status)) {
-              ok = false;
-              break;
-            }
-            p_phase[i] ^= 1;
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + 256 + i * D;
-            const uint32_t a_tmem = tmem_base + i * 128;
-            // V block: [keys][D] with 64-wide column boxes 16 KiB apart (LBO),
-            // 8-key groups 1 KiB apart (SBO); 16 keys per step = 2 KiB. Descriptors
-            // are formed per step from one base.
-            const uint64_t v_base = v_desc0 + (uint64_t)((s_prev * TB) >> 4);
-            const uint32_t first = o_started[i] ? 1u : 0u;
-#pragma unroll
-            for (int ks = 0; ks < kBKV / 16; ++ks)
-              umma_ts(d_tmem, a_tmem + ks * 8, v_base + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (first | (uint32_t)ks) != 0 ? 1u : 0u);
-            o_started[i] = true;
-            pending[i] = false;
+          mbar_expect_tx(&k_full[s], KB);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(k_s + s * KB + c * KBOX, &tmap_k, &k_full[s], c * 64, hk, j * kBKV, (int)b);
+          if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) {
+            ok = false;
+            break;
           }
-          if (have_block && j >= r.lo && j < r.hi) {
-            if (!q_ready[i]) {
-              if (!mbar_wait(&q_full[i], 0, p.status)) {
-                ok = false;
-                break;
-              }
-              q_ready[i] = true;
-            }
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + i * 128;
-            const uint64_t qa = q_desc0 + (uint64_t)((i * TB) >> 4);
-            const uint64_t kb = k_desc0 + (uint64_t)((s * TB) >> 4);
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              // 16 columns = 32 bytes inside a 64-column box; boxes are 16 KiB apart
-              const uint64_t off = (uint64_t)((ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2);
-              umma_ss(d_tmem, qa + off, kb + off, idesc_qk, ks != 0 ? 1u : 0u);
-            }
-            tc_commit(&s_full[i]);
-            pending[i] = true;
-          } else if (j > r.lo && j == r.hi && r.hi > r.lo) {
-            // Tile i's last P.V was just issued: publish its finished O.
-            tc_commit(&s_full[i]);
-          }
-        }
-        if (!ok) break;
-        if (j > u_lo) tc_commit(&v_empty[s_prev]);  // both tiles' P.V of block j-1 are issued
-        if (have_block) {
-          tc_commit(&k_empty[s]);
-          s_prev = s;
+          mbar_expect_tx(&v_full[s], KB);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(v_s + s * KB + c * KBOX, &tmap_v, &v_full[s], c * 64, hk, j * kBKV, (int)b);
           if (++s == S) {
             s = 0;
             ph ^= 1;
           }
         }
+        if (!ok) {
+          // Error path: give copies in flight a bounded time to land.
+          for (uint32_t it = 0; it < (1u << 18); ++it) {
+            bool all = true;
+            for (int i = 0; i < S; ++i) all = all && mbar_try_wait(&k_full[i], ph) && mbar_try_wait(&v_full[i], ph);
+            if (all) break;
+          }
+        }
+      }
+    } else if (warp == 1 || warp == 3) {
+      // ---------------- MMA issuers: warp 1 drives tile 0, warp 3 tile 1 ----------------
+      // Each query tile has its own issuing warp, so the barrier round trips of
+      // one tile's schedule overlap the other's MMAs. The whole warp walks the
+      // schedule (addresses and descriptors stay warp-uniform values); one
+      // elected lane issues the MMAs and commits.
+      const int i = warp == 1 ? 0 : 1;
+      const Range r = i == 0 ? r0 : r1;
+      const bool leader = elect_one();
+      if (u_hi > u_lo) {
+        constexpr uint32_t idesc_qk = umma_idesc(Elem<T>::kUmmaFormat, 128, kBKV, 0, 0);
+        constexpr uint32_t idesc_pv = umma_idesc(Elem<T>::kUmmaFormat, 128, D, 0, 1);
+        const uint64_t qa = umma_desc_sw128(smem_u32(q_s) + i * QB, 16, 1024);
+        const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_s), 16, 1024);
+        // V block: [keys][D]; 64-column boxes KBOX apart (LBO), 8-key groups 1 KiB apart (SBO).
+        const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_s), KBOX, 1024);
+        const int nblk = r.hi - r.lo;
+        bool ok = true;
+        bool q_ready = false;
+        // Step t issues O += P(t-1).V(t-1) and then S(t+1) = Q.K(t+1)^T into the
+        // score buffer that P(t-1) just vacated: S runs one block ahead of the
+        // softmax. Both issuers walk the union of the two tiles' key ranges and
+        // each releases every K/V slot (the ring barriers count two arrivals).
+        for (int t = u_lo - 1; t <= u_hi && ok; ++t) {
+          const int jq = t + 1;  // block whose scores are issued this step
+          const int jp = t - 1;  // block whose P.V is issued this step
+          const bool have_k = jq >= u_lo && jq < u_hi;
+          const bool have_v = jp >= u_lo && jp < u_hi;
+          const int ks_slot = have_k ? (jq - u_lo) % S : 0;
+          const int vs_slot = have_v ? (jp - u_lo) % S : 0;
+          const bool do_pv = have_v && jp >= r.lo && jp < r.hi;
+          const bool do_qk = have_k && jq >= r.lo && jq < r.hi;
+          TRACE(0, t - u_lo + 1, 3 * i);
+          // Every slot is waited for and released by both issuers, used or not:
+          // an issuer can then never arrive twice on one phase of a ring barrier.
+          if ((have_k && !mbar_wait(&k_full[ks_slot], (uint32_t)(((jq - u_lo) / S) & 1), p.status)) ||
+              (have_v && !mbar_wait(&v_full[vs_slot], (uint32_t)(((jp - u_lo) / S) & 1), p.status))) {
+            ok = false;
+            break;
+          }
+          if (do_pv) {
+            const int n = jp - r.lo;  // this tile's block counter
+            if (!mbar_wait(&p_full[i * 2 + (n & 1)], (uint32_t)((n >> 1) & 1), p.status)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            TRACE(0, t - u_lo + 1, 1 + 3 * i);
+            const uint32_t d_tmem = tmem_base + 256 + i * D;
+            const uint32_t a_tmem = tmem_base + (uint32_t)((i * 2 + (n & 1)) * kBKV);
+            const uint64_t vb = v_desc0 + (uint64_t)((vs_slot * KB) >> 4);
+            const uint32_t first = n != 0 ? 1u : 0u;
+#pragma unroll
+            for (int ks = 0; ks < kBKV / 16; ++ks)  // 16 keys per step = 2 KiB of V, 8 packed P columns
+              if (leader)
+                umma_ts(d_tmem, a_tmem + ks * 8, vb + (uint64_t)(ks * (2048 >> 4)), idesc_pv,
+                        (first | (uint32_t)ks) != 0 ? 1u : 0u);
+            // The last two P.V of a tile have no later S to announce them: they
+            // are published on tail_done (phase 0: block N-2, phase 1: block N-1;
+            // a one-block tile uses phase 0 only).
+            if (leader && n + 2 >= nblk) tc_commit(&tail_done[i]);
+          }
+          if (do_qk) {
+            if (!q_ready) {
+              if (!mbar_wait(&q_full[i], 0, p.status)) {
+                ok = false;
+                break;
+              }
+              q_ready = true;
+            }
+            tc_fence_after();
+            const int n = jq - r.lo;
+            const uint32_t d_tmem = tmem_base + (uint32_t)((i * 2 + (n & 1)) * kBKV);
+            const uint64_t kb = k_desc0 + (uint64_t)((ks_slot * KB) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              // 16 columns = 32 bytes inside a 64-column box
+              const uint64_t qoff = (uint64_t)((ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2);
+              const uint64_t koff = (uint64_t)((ks >> 2) * (KBOX >> 4) + (ks & 3) * 2);
+              if (leader) umma_ss(d_tmem, qa + qoff, kb + koff, idesc_qk, ks != 0 ? 1u : 0u);
+            }
+            // In-order completion: S(t+1) complete implies P.V(t-1) complete.
+            if (leader) tc_commit(&s_full[i * 2 + (n & 1)]);
+            TRACE(0, t - u_lo + 1, 2 + 3 * i);
+          }
+          if (leader && have_v) tc_commit(&v_empty[vs_slot]);
+          if (leader && have_k) tc_commit(&k_empty[ks_slot]);
+          __syncwarp();
+        }
       }
     }
-  }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ---------------- softmax + epilogue ----------------
@@ -404,7 +416,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     const bool row_ok = row < p.t;
     const int64_t i_last = (i_first + kBQ - 1 < p.t - 1) ? i_first + kBQ - 1 : p.t - 1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + i * 128 + lane_addr;
     const uint32_t o_tmem = tmem_base + 256 + i * D + lane_addr;
     const float sl2 = p.scale_log2;
     int64_t seg_me = 0, seg_last = 0;
@@ -440,34 +451,35 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     };
     float m_run = -INFINITY;  // running maximum, scaled log2 units
     float l_run = 0.f;
-    uint32_t s_phase = 0;
     bool ok = true;
+    const int nblk = r.hi - r.lo;
     for (int j = r.lo; j < r.hi; ++j) {
-      if (!mbar_wait(&s_full[i], s_phase, p.status)) {
+      const int n = j - r.lo;
+      const int buf = n & 1;
+      if (!mbar_wait(&s_full[i * 2 + buf], (uint32_t)((n >> 1) & 1), p.status)) {
         ok = false;
         break;
       }
-      s_phase ^= 1;
       tc_fence_after();
+      TRACE(1 + i, n, 0);
+      const uint32_t s_tmem = tmem_base + (uint32_t)((i * 2 + buf) * kBKV) + lane_addr;
       const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
       bool need_mask = j1 >= ctx.len || ctx.general_mask || p.has_chunk;
       if (p.causal && j1 > i_first) need_mask = true;
       if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
       if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
 
-      // The whole 128-column score row of this thread is read once, with the
-      // four loads in flight together.
-      uint32_t sr[4][32];
+      // The 64-column score row of this thread, both loads in flight together.
+      uint32_t sr[2][32];
       tmem_ld32(s_tmem, sr[0]);
       tmem_ld32(s_tmem + 32, sr[1]);
-      tmem_ld32(s_tmem + 64, sr[2]);
-      tmem_ld32(s_tmem + 96, sr[3]);
       tmem_ld_wait();
+      TRACE(1 + i, n, 1);
       if (need_mask) {
         // Hidden scores become -inf: they drop out of the maximum and their
         // probability is 2^(-inf) = 0 (the scale is positive on this path).
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           const uint32_t vw = vis_word((int)j0 + 32 * c);
 #pragma unroll
           for (int e = 0; e < 32; ++e)
@@ -479,7 +491,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       {
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             m0 = max3(m0, __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
@@ -497,12 +509,25 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       // The accumulator is rescaled by warp-wide TMEM accesses, so the branch is
       // taken by the whole warp when any of its rows moved; rows that kept their
       // maximum scale by exactly 1.
+      bool tail0_seen = false;
       const bool moved = m_new != m_run && m_run != -INFINITY;
       const float corr = moved ? ex2_approx(m_run - m_new) : 1.0f;
       if (__any_sync(0xffffffffu, moved)) {
+        // S runs ahead of P.V: the previous block's P.V may still be in flight.
+        // Completion is in issue order, so it has landed once S of the next
+        // block is complete (that wait does not consume the phase: the regular
+        // wait of block n+1 passes at once afterwards); the tile's last block
+        // has no next S and reads the tail barrier's first phase instead.
+        const bool landed = n + 1 < nblk
+                                ? mbar_wait(&s_full[i * 2 + ((n + 1) & 1)], (uint32_t)(((n + 1) >> 1) & 1), p.status)
+                                : mbar_wait(&tail_done[i], 0, p.status);
+        if (!landed) {
+          ok = false;
+          break;
+        }
+        tail0_seen = n + 1 == nblk;
+        tc_fence_after();
         l_run *= corr;
-        // O_i holds the sum over earlier blocks; its last P.V completed before
-        // this block's S was published.
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t orr[32];
@@ -515,15 +540,16 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_st_wait();
       }
       m_run = m_new;
+      TRACE(1 + i, n, 2);
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
       // p = 2^(s*scale - m) with the scale and the subtraction as packed f32x2
       // FMAs; the row sum is taken from the f32 values, P is rounded to the
       // stream type and written over S.
       const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           float2 x0 = __ffma2_rn(make_float2(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1])), sl2_2, nm_2);
@@ -534,24 +560,33 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           x1.y = ex2_approx(x1.y);
           la = __fadd2_rn(la, x0);
           lb = __fadd2_rn(lb, x1);
-          pk[e / 2] = Elem<T>::pack(x0.x, x0.y);
-          pk[e / 2 + 1] = Elem<T>::pack(x1.x, x1.y);
+          pk[16 * c + e / 2] = Elem<T>::pack(x0.x, x0.y);
+          pk[16 * c + e / 2 + 1] = Elem<T>::pack(x1.x, x1.y);
         }
-        tmem_st16(s_tmem + 16 * c, pk);
       }
-      const float l0 = la.x + la.y, l1 = lb.x + lb.y, l2 = 0.f, l3 = 0.f;
-      l_run += (l0 + l1) + (l2 + l3);
+      tmem_st32(s_tmem, pk);
+      l_run += (la.x + la.y) + (lb.x + lb.y);
+      TRACE(1 + i, n, 3);
       // Every lane's P stores have completed (wait::st is warp-wide); one lane
       // per warp then publishes the tile to the MMA issuer.
       tmem_st_wait();
+      // The tail barrier sees two commits (P.V of blocks N-2 and N-1); a parity
+      // wait tells only adjacent phases apart, so the first is observed before
+      // the last P — which lets the second happen — is published.
+      if (n + 1 == nblk && nblk >= 2 && !tail0_seen && !mbar_wait(&tail_done[i], 0, p.status)) {
+        ok = false;
+        break;
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[i]);
+      if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
+      TRACE(1 + i, n, 4);
     }
     // ---- epilogue: O / l ----
     T* orow = (T*)p.o + b * p.o_sb + row * p.o_st + (int64_t)h * p.o_sh;
     if (r.hi > r.lo && ok) {
-      if (mbar_wait(&s_full[i], s_phase, p.status)) {
+      // the last P.V: the tail barrier's second phase (its only one for a one-block tile)
+      if (mbar_wait(&tail_done[i], nblk >= 2 ? 1u : 0u, p.status)) {
         tc_fence_after();
         const float inv = l_run == 0.f ? 0.f : 1.0f / l_run;
 #pragma unroll 1
@@ -589,13 +624,24 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   }
 }
 
+#ifdef SVODB_TRACE
+}  // namespace
+}  // namespace svodb
+extern "C" int svodb_debug_read_trace(unsigned int* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, svodb::g_trace, sizeof(unsigned int) * n);
+}
+namespace svodb {
+namespace {
+#endif
+
 bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T, int D>
 int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   using C = FaCfg<D>;
   CUtensorMap tq, tk, tv;
-  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint32_t box[4] = {64, 1, 128, 1};     // Q tile rows
+  const uint32_t kvbox[4] = {64, 1, kBKV, 1};  // K/V block rows
   {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
     const uint64_t st[3] = {(uint64_t)a.q_sh, (uint64_t)a.q_st, (uint64_t)a.q_sb};
@@ -605,8 +651,8 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.batch};
     const uint64_t stk[3] = {(uint64_t)a.k_sh, (uint64_t)a.k_st, (uint64_t)a.k_sb};
     const uint64_t stv[3] = {(uint64_t)a.v_sh, (uint64_t)a.v_st, (uint64_t)a.v_sb};
-    if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, box)) return -1;
-    if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, box)) return -1;
+    if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
+    if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, kvbox)) return -1;
   }
   static bool attr_set = false;
   if (!attr_set) {
