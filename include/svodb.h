@@ -136,6 +136,25 @@ size_t svodb_attention_workspace_bytes(int64_t batch, int64_t t, int64_t heads, 
 int svodb_attention(const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v, const svodb_attn_opts* opts,
                     svodb_tensor* o, void* stream);
 
+/* Bytes of the scratch array built into the library for
+ * `svodb_attention_splits_noalloc`; every GPU that loads the library holds this
+ * much until the process exits. */
+#define SVODB_NOALLOC_SCRATCH_BYTES (8u << 20)
+
+/* No counterpart in the reference. `svodb_attention` with key splits, for
+ * callers that may not allocate device memory when they call (inside a stream
+ * capture or a plan replay, where memory was laid out ahead of time and
+ * cudaMalloc is not allowed): the f32 partials live in a fixed
+ * SVODB_NOALLOC_SCRATCH_BYTES array inside the library instead of
+ * `opts->workspace`, which is ignored. Allocates nothing. Shapes whose partials
+ * (`svodb_attention_workspace_bytes`) exceed the array return
+ * SVODB_ERR_WORKSPACE. The array is shared by every call on a device: calls
+ * that overlap on the GPU race, so issue them on one stream; nothing in it
+ * needs clearing between calls. The first call on a device looks up the
+ * array's address; make it before starting a stream capture. */
+int svodb_attention_splits_noalloc(const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v,
+                                   const svodb_attn_opts* opts, svodb_tensor* o, void* stream);
+
 /* `ops::attention_packed(qkv, heads, kv_heads, opts)` (tk/src/ops/attention.rs:107-122):
  * qkv [B,T,(H+2Hkv)*D] read in place -> o [B,T,H,D]. */
 int svodb_attention_packed(const svodb_tensor* qkv, int32_t heads, int32_t kv_heads, const svodb_attn_opts* opts,

@@ -21,6 +21,8 @@ OK, ERR_SHAPE, ERR_DTYPE, ERR_HEADS, ERR_GRAPH, ERR_LAUNCH, ERR_UNREALIZED, ERR_
 
 F32, F16, BF16, I32, I64, U8 = range(6)
 
+NOALLOC_SCRATCH_BYTES = 8 << 20  # SVODB_NOALLOC_SCRATCH_BYTES
+
 
 class Tensor(C.Structure):
     _fields_ = [
@@ -101,6 +103,7 @@ SYMBOLS = [
     ("svodb_linear", C.c_int, [TensorP, TensorP, C.POINTER(LinearOpts), TensorP, C.c_void_p]),
     ("svodb_attention_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     ("svodb_attention", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
+    ("svodb_attention_splits_noalloc", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
     ("svodb_attention_packed", C.c_int, [TensorP, C.c_int32, C.c_int32, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
     ("svodb_combine_splits", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_void_p]),
     ("svodb_heads", C.c_int, [TensorP, C.POINTER(QkvOpts), TensorP, TensorP, TensorP, C.c_void_p]),

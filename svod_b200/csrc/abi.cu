@@ -182,6 +182,13 @@ bool same_shape(const svodb_tensor* a, const svodb_tensor* b) {
 __device__ uint32_t g_status_word = 0;
 
 namespace svodb {
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+}
+
 uint32_t* device_status_word() {
   static std::mutex mu;
   static std::vector<uint32_t*> words(64, nullptr);

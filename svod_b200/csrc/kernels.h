@@ -154,6 +154,9 @@ int launch_gemm_generic(const GemmArgs& a, cudaStream_t s);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 bool gemm_tc_covers(const GemmArgs& a);
 
+// Sets the calling thread's `svodb_last_error` text (printf-style).
+void set_last_error(const char* fmt, ...);
+
 // The device status word bounded waits report into (one per device).
 uint32_t* device_status_word();
 
