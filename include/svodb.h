@@ -204,7 +204,9 @@ int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_
  * tensor/src/nn/norm.rs:205-213) and Qwen3's last-token gather
  * (model/src/qwen3/model.rs:77-99): hidden [B,L,D] -> out [B,D] f32 rows of an
  * `out` that may be a slice of a wider gather buffer.
- * mode 0 = CLS, 1 = masked mean (mask [B,L] u8/i32), 2 = last token (lengths [B] i32). */
+ * mode 0 = CLS, 1 = masked mean (mask [B,L] u8/i32), 2 = last token (lengths [B] i32),
+ * 3 = gather: token indices [B,S] i32 -> out [B*S, D], the pooled slots of packed rows
+ * (model/src/qwen3/embed.rs:119-136, embedder.rs:37-52). */
 int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
                svodb_tensor* out, void* stream);
 

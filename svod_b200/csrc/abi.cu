@@ -775,10 +775,18 @@ int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, 
   TRY(realized(OP, "out", out));
   if (hidden->rank != 3 || !contiguous(hidden) || !is_float(hidden->dtype)) return shape_err(OP, "hidden", hidden, "[B, L, D]");
   const int64_t B = hidden->shape[0], L = hidden->shape[1], D = hidden->shape[2];
-  if (out->rank != 2 || out->shape[0] != B || out->shape[1] != D || out->stride[1] != 1 || out->dtype != SVODB_F32)
-    return shape_err(OP, "out", out, "[B, D] f32");
-  if (mode < 0 || mode > 2) return fail(SVODB_ERR_GRAPH, "%s: mode %d", OP, mode);
+  if (mode < 0 || mode > 3) return fail(SVODB_ERR_GRAPH, "%s: mode %d", OP, mode);
   const svodb_tensor* aux = mask_or_lengths;
+  int64_t slots = 1;
+  if (mode == 3) {
+    TRY(realized(OP, "token index", aux));
+    if (aux->rank != 2 || aux->shape[0] != B || !contiguous(aux)) return shape_err(OP, "token index", aux, "[B, S]");
+    if (aux->dtype != SVODB_I32) return dtype_err(OP, "token index", aux->dtype, SVODB_I32);
+    slots = aux->shape[1];
+  }
+  if (out->rank != 2 || out->shape[0] != B * slots || out->shape[1] != D || out->stride[1] != 1 ||
+      out->dtype != SVODB_F32)
+    return shape_err(OP, "out", out, "[B (x S), D] f32");
   if (mode == 1) {
     TRY(realized(OP, "mask", aux));
     if (aux->rank != 2 || aux->shape[0] != B || aux->shape[1] != L || !contiguous(aux)) return shape_err(OP, "mask", aux, "[B, L]");
@@ -794,6 +802,7 @@ int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, 
   a.aux = aux ? aux->data : nullptr;
   a.aux_i32 = aux ? aux->dtype == SVODB_I32 : 0;
   a.mode = mode;
+  a.slots = (int)slots;
   a.normalize = normalize;
   a.out = (float*)out->data;
   a.out_row_stride = out->stride[0];

@@ -44,7 +44,11 @@ struct Cfg {
   static constexpr int kStageBytes = (BM + BN) * BK * 2;
   static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  // Output staging for the TMA-store epilogue: one 128-row x 64-column sub-tile
+  // (16 KiB, 128-byte swizzle) per column half of the tile.
+  static constexpr int kStagingBytes = 2 * 128 * 128;
+  static constexpr size_t kSmemBytes =
+      (size_t)kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct Params {
@@ -65,6 +69,7 @@ struct Params {
   int rope_width;     // heads * head_dim turned columns (0 = none)
   int rope_head_dim;
   int64_t rope_seq;
+  int tma_epilogue;   // stage the output through shared memory and TMA-store it
   uint32_t* status;
 };
 
@@ -155,26 +160,45 @@ __device__ __forceinline__ void store32(const Params& p, int64_t row, bool row_o
   }
 }
 
+#ifdef SVODB_TRACE
+// Timeline probe (debug builds only): clock() stamps of CTA 0's MMA warp.
+__device__ unsigned int g_gemm_trace[8 * 64 * 4];
+#define GTRACE(kb, ev)                                                                            \
+  do {                                                                                            \
+    if (blockIdx.x == 0 && lane == 0 && gtile < 8 && (kb) < 64) g_gemm_trace[(gtile * 64 + (kb)) * 4 + (ev)] = (unsigned int)clock(); \
+  } while (0)
+#else
+#define GTRACE(kb, ev) \
+  do {                 \
+  } while (0)
+#endif
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
                    const Params p) {
   using C = Cfg<BN>;
   constexpr int S = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   // The swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * C::kStageBytes);
+  uint8_t* staging = smem + (size_t)S * C::kStageBytes;  // [2 halves][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::kStagingBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + S;
   uint64_t* acc_full = bars + 2 * S;
   uint64_t* acc_empty = bars + 2 * S + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  uint64_t* res_full = bars + 2 * S + 4;  // [2 halves]: residual sub-tile landed in staging
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.k + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+#ifdef SVODB_TRACE
+  int gtile = 0;
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -184,6 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kEpiWarps);
+      mbar_init(&res_full[i], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -250,8 +275,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the schedule so that addresses and descriptors stay
+    // warp-uniform values; one elected lane issues the MMAs and the commits.
+    {
       constexpr uint32_t idesc = umma_idesc(Elem<T>::kUmmaFormat, BM, BN, 0, 0);
+      const bool leader = elect_one();
+      const uint64_t desc0 = umma_desc_sw128(smem_u32(smem), 16, 1024);
       int s = 0;
       uint32_t ph = 0;
       int as = 0;
@@ -265,30 +294,34 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
+          GTRACE(kb, 0);
           if (!mbar_wait(&full[s], ph, p.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::kStageBytes);
-          const uint32_t b_addr = a_addr + BM * BK * 2;
+          GTRACE(kb, 1);
+          const uint64_t a_desc = desc0 + (uint64_t)((s * C::kStageBytes) >> 4);
+          const uint64_t b_desc = a_desc + (uint64_t)((BM * BK * 2) >> 4);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4) {
-            const uint64_t a_desc = umma_desc_sw128(a_addr + k4 * 32, 16, 1024);
-            const uint64_t b_desc = umma_desc_sw128(b_addr + k4 * 32, 16, 1024);
-            umma_ss(d_tmem, a_desc, b_desc, idesc, (kb | k4) != 0 ? 1u : 0u);
-          }
-          tc_commit(&empty[s]);
+          for (int k4 = 0; k4 < BK / 16; ++k4)  // 16 columns = 32 bytes inside the 128-byte swizzle row
+            if (leader) umma_ss(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+          if (leader) tc_commit(&empty[s]);
+          GTRACE(kb, 2);
           if (++s == S) {
             s = 0;
             ph ^= 1;
           }
         }
-        if (ok) tc_commit(&acc_full[as]);
+        if (ok && leader) tc_commit(&acc_full[as]);
+        __syncwarp();
         if (++as == 2) {
           as = 0;
           aph ^= 1;
         }
+#ifdef SVODB_TRACE
+        gtile++;
+#endif
       }
     }
   } else {
@@ -299,6 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const T* bias = (const T*)p.bias;
     int as = 0;
     uint32_t aph = 0;
+    uint32_t res_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mt, nt;
@@ -314,7 +348,77 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
       const int cols = p.out_bn / 2;  // output columns this warp covers
       const int c_lo = chalf * cols;
-      if (p.rope_width > 0 && n0 + c_lo < p.rope_width) {
+      if (p.tma_epilogue) {
+        // Staged epilogue: each column half (4 warps, 128 rows) builds 64-column
+        // sub-tiles in swizzled shared memory; one thread TMA-loads the residual
+        // sub-tile into the same buffer beforehand and TMA-stores the result, so
+        // global memory sees whole 128-byte rows instead of per-thread 16-byte
+        // pieces (which would compete with the operand loads of the next tile).
+        uint8_t* stg = staging + chalf * (128 * 128);
+        const bool chief = (ew & 3) == 0 && lane == 0;
+        const int r_tile = quarter * 32 + lane;  // this thread's row of the tile
+        const int m0 = mt * BM;
+        for (int sub = 0; sub < cols / 64; ++sub) {
+          const int c0 = c_lo + sub * 64;
+          const int n_at = n0 + c0;
+          // the previous store out of this buffer must have read it
+          if (chief) tma_store_wait_read();
+          named_barrier(1 + chalf, 128);
+          if (p.residual != nullptr && chief && n_at < p.n) {
+            mbar_expect_tx(&res_full[chalf], 128 * 128);
+            tma_load_2d(stg, &tmap_r, &res_full[chalf], n_at, m0);
+          }
+          float x[64];
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            float (&xs)[32] = *reinterpret_cast<float (*)[32]>(&x[32 * hc]);
+            acc32<T>(t_acc + (uint32_t)(c0 + 32 * hc), bias, n_at + 32 * hc, p.n, xs);
+            act32(xs, p.act);
+            if (p.gated) {
+              float u[32];
+              acc32<T>(t_acc + (uint32_t)(BN / 2 + c0 + 32 * hc), bias != nullptr ? bias + p.n : nullptr,
+                       n_at + 32 * hc, p.n, u);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) xs[i] *= u[i];
+            }
+            if (p.has_scale) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) xs[i] *= p.scale;
+            }
+          }
+          if (p.residual != nullptr && n_at < p.n) {
+            // A timed-out wait is only recorded here: every thread of the half
+            // still walks both named barriers below, then leaves the tile loop.
+            if (!mbar_wait(&res_full[chalf], res_phase, p.status)) ok = false;
+            res_phase ^= 1;
+          }
+          // row r of the sub-tile: 8 chunks of 16 bytes, chunk c at (c ^ (r & 7))
+          uint8_t* srow = stg + r_tile * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint4* slot = reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4));
+            if (p.residual != nullptr && n_at < p.n) {
+              const uint4 rv = *slot;
+              const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = Elem<T>::unpack(rr[i]);
+                x[c * 8 + 2 * i] += f.x;
+                x[c * 8 + 2 * i + 1] += f.y;
+              }
+            }
+            *slot = make_uint4(Elem<T>::pack(x[c * 8 + 0], x[c * 8 + 1]), Elem<T>::pack(x[c * 8 + 2], x[c * 8 + 3]),
+                               Elem<T>::pack(x[c * 8 + 4], x[c * 8 + 5]), Elem<T>::pack(x[c * 8 + 6], x[c * 8 + 7]));
+          }
+          fence_proxy_async_smem();
+          named_barrier(1 + chalf, 128);
+          if (chief && n_at < p.n) {
+            tma_store_2d(&tmap_c, stg, n_at, m0);
+            tma_store_commit();
+          }
+        }
+        if (!ok) break;
+      } else if (p.rope_width > 0 && n0 + c_lo < p.rope_width) {
         // In-store RoPE: whole heads, pairs (c, c + head_dim/2) from two chunks.
         const int hd = p.rope_head_dim, half = hd / 2;
         const T* cos = (const T*)p.rope_cos;
@@ -373,6 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
+  if (p.tma_epilogue && warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -394,6 +499,17 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
   if (!make_tmap_2d(&ta, a.a, dt, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, BM)) return -1;
   const uint64_t w_rows = (uint64_t)(a.gated ? 2 * a.n : a.n);
   if (!make_tmap_2d(&tw, a.w, dt, (uint64_t)a.k, w_rows, (uint64_t)a.ldw, BK, a.gated ? BN / 2 : BN)) return -1;
+  // The staged epilogue needs whole 64-column sub-tiles per column half and
+  // plain (non-rotating) stores; small tiles and RoPE keep the direct stores.
+  p.tma_epilogue = (p.out_bn >= 128 && a.rope_cos == nullptr) ? 1 : 0;
+  CUtensorMap tc = ta, tr = ta;
+  if (p.tma_epilogue) {
+    if (!make_tmap_2d(&tc, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, BM)) return -1;
+    tr = tc;
+    if (a.residual != nullptr &&
+        !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
+      return -1;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -403,11 +519,21 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
-  gemm_tc_kernel<T, BN><<<grid, kThreads, C::kSmemBytes, s>>>(ta, tw, p);
+  gemm_tc_kernel<T, BN><<<grid, kThreads, C::kSmemBytes, s>>>(ta, tw, tc, tr, p);
   if (cfg != nullptr)
     snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d}", BM, BN, BK, C::kStages, a.gated, grid);
   return 0;
 }
+
+#ifdef SVODB_TRACE
+}  // namespace
+}  // namespace svodb
+extern "C" int svodb_debug_read_gemm_trace(unsigned int* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, svodb::g_gemm_trace, sizeof(unsigned int) * n);
+}
+namespace svodb {
+namespace {
+#endif
 
 int sm_count() {
   static int sms = 0;

@@ -93,9 +93,10 @@ __global__ void __launch_bounds__(256)
 template <typename T>
 __global__ void __launch_bounds__(256)
     pool_kernel(const T* __restrict__ hidden, const void* __restrict__ aux, int aux_i32, int mode,
-                float* __restrict__ out, int64_t out_row_stride, int64_t l_len, int d) {
+                float* __restrict__ out, int64_t out_row_stride, int64_t l_len, int d, int slots) {
   __shared__ float part[2][128];
-  const int64_t b = blockIdx.y;
+  // mode 3 gathers `slots` tokens per row: output row y = (b, slot)
+  const int64_t b = mode == 3 ? blockIdx.y / slots : blockIdx.y;
   const int col = blockIdx.x * 128 + (threadIdx.x & 127);
   const int tl = threadIdx.x >> 7;
   const T* h = hidden + b * l_len * d;
@@ -113,6 +114,9 @@ __global__ void __launch_bounds__(256)
     if (mode == 2) {
       t = (int64_t)((const int32_t*)aux)[b] - 1;
       t = t < 0 ? 0 : (t > l_len - 1 ? l_len - 1 : t);
+    } else if (mode == 3) {
+      t = (int64_t)((const int32_t*)aux)[blockIdx.y];
+      t = t < 0 ? 0 : (t > l_len - 1 ? l_len - 1 : t);
     }
     acc = Elem<T>::to_f(h[t * d + col]);
   }
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(256)
   if (tl == 0 && col < d) {
     float v = part[0][threadIdx.x] + part[1][threadIdx.x];
     if (mode == 1) v = v / fmaxf(cnts[0] + cnts[1], 1e-9f);
-    out[b * out_row_stride + col] = v;
+    out[(int64_t)blockIdx.y * out_row_stride + col] = v;
   }
 }
 
@@ -178,17 +182,18 @@ void launch_embed(const EmbedArgs& a, cudaStream_t s) {
 
 void launch_pool(const PoolArgs& a, cudaStream_t s) {
   if (a.batch == 0) return;
-  dim3 grid((unsigned)((a.d + 127) / 128), (unsigned)a.batch);
+  const int64_t out_rows = a.mode == 3 ? a.batch * a.slots : a.batch;
+  dim3 grid((unsigned)((a.d + 127) / 128), (unsigned)out_rows);
   if (a.dtype == SVODB_BF16)
     pool_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
-                                                    a.out_row_stride, a.l, a.d);
+                                                    a.out_row_stride, a.l, a.d, a.slots);
   else if (a.dtype == SVODB_F16)
     pool_kernel<__half><<<grid, 256, 0, s>>>((const __half*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
-                                             a.out_row_stride, a.l, a.d);
+                                             a.out_row_stride, a.l, a.d, a.slots);
   else
     pool_kernel<float><<<grid, 256, 0, s>>>((const float*)a.hidden, a.aux, a.aux_i32, a.mode, a.out,
-                                            a.out_row_stride, a.l, a.d);
-  if (a.normalize) l2_kernel<<<(unsigned)a.batch, 256, 0, s>>>(a.out, a.out_row_stride, a.d);
+                                            a.out_row_stride, a.l, a.d, a.slots);
+  if (a.normalize) l2_kernel<<<(unsigned)out_rows, 256, 0, s>>>(a.out, a.out_row_stride, a.d);
 }
 
 void launch_rope_table(double theta, const int32_t* positions, int64_t n_pos, int head_dim, void* cos, void* sin,

@@ -63,7 +63,8 @@ struct PoolArgs {
   const void* hidden;
   const void* aux;  // mask [B,L] (u8 or i32) or lengths [B] i32
   int aux_i32;
-  int mode;  // 0 cls, 1 mean, 2 last
+  int mode;  // 0 cls, 1 mean, 2 last, 3 gather `slots` tokens per row (aux = [B, slots] i32)
+  int slots;
   int normalize;
   float* out;
   int64_t out_row_stride;

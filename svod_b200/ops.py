@@ -377,7 +377,7 @@ def embed(ids, table, pos_table=None, type_row=None, pad_id: int = -1):
     return out
 
 
-POOL_CLS, POOL_MEAN, POOL_LAST = 0, 1, 2
+POOL_CLS, POOL_MEAN, POOL_LAST, POOL_GATHER = 0, 1, 2, 3
 
 
 def pool(hidden, aux=None, mode: int = POOL_CLS, normalize: bool = True, out=None):
@@ -385,7 +385,8 @@ def pool(hidden, aux=None, mode: int = POOL_CLS, normalize: bool = True, out=Non
     -> f32 `[B,D]`; `out` may be a row slice of a wider gather buffer."""
     B, _, D = hidden.shape
     if out is None:
-        out = torch.empty(B, D, dtype=torch.float32, device=hidden.device)
+        rows = B * aux.shape[1] if mode == POOL_GATHER else B
+        out = torch.empty(rows, D, dtype=torch.float32, device=hidden.device)
     if aux is not None and aux.dtype not in (torch.bool, torch.uint8, torch.int32):
         aux = aux.to(torch.int32)
     a, b, c = _desc(hidden), _desc(aux), _desc(out)

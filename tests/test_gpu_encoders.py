@@ -153,3 +153,40 @@ def test_padding_rows_do_not_change_live_rows():
     ids2[0, 100:] = 7
     b = m.forward(ids2, lengths)
     assert torch.equal(a[0], b[0])
+
+
+def test_packed_rows_match_separate_forwards():
+    """`packed_rows_match_separate_forwards` (model/src/test/unit/qwen3/model.rs:104):
+    rows packed end to end with segment starts and per-token positions embed as
+    each row alone does."""
+    from svod_b200 import encoder_head as EH
+    cfg = E.Qwen3Config(vocab_size=1000, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=64, intermediate_size=512)
+    m = E.Qwen3Embedder.random_init(cfg, seed=3)
+    rng = np.random.default_rng(0)
+    rows = [rng.integers(1, 1000, n).tolist() for n in (200, 17, 90, 128, 1, 60)]
+    packed = EH.Qwen3PackedEmbedder(m, max_batch=2, max_len=512).embed(rows)
+    for r, got in zip(rows, packed):
+        ids = torch.tensor([r], dtype=torch.int32).cuda()
+        alone = m.forward(ids, torch.tensor([len(r)], dtype=torch.int32).cuda())
+        assert max_abs(got, host(alone)[0]) < 2e-2
+        assert abs(float(np.linalg.norm(got)) - 1.0) < 1e-3
+
+
+def test_head_plans_bucket_capture_once_and_return_live_rows():
+    from svod_b200 import encoder_head as EH
+    cfg = E.XlmRobertaConfig(vocab_size=500, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                             intermediate_size=512, max_position_embeddings=514)
+    m = E.XlmRobertaEncoder.random_init(cfg, seed=4)
+    plans = EH.HeadPlans(m, max_batch=8, max_seq=512, pad_id=1)
+    rng = np.random.default_rng(1)
+    chunks = [rng.integers(2, 500, n).tolist() for n in (100, 30, 128, 5, 77)]
+    out = EH.embed_chunks(plans, chunks)
+    assert out.shape == (5, 256) and len(plans.plans) == 1 and (8, 128) in plans.plans
+    for c, got in zip(chunks, out):
+        ids = torch.tensor([c], dtype=torch.int32).cuda()
+        mask = torch.ones(1, len(c), dtype=torch.bool).cuda()
+        alone = m.forward(ids, mask)
+        assert max_abs(got, host(alone)[0]) < 2e-2
+    out2 = EH.embed_chunks(plans, chunks[:2])          # another bucket: (2, 128)
+    assert len(plans.plans) == 2 and max_abs(out2, out[:2]) < 2e-2
