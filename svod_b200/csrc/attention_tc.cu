@@ -147,6 +147,10 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
   return p;
 }
 
+#ifndef SVODB_FA_TURNS
+#define SVODB_FA_TURNS 1  // the two query tiles take turns on the MUFU unit
+#endif
+
 #ifndef SVODB_FA_POLY
 #define SVODB_FA_POLY 0  // of every 4 score pairs, how many take the polynomial 2^x
 #endif
@@ -194,7 +198,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   uint64_t* s_full = v_empty + S;              // [2 tiles][2 buffers]
   uint64_t* p_full = s_full + 4;               // [2 tiles][2 buffers]
   uint64_t* tail_done = p_full + 4;            // [2 tiles]: the last two P.V of a tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail_done + 2);
+  uint64_t* turn = tail_done + 2;              // [2 tiles][4 warps]: whose exponentials run next
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 8);
   int* scan = reinterpret_cast<int*>(tmem_slot + 1);  // [0] first zero, [1] last nonzero + 1
 
   const int warp = threadIdx.x >> 5;
@@ -219,6 +224,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&turn[i], 1);
     for (int i = 0; i < S; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 2);  // released by both tiles' issuers
@@ -479,6 +485,15 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     float l_run = 0.f;
     bool ok = true;
     const int nblk = r.hi - r.lo;
+    // The two tiles' warps of one quarter share a scheduler and its MUFU unit.
+    // Left alone they fall into step, their exponential bursts collide and the
+    // unit idles while both read scores and take maxima. They take turns
+    // instead: tile 0 runs the exponentials of its block n, then tile 1 those
+    // of its block n, then tile 0 block n+1, ... for the blocks both tiles have,
+    // so one tile's TMEM reads and maxima overlap the other's exponentials.
+    const int n_paired = SVODB_FA_TURNS ? min(r0.hi - r0.lo, r1.hi - r1.lo) : 0;
+    uint64_t* my_turn = &turn[i * 4 + quarter];
+    uint64_t* other_turn = &turn[(1 - i) * 4 + quarter];
     for (int j = r.lo; j < r.hi; ++j) {
       const int n = j - r.lo;
       const int buf = n & 1;
@@ -567,7 +582,16 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       }
       m_run = m_new;
       TRACE(1 + i, n, 2);
-      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float m_use = m_run == -INFINITY ? 0.f : m_run;
+      if (n < n_paired && (i == 1 || n > 0)) {
+        // tile 1 follows tile 0's block n; tile 0 follows tile 1's block n-1
+        const uint32_t done = (uint32_t)(i == 1 ? n : n - 1);
+        if (!mbar_wait(my_turn, done & 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        asm volatile("" : "+f"(m_use));  // keeps the exponentials below the wait
+      }
       // p = 2^(s*scale - m) with the scale and the subtraction as packed f32x2
       // FMAs; the row sum is taken from the f32 values, P is rounded to the
       // stream type and written over S.
@@ -603,6 +627,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         }
       }
       tmem_st32(s_tmem, pk);
+      if (n < n_paired) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(other_turn);
+      }
       l_run += (la.x + la.y) + (lb.x + lb.y);
       TRACE(1 + i, n, 3);
       // Every lane's P stores have completed (wait::st is warp-wide); one lane
