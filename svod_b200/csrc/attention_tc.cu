@@ -151,6 +151,14 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
 #define SVODB_FA_TURNS 1  // the two query tiles take turns on the MUFU unit
 #endif
 
+#ifndef SVODB_FA_HANDOVER
+#define SVODB_FA_HANDOVER 32  // score pairs (of 32) after which the MUFU unit is handed to the other tile
+#endif
+
+#ifndef SVODB_FA_PREFETCH_S
+#define SVODB_FA_PREFETCH_S 1  // request the next block's scores before publishing P
+#endif
+
 #ifndef SVODB_FA_POLY
 #define SVODB_FA_POLY 0  // of every 4 score pairs, how many take the polynomial 2^x
 #endif
@@ -163,7 +171,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 
 #ifdef SVODB_TRACE
 // Timeline probe (debug builds only): clock() stamps of CTA (0,0,0).
-__device__ unsigned int g_trace[3 * 64 * 8];
+__device__ unsigned int g_trace[9 * 64 * 8];
 #define TRACE(role, iter, ev)                                                    \
   do {                                                                           \
     if (trace_on && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = (unsigned int)clock(); \
@@ -198,15 +206,14 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   uint64_t* s_full = v_empty + S;              // [2 tiles][2 buffers]
   uint64_t* p_full = s_full + 4;               // [2 tiles][2 buffers]
   uint64_t* tail_done = p_full + 4;            // [2 tiles]: the last two P.V of a tile
-  uint64_t* turn = tail_done + 2;              // [2 tiles][4 warps]: whose exponentials run next
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail_done + 2);
   int* scan = reinterpret_cast<int*>(tmem_slot + 1);  // [0] first zero, [1] last nonzero + 1
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 #ifdef SVODB_TRACE
   const bool trace_on = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
-                        (warp == 1 || warp == 3 || warp == 4 || warp == 8);
+                        (warp == 1 || warp == 3 || warp >= 4);
 #endif
   // Heavier (later, under a causal mask) query tiles are scheduled first.
   const int qt = p.n_qt - 1 - (int)blockIdx.x;
@@ -224,7 +231,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp
     }
-    for (int i = 0; i < 8; ++i) mbar_init(&turn[i], 1);
     for (int i = 0; i < S; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 2);  // released by both tiles' issuers
@@ -491,31 +497,46 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     // instead: tile 0 runs the exponentials of its block n, then tile 1 those
     // of its block n, then tile 0 block n+1, ... for the blocks both tiles have,
     // so one tile's TMEM reads and maxima overlap the other's exponentials.
+    // The hand-over is a named barrier per (tile, quarter) over the two warps
+    // (64 threads): the waiting warp is descheduled and polls nothing, so it
+    // takes neither issue slots nor MIO queue entries from the warp that runs.
+    // A named barrier has no timeout, so a warp that gives up (a bounded wait
+    // ran out) still walks the rest of the hand-over sequence below the loop
+    // and its partner is never left waiting.
     const int n_paired = SVODB_FA_TURNS ? min(r0.hi - r0.lo, r1.hi - r1.lo) : 0;
-    uint64_t* my_turn = &turn[i * 4 + quarter];
-    uint64_t* other_turn = &turn[(1 - i) * 4 + quarter];
+    const int my_turn = 1 + i * 4 + quarter;
+    const int other_turn = 1 + (1 - i) * 4 + quarter;
+    int turns_done = 0;  // hand-over steps this warp has completed
+    // The 64-column score row of this thread. The read of block n+1 is issued
+    // at the end of block n whenever those scores are already complete (they
+    // usually are: S runs a block ahead), so its latency and the barrier probe
+    // hide behind the publication of P(n).
+    uint32_t sr[2][32];
+    bool requested = false;
     for (int j = r.lo; j < r.hi; ++j) {
       const int n = j - r.lo;
       const int buf = n & 1;
-      if (!mbar_wait(&s_full[i * 2 + buf], (uint32_t)((n >> 1) & 1), p.status)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      TRACE(1 + i, n, 0);
+      turns_done = n;
       const uint32_t s_tmem = tmem_base + (uint32_t)((i * 2 + buf) * kBKV) + lane_addr;
+      if (!requested) {
+        if (!mbar_wait(&s_full[i * 2 + buf], (uint32_t)((n >> 1) & 1), p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        tmem_ld32(s_tmem, sr[0]);
+        tmem_ld32(s_tmem + 32, sr[1]);
+      }
+      TRACE(warp - 3, n, 0);
       const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
       bool need_mask = j1 >= ctx.len || ctx.general_mask || p.has_chunk;
       if (p.causal && j1 > i_first) need_mask = true;
       if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
       if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
 
-      // The 64-column score row of this thread, both loads in flight together.
-      uint32_t sr[2][32];
-      tmem_ld32(s_tmem, sr[0]);
-      tmem_ld32(s_tmem + 32, sr[1]);
-      tmem_ld_wait();
-      TRACE(1 + i, n, 1);
+      tmem_ld_wait_for(sr[0]);
+      tmem_ld_wait_for(sr[1]);
+      TRACE(warp - 3, n, 1);
       if (need_mask) {
         // Hidden scores become -inf: they drop out of the maximum and their
         // probability is 2^(-inf) = 0 (the scale is positive on this path).
@@ -581,16 +602,12 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_st_wait();
       }
       m_run = m_new;
-      TRACE(1 + i, n, 2);
+      TRACE(warp - 3, n, 2);
       float m_use = m_run == -INFINITY ? 0.f : m_run;
       if (n < n_paired && (i == 1 || n > 0)) {
         // tile 1 follows tile 0's block n; tile 0 follows tile 1's block n-1
-        const uint32_t done = (uint32_t)(i == 1 ? n : n - 1);
-        if (!mbar_wait(my_turn, done & 1u, p.status)) {
-          ok = false;
-          break;
-        }
-        asm volatile("" : "+f"(m_use));  // keeps the exponentials below the wait
+        named_barrier(my_turn, 64);
+        asm volatile("" : "+f"(m_use));  // keeps the exponentials below the barrier
       }
       // p = 2^(s*scale - m) with the scale and the subtraction as packed f32x2
       // FMAs; the row sum is taken from the f32 values, P is rounded to the
@@ -598,6 +615,40 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[32];
+#if SVODB_FA_POLY == 0
+      // The MUFU unit takes one warp instruction every 8 cycles and returns its
+      // result some tens of cycles later. All scaled scores are formed first,
+      // then the 64 exponentials are issued back to back while the sums and the
+      // 16-bit packing of pair k - kLag run in their shadow, so nothing waits
+      // on a result that was only just requested.
+      constexpr int kLag = 6;
+      float2 xs[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k)
+        xs[k] = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
+                                       __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
+                           sl2_2, nm_2);
+#pragma unroll
+      for (int k = 0; k < 32 + kLag; ++k) {
+        if (k < 32) {
+          xs[k].x = ex2_approx(xs[k].x);
+          xs[k].y = ex2_approx(xs[k].y);
+        }
+        if (k == SVODB_FA_HANDOVER - 1 && SVODB_FA_HANDOVER < 32) {
+          // hand the MUFU unit over part-way: the other tile's first exponentials
+          // overlap this tile's last ones (the operand ties the arrival to the
+          // exponential it follows)
+          if (n < n_paired && (i == 0 || n + 1 < n_paired))
+            asm volatile("bar.arrive %0, 64;" ::"r"(other_turn), "f"(xs[k].y) : "memory");
+        }
+        if (k >= kLag) {
+          const int d = k - kLag;
+          if (d & 1) lb = __fadd2_rn(lb, xs[d]);
+          else la = __fadd2_rn(la, xs[d]);
+          pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
+        }
+      }
+#else
       // The exponentials are split between the MUFU unit and a polynomial on the
       // FMA pipe, which are otherwise the softmax's two unevenly loaded pipes.
       // Blocks that hide keys keep every exponential on MUFU (exact zeros).
@@ -626,16 +677,31 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           for (int q = 0; q < 4; ++q) pk[16 * c + e / 2 + q] = Elem<T>::pack(x[q].x, x[q].y);
         }
       }
+#endif
       tmem_st32(s_tmem, pk);
-      if (n < n_paired) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(other_turn);
-      }
+      // tile 0 waits for tile 1's block n only if it has a paired block n+1
+      if (SVODB_FA_HANDOVER >= 32 && n < n_paired && (i == 0 || n + 1 < n_paired))
+        named_barrier_arrive(other_turn, 64);
+      turns_done = n + 1;
       l_run += (la.x + la.y) + (lb.x + lb.y);
-      TRACE(1 + i, n, 3);
+      TRACE(warp - 3, n, 3);
+      requested = false;
+      if (SVODB_FA_PREFETCH_S && n + 1 < nblk &&
+          mbar_test_wait(&s_full[i * 2 + (buf ^ 1)], (uint32_t)(((n + 1) >> 1) & 1))) {
+        tc_fence_after();
+        const uint32_t next_tmem = tmem_base + (uint32_t)((i * 2 + (buf ^ 1)) * kBKV) + lane_addr;
+        tmem_ld32(next_tmem, sr[0]);
+        tmem_ld32(next_tmem + 32, sr[1]);
+        requested = true;
+      }
+      TRACE(warp - 3, n, 5);
+#ifdef SVODB_TRACE
+      if (trace_on && n < 64) g_trace[((warp - 3) * 64 + n) * 8 + 6] = requested ? 1u : 0u;
+#endif
       // Every lane's P stores have completed (wait::st is warp-wide); one lane
       // per warp then publishes the tile to the MMA issuer.
       tmem_st_wait();
+      TRACE(warp - 3, n, 7);
       // The tail barrier sees two commits (P.V of blocks N-2 and N-1); a parity
       // wait tells only adjacent phases apart, so the first is observed before
       // the last P — which lets the second happen — is published.
@@ -646,7 +712,13 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
-      TRACE(1 + i, n, 4);
+      TRACE(warp - 3, n, 4);
+    }
+    if (!ok) {
+      for (int m = turns_done; m < n_paired; ++m) {
+        if (i == 1 || m > 0) named_barrier(my_turn, 64);
+        if (i == 0 || m + 1 < n_paired) named_barrier_arrive(other_turn, 64);
+      }
     }
     // ---- epilogue: O / l ----
     T* orow = (T*)p.o + b * p.o_sb + row * p.o_st + (int64_t)h * p.o_sh;
