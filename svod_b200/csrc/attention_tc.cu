@@ -14,23 +14,34 @@
 //
 // Blackwell design — one CTA per (256 query rows, head, batch), 384 threads:
 //   warp 0        TMA loader: two 128-row Q tiles once, then K and V blocks of
-//                 128 keys through separate shared-memory rings (non-multicast
+//                 64 keys through two 4-stage shared-memory rings (non-multicast
 //                 TMA, 128B swizzle; ragged T / Tk tails zero-filled).
-//   warp 1        MMA issuer (one thread): S_i = Q_i.K^T (SS, both K-major) into
-//                 TMEM, then O_i += P_i.V with P read from TMEM (TS) and V as the
-//                 MN-major shared-memory operand. The two query tiles alternate
-//                 (PV_0, QK_0, PV_1, QK_1) so the tensor core works on one tile
-//                 while the other tile's softmax runs.
-//   warps 2-3     turn a bool key mask into a prefix length or a bitmask.
+//   warps 1, 3    MMA issuers, one per query tile (the whole warp walks the
+//                 schedule so descriptors stay warp-uniform; an elected lane
+//                 issues). Step t: O_i += P_i(t-1).V(t-1) with P read from TMEM
+//                 (TS form) and V as the MN-major shared-memory operand, then
+//                 S_i(t+1) = Q_i.K(t+1)^T (SS form) into the score buffer that
+//                 P_i(t-1) just vacated: scores run one block ahead of the
+//                 softmax. Completion is in issue order, so "S(t+1) complete"
+//                 also tells the softmax that P.V(t-1) has landed; only the last
+//                 two P.V of a tile need a barrier of their own (tail_done).
+//   warp 2        TMEM allocation; warps 2-3 turn a bool key mask into a prefix
+//                 length or a bitmask before the main loop.
 //   warps 4-7     softmax of tile 0: one query row per thread, S read from TMEM
 //   warps 8-11    softmax of tile 1  (tcgen05.ld), P written back over S as
 //                 packed 16-bit (tcgen05.st), O rescaled in TMEM when a row's
-//                 maximum moves, final O/l -> global.
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D);
-// P_i aliases the first 64 columns of S_i.
+//                 maximum moves, final O/l -> global. The two warps that share
+//                 a scheduler (same lane quarter, different tile) take turns on
+//                 the MUFU unit through a named barrier, and a warp requests the
+//                 next block's scores before it publishes P.
+// Registers: setmaxnreg moves the loader/issuer warpgroup down to 64 and the
+// softmax warpgroups up to 216 inside the CTA's launch-time pool (384 x 168).
+// TMEM (512 columns): per tile two 64-column score buffers, S_i[buf] at
+// (2i+buf)*64; O_i at 256 + i*D; P aliases the first 32 columns of its S buffer.
 //
 // Every mbarrier wait is bounded; a timeout records a status code and the CTA
-// drains and frees its TMEM.
+// drains and frees its TMEM. Named barriers have no timeout, so a warp that
+// gave up still walks the rest of its hand-over sequence.
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
