@@ -182,10 +182,12 @@ def reference_arm(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
-def build_model(kind: str, device):
+def build_model(kind: str, device, reference_ops: bool = False):
     from svod_b200 import encoders as E
     if kind == "qwen3":
-        return E.Qwen3Embedder.random_init(E.Qwen3Config(), seed=0, device=device), "lengths"
+        m = E.Qwen3Embedder.random_init(E.Qwen3Config(), seed=0, device=device)
+        m.fused_prologue = not reference_ops
+        return m, "lengths"
     if kind == "xlmr":
         return E.XlmRobertaEncoder.random_init(E.XlmRobertaConfig(), seed=0, device=device), "mask"
     return E.ModernBertEncoder.random_init(E.ModernBertConfig(), seed=0, device=device), "mask"
@@ -282,7 +284,7 @@ def gpu_arm(args):
     kind, batch, seq = WORKLOADS[args.workload]
     peaks = measured_peaks()
 
-    model, aux_kind = build_model(kind, device)
+    model, aux_kind = build_model(kind, device, args.reference_ops)
     D = model.cfg.hidden_size
     gathered = torch.zeros(world * batch, D, dtype=torch.float32, device=device)
     mine = gathered[rank * batch:(rank + 1) * batch]
@@ -452,6 +454,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b-embed", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--reference-ops", action="store_true",
+                    help="Qwen3: the reference's op sequence (linear, heads, attention) instead of the "
+                         "q/k prologue fused into the projection's store")
     ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "rms_norm", "heads"],
                     help="run a few launches of one kernel on a small case (for profiler captures) and exit")
     ap.add_argument("--case-batch", type=int, default=4)

@@ -87,6 +87,8 @@ int svodb_device_status(void* stream);
 
 /* ---- op layer: `svod_tk::ops` --------------------------------------------- */
 
+struct svodb_qkv_opts;
+
 /* `ops::Linear` + `ops::Rotary` (tk/src/ops/linear.rs:24-56). */
 typedef struct svodb_linear_opts {
   const svodb_tensor* bias;     /* [N] ([2N] gated) or NULL */
@@ -101,6 +103,14 @@ typedef struct svodb_linear_opts {
   int32_t rope_head_dim;
   int64_t into_at;              /* y is channels [at, at+N) of a wider buffer: pass
                                    `y` as that view (data offset, wide row stride) */
+  /* No counterpart in the reference's `Linear`: the attention prologue of
+   * `ops::heads` (tk/src/ops/heads.rs:37-102) applied in this projection's
+   * store. x is [B,T,K], N = (heads + 2*kv_heads)*head_dim; q and k heads are
+   * RMS-normalised and rotated from the f32 accumulator (no rounding between
+   * the projection and the prologue), v heads pass through, and y stays the
+   * packed [B,T,N] projection that `svodb_attention_packed` reads in place.
+   * Excludes rope_*, gated, act, scale and residual. NULL = off. */
+  const struct svodb_qkv_opts* qkv;
 } svodb_linear_opts;
 
 /* `ops::linear(x, w, opts)` (tk/src/ops/linear.rs:63-191):

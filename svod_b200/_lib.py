@@ -50,6 +50,7 @@ class LinearOpts(C.Structure):
         ("rope_heads", C.c_int32),
         ("rope_head_dim", C.c_int32),
         ("into_at", C.c_int64),
+        ("qkv", C.c_void_p),  # const svodb_qkv_opts* (QkvOpts is declared below)
     ]
 
 

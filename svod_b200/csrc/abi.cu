@@ -245,6 +245,27 @@ int svodb_device_status(void* stream) {
 // ---------------------------------------------------------------------------
 // linear
 // ---------------------------------------------------------------------------
+namespace {
+// The attention prologue over a packed projection y [B,T,(H+2Hkv)*D], each head
+// rewritten where it lies.
+void heads_in_place(const svodb_qkv_opts* qo, svodb_tensor* y, int per_batch, cudaStream_t s) {
+  if (qo->q_norm == nullptr && qo->k_norm == nullptr && qo->rope_cos == nullptr) return;
+  HeadsArgs h{};
+  h.qkv = y->data;
+  h.q_w = qo->q_norm ? qo->q_norm->data : nullptr;
+  h.k_w = qo->k_norm ? qo->k_norm->data : nullptr;
+  h.cos = qo->rope_cos ? qo->rope_cos->data : nullptr;
+  h.sin = qo->rope_sin ? qo->rope_sin->data : nullptr;
+  h.batch = y->shape[0], h.t = y->shape[1];
+  h.heads = qo->heads, h.kv_heads = qo->kv_heads, h.d = qo->head_dim;
+  h.eps = (float)qo->eps;
+  h.per_batch_tables = per_batch;
+  h.dtype = y->dtype;
+  h.in_place = 1;
+  launch_heads(h, s);
+}
+}  // namespace
+
 int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linear_opts* opts, svodb_tensor* y,
                  void* stream) {
   static const char* OP = "linear";
@@ -282,6 +303,41 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
   }
   const bool rope = opts->rope_cos != nullptr;
   int64_t seq = 0;
+  const svodb_qkv_opts* qo = opts->qkv;
+  int qkv_per_batch = 0;
+  if (qo != nullptr) {
+    // The `ops::heads` prologue in the store: same checks as `svodb_heads`.
+    if (rope || opts->gated || opts->act != SVODB_ACT_NONE || opts->has_scale || opts->residual != nullptr)
+      return fail(SVODB_ERR_GRAPH, "%s: the qkv prologue excludes rope, gate, activation, scale and residual", OP);
+    const int H = qo->heads, Hkv = qo->kv_heads, d = qo->head_dim;
+    if (!(Hkv > 0 && H > 0 && H % Hkv == 0))
+      return fail(SVODB_ERR_HEADS, "%s: %d query heads are not a multiple of %d key/value heads", OP, H, Hkv);
+    if (x->rank != 3) return shape_err(OP, "x", x, "[B, T, K] under the qkv prologue");
+    if (d <= 0 || n != (int64_t)(H + 2 * Hkv) * d) return shape_err(OP, "w", w, "[(heads + 2*kv_heads)*head_dim, K]");
+    const svodb_tensor* norms[2] = {qo->q_norm, qo->k_norm};
+    const char* nnames[2] = {"q norm", "k norm"};
+    for (int i = 0; i < 2; ++i) {
+      if (norms[i] == nullptr) continue;
+      TRY(realized(OP, nnames[i], norms[i]));
+      if (norms[i]->rank != 1 || norms[i]->shape[0] != d || !contiguous(norms[i]))
+        return shape_err(OP, nnames[i], norms[i], "[head_dim]");
+      if (norms[i]->dtype != x->dtype) return dtype_err(OP, nnames[i], norms[i]->dtype, x->dtype);
+    }
+    if (qo->rope_cos != nullptr) {
+      if (d % 2 != 0) return shape_err(OP, "w", w, "an even head_dim under a rotation");
+      TRY(realized(OP, "cos", qo->rope_cos));
+      TRY(realized(OP, "sin", qo->rope_sin));
+      const svodb_tensor* c = qo->rope_cos;
+      const int64_t B = x->shape[0], T = x->shape[1];
+      const bool fits = c->rank == 4 && (c->shape[0] == 1 || c->shape[0] == B) && c->shape[1] == T &&
+                        c->shape[2] == 1 && c->shape[3] == d / 2 && contiguous(c);
+      if (!fits) return shape_err(OP, "cos", c, "[1 | B, T, 1, head_dim/2]");
+      if (!same_shape(qo->rope_sin, c) || !contiguous(qo->rope_sin)) return shape_err(OP, "sin", qo->rope_sin, "the shape of cos");
+      if (c->dtype != x->dtype) return dtype_err(OP, "cos", c->dtype, x->dtype);
+      if (qo->rope_sin->dtype != x->dtype) return dtype_err(OP, "sin", qo->rope_sin->dtype, x->dtype);
+      qkv_per_batch = c->shape[0] != 1;
+    }
+  }
   if (rope) {
     const int hd = opts->rope_head_dim, nh = opts->rope_heads;
     if (x->rank != 3 || opts->gated) return shape_err(OP, "x", x, "[B, T, K] under a plain weight");
@@ -301,6 +357,7 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
       (opts->residual != nullptr && !rows_dense(opts->residual)))
     return fail(SVODB_ERR_GRAPH, "%s: operands must be dense rows (innermost stride 1)", OP);
   TRY(no_alias(OP, y, {x, w, opts->bias, opts->residual, opts->rope_cos, opts->rope_sin}));
+  if (qo != nullptr) TRY(no_alias(OP, y, {qo->q_norm, qo->k_norm, qo->rope_cos, qo->rope_sin}));
 
   GemmArgs a{};
   a.a = x->data;
@@ -339,16 +396,46 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
   }
   cudaStream_t s = (cudaStream_t)stream;
   char cfg[128];
+  if (qo != nullptr) {
+    // In the store when the tensor-core kernel covers it (dense y rows of 128-
+    // column heads); else a plain projection and the prologue over y in place.
+    GemmArgs f = a;
+    f.rope_head_dim = qo->head_dim;
+    f.rope_heads = qo->heads + qo->kv_heads;
+    if (qo->rope_cos != nullptr) {
+      f.rope_cos = qo->rope_cos->data;
+      f.rope_sin = qo->rope_sin->data;
+      f.rope_seq = qkv_per_batch ? a.m : x->shape[1];
+    }
+    f.norm_q = qo->q_norm ? qo->q_norm->data : nullptr;
+    f.norm_k = qo->k_norm ? qo->k_norm->data : nullptr;
+    f.norm_q_heads = qo->heads;
+    f.norm_k_heads = qo->kv_heads;
+    f.norm_eps = (float)qo->eps;
+    const bool any = f.rope_cos != nullptr || f.norm_q != nullptr || f.norm_k != nullptr;
+    if (any && gemm_tc_covers(f)) {
+      int rc = launch_gemm_tc(f, s, cfg, sizeof cfg);
+      if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+      if (rc == 0) {
+        chose_kernel(OP, "gemm", cfg);
+        return check_launch(OP);
+      }
+    }
+    if (any && !contiguous(y))
+      return fail(SVODB_ERR_GRAPH, "%s: the qkv prologue outside the kernel needs a contiguous y", OP);
+  }
   if (gemm_tc_covers(a)) {
     int rc = launch_gemm_tc(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
     if (rc == 0) {
       chose_kernel(OP, "gemm", cfg);
+      if (qo != nullptr) heads_in_place(qo, y, qkv_per_batch, s);
       return check_launch(OP);
     }
   }
   const char* why = !is_half(a.dtype) ? "dtype" : (n % 8 != 0 || k % 16 != 0) ? "shape" : "config";
   launch_gemm_generic(a, s);
+  if (qo != nullptr) heads_in_place(qo, y, qkv_per_batch, s);
   chose_graph(OP, why);
   return check_launch(OP);
 }

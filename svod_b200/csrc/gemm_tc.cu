@@ -48,7 +48,7 @@ struct Cfg {
   // (16 KiB, 128-byte swizzle) per column half of the tile.
   static constexpr int kStagingBytes = 2 * 128 * 128;
   static constexpr size_t kSmemBytes =
-      (size_t)kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+      (size_t)kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/ + 1024 /*head norm weights*/;
 };
 
 struct Params {
@@ -70,6 +70,15 @@ struct Params {
   int rope_head_dim;
   int64_t rope_seq;
   int tma_epilogue;   // stage the output through shared memory and TMA-store it
+  // Attention prologue in the store (the tile's column half is one 128-wide
+  // head): RMSNorm over the head with `norm_q` for columns below norm_q_cols,
+  // `norm_k` below norm_cols, none above; then the rotation for columns below
+  // rope_width; staged and TMA-stored like the plain epilogue.
+  int head_epilogue;
+  const void* norm_q;
+  const void* norm_k;
+  int norm_q_cols, norm_cols;
+  float norm_eps;
   uint32_t* status;
 };
 
@@ -191,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_empty = bars + 2 * S + 2;
   uint64_t* res_full = bars + 2 * S + 4;  // [2 halves]: residual sub-tile landed in staging
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+  float* head_w = reinterpret_cast<float*>(bars + 32);  // [2][128]: q and k head-norm weights as f32
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -217,6 +227,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
+  }
+  if (p.head_epilogue && threadIdx.x < 256) {
+    const T* wsrc = (const T*)(threadIdx.x < 128 ? p.norm_q : p.norm_k);
+    head_w[threadIdx.x] = wsrc != nullptr ? Elem<T>::to_f(wsrc[threadIdx.x & 127]) : 1.0f;
   }
   tc_fence_before();
   __syncthreads();
@@ -340,14 +354,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int64_t row = (int64_t)mt * BM + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       const int n0 = nt * p.out_bn;
+      const int cols = p.out_bn / 2;  // output columns this warp covers
+      const int c_lo = chalf * cols;
+      // Head epilogue: this row's rotation tables are requested before the wait
+      // for the accumulator, so their L2 latency passes while the tile's MMAs
+      // finish (the second half of each 128-byte table row then hits L1).
+      uint4 cs4[4], sn4[4];
+      const bool head_turned = p.head_epilogue && n0 + c_lo < p.rope_width;
+      const int64_t rope_pos = row_ok ? row % p.rope_seq : 0;
+      if (head_turned) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          cs4[v] = ldg128((const T*)p.rope_cos + rope_pos * 64 + v * 8);
+          sn4[v] = ldg128((const T*)p.rope_sin + rope_pos * 64 + v * 8);
+        }
+      }
       if (!mbar_wait(&acc_full[as], aph, p.status)) {
         ok = false;
         break;
       }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
-      const int cols = p.out_bn / 2;  // output columns this warp covers
-      const int c_lo = chalf * cols;
       if (p.tma_epilogue) {
         // Staged epilogue: each column half (4 warps, 128 rows) builds 64-column
         // sub-tiles in swizzled shared memory; one thread TMA-loads the residual
@@ -418,6 +445,132 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (!ok) break;
+      } else if (p.head_epilogue) {
+        // One 128-column head per column half. A first pass over the accumulator
+        // takes the sum of squares; the second forms both halves of the head at
+        // once (a rotated column needs its partner 64 columns away): the first
+        // half goes to the staging buffer, the second waits packed in registers
+        // until the first sub-tile's TMA store has read the buffer.
+        uint8_t* stg = staging + chalf * (128 * 128);
+        const bool chief = (ew & 3) == 0 && lane == 0;
+        const int r_tile = quarter * 32 + lane;
+        const int m0 = mt * BM;
+        const int h_col = n0 + c_lo;  // first output column of this head
+        const bool turned = head_turned;
+        const float* nw = h_col < p.norm_q_cols ? head_w : (h_col < p.norm_cols ? head_w + 128 : nullptr);
+        const T* cos = (const T*)p.rope_cos;
+        const T* sin = (const T*)p.rope_sin;
+        const int64_t pos = rope_pos;
+        const uint32_t t_head = t_acc + (uint32_t)c_lo;
+        float inv = 1.f;
+        if (nw != nullptr) {
+          float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld32(t_head + (uint32_t)c, r0);
+            tmem_ld32(t_head + (uint32_t)(c + 32), r1);
+            tmem_ld_wait();
+            if (bias != nullptr) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float b0[8], b1[8];
+                load8<T>(bias + h_col + c + v * 8, true, b0);
+                load8<T>(bias + h_col + c + 32 + v * 8, true, b1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  r0[v * 8 + i] = __float_as_uint(__uint_as_float(r0[v * 8 + i]) + b0[i]);
+                  r1[v * 8 + i] = __float_as_uint(__uint_as_float(r1[v * 8 + i]) + b1[i]);
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              ss0 = fmaf(__uint_as_float(r0[i]), __uint_as_float(r0[i]), ss0);
+              ss1 = fmaf(__uint_as_float(r1[i]), __uint_as_float(r1[i]), ss1);
+            }
+          }
+          inv = rsqrtf((ss0 + ss1) * (1.0f / 128.0f) + p.norm_eps);
+        }
+        // the previous store out of this buffer must have read it
+        if (chief) tma_store_wait_read();
+        named_barrier(1 + chalf, 128);
+        uint8_t* srow = stg + r_tile * 128;
+        uint32_t keep[32];  // second half of the head, packed
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t_head + (uint32_t)(32 * hc), ra);
+          tmem_ld32(t_head + (uint32_t)(64 + 32 * hc), rb);
+          if (turned && hc == 1) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              cs4[v] = ldg128(cos + pos * 64 + 32 + v * 8);
+              sn4[v] = ldg128(sin + pos * 64 + 32 + v * 8);
+            }
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              a[i] = __uint_as_float(ra[v * 8 + i]);
+              b[i] = __uint_as_float(rb[v * 8 + i]);
+            }
+            if (bias != nullptr) {
+              float b0[8], b1[8];
+              load8<T>(bias + h_col + 32 * hc + v * 8, true, b0);
+              load8<T>(bias + h_col + 64 + 32 * hc + v * 8, true, b1);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) a[i] += b0[i], b[i] += b1[i];
+            }
+            if (nw != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                a[i] = a[i] * inv * nw[32 * hc + v * 8 + i];
+                b[i] = b[i] * inv * nw[64 + 32 * hc + v * 8 + i];
+              }
+            }
+            if (turned) {
+              const uint32_t cu[4] = {cs4[v].x, cs4[v].y, cs4[v].z, cs4[v].w};
+              const uint32_t su[4] = {sn4[v].x, sn4[v].y, sn4[v].z, sn4[v].w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 c2 = Elem<T>::unpack(cu[i]), s2 = Elem<T>::unpack(su[i]);
+                const float a0 = a[2 * i], a1 = a[2 * i + 1], b0 = b[2 * i], b1 = b[2 * i + 1];
+                a[2 * i] = a0 * c2.x - b0 * s2.x;
+                b[2 * i] = a0 * s2.x + b0 * c2.x;
+                a[2 * i + 1] = a1 * c2.y - b1 * s2.y;
+                b[2 * i + 1] = a1 * s2.y + b1 * c2.y;
+              }
+            }
+            const int chunk = hc * 4 + v;  // 16-byte chunk of the 64-column sub-tile row
+            *reinterpret_cast<uint4*>(srow + ((chunk ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(a[0], a[1]), Elem<T>::pack(a[2], a[3]), Elem<T>::pack(a[4], a[5]),
+                           Elem<T>::pack(a[6], a[7]));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) keep[chunk * 4 + i] = Elem<T>::pack(b[2 * i], b[2 * i + 1]);
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier(1 + chalf, 128);
+        if (chief && h_col < p.n) {
+          tma_store_2d(&tmap_c, stg, h_col, m0);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        named_barrier(1 + chalf, 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4)) =
+              make_uint4(keep[c * 4], keep[c * 4 + 1], keep[c * 4 + 2], keep[c * 4 + 3]);
+        fence_proxy_async_smem();
+        named_barrier(1 + chalf, 128);
+        if (chief && h_col + 64 < p.n) {
+          tma_store_2d(&tmap_c, stg, h_col + 64, m0);
+          tma_store_commit();
+        }
       } else if (p.rope_width > 0 && n0 + c_lo < p.rope_width) {
         // In-store RoPE: whole heads, pairs (c, c + head_dim/2) from two chunks.
         const int hd = p.rope_head_dim, half = hd / 2;
@@ -477,7 +630,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
-  if (p.tma_epilogue && warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
+  if ((p.tma_epilogue || p.head_epilogue) && warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -501,9 +654,12 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
   if (!make_tmap_2d(&tw, a.w, dt, (uint64_t)a.k, w_rows, (uint64_t)a.ldw, BK, a.gated ? BN / 2 : BN)) return -1;
   // The staged epilogue needs whole 64-column sub-tiles per column half and
   // plain (non-rotating) stores; small tiles and RoPE keep the direct stores.
-  p.tma_epilogue = (p.out_bn >= 128 && a.rope_cos == nullptr) ? 1 : 0;
+  const bool per_head = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
+  p.tma_epilogue = (p.out_bn >= 128 && !per_head) ? 1 : 0;
+  // Heads of 128 columns are one column half of a 256-wide tile: staged too.
+  p.head_epilogue = (per_head && a.rope_head_dim == 128 && p.out_bn == 256) ? 1 : 0;
   CUtensorMap tc = ta, tr = ta;
-  if (p.tma_epilogue) {
+  if (p.tma_epilogue || p.head_epilogue) {
     if (!make_tmap_2d(&tc, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, BM)) return -1;
     tr = tc;
     if (a.residual != nullptr &&
@@ -569,6 +725,12 @@ bool gemm_tc_covers(const GemmArgs& a) {
     if (a.gated || a.act != kActNone || a.residual != nullptr || a.has_scale) return false;
     if (!aligned16(a.rope_cos) || !aligned16(a.rope_sin)) return false;
   }
+  if (a.norm_q != nullptr || a.norm_k != nullptr) {
+    // The per-head norm lives in the staged head epilogue: 128-column heads.
+    if (a.rope_head_dim != 128) return false;
+    if (a.gated || a.act != kActNone || a.residual != nullptr || a.has_scale) return false;
+    if ((a.norm_q != nullptr && !aligned16(a.norm_q)) || (a.norm_k != nullptr && !aligned16(a.norm_k))) return false;
+  }
   return true;
 }
 
@@ -591,7 +753,12 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len)
   p.rope_sin = a.rope_sin;
   p.rope_width = a.rope_cos != nullptr ? a.rope_heads * a.rope_head_dim : 0;
   p.rope_head_dim = a.rope_head_dim;
-  p.rope_seq = a.rope_seq;
+  p.rope_seq = a.rope_seq > 0 ? a.rope_seq : 1;
+  p.norm_q = a.norm_q;
+  p.norm_k = a.norm_k;
+  p.norm_q_cols = a.norm_q != nullptr ? a.norm_q_heads * a.rope_head_dim : 0;
+  p.norm_cols = a.norm_k != nullptr ? (a.norm_q_heads + a.norm_k_heads) * a.rope_head_dim : p.norm_q_cols;
+  p.norm_eps = a.norm_eps;
   p.status = a.status;
   const int sms = sm_count();
   // Tile width: the widest MMA whose tile count still fills the SMs. A gated
@@ -600,7 +767,8 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len)
   const int64_t tiles_m = (a.m + BM - 1) / BM;
   auto tiles = [&](int bn) { return tiles_m * ((a.n + (a.gated ? bn / 2 : bn) - 1) / (a.gated ? bn / 2 : bn)); };
   int bn = 256;
-  const int min_bn = a.gated ? 128 : (a.rope_cos != nullptr ? 2 * a.rope_head_dim : 64);
+  const bool per_head = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
+  const int min_bn = a.gated ? 128 : (per_head ? 2 * a.rope_head_dim : 64);
   while (bn > min_bn && tiles(bn) < sms) bn /= 2;
   if (bn < min_bn) bn = min_bn;
   if (bn > 256) return 1;

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(256)
     heads_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
                  const T* __restrict__ cos, const T* __restrict__ sin, T* __restrict__ q, T* __restrict__ k,
                  T* __restrict__ v, int64_t tokens, int64_t t_len, int heads, int kv_heads, float eps,
-                 int per_batch_tables) {
+                 int per_batch_tables, int in_place) {
   constexpr int D = LPH * 16;
   constexpr int HALF = D / 2;
   const int slots = heads + 2 * kv_heads;
@@ -90,7 +90,10 @@ __global__ void __launch_bounds__(256)
   }
   if (!live) return;
   T* dst;
-  if (which == 0) dst = q + (token * heads + slot) * D;
+  // In place: the head goes back where it came from (every element is read by
+  // the one thread that rewrites it, before it does).
+  if (in_place) dst = const_cast<T*>(src);
+  else if (which == 0) dst = q + (token * heads + slot) * D;
   else if (which == 1) dst = k + (token * kv_heads + (slot - heads)) * D;
   else dst = v + (token * kv_heads + (slot - heads - kv_heads)) * D;
   stg128(dst + sub * 8, pack8<T>(x1));
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(128)
     heads_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
                          const T* __restrict__ cos, const T* __restrict__ sin, T* __restrict__ q, T* __restrict__ k,
                          T* __restrict__ v, int64_t tokens, int64_t t_len, int heads, int kv_heads, int d, float eps,
-                         int per_batch_tables) {
+                         int per_batch_tables, int in_place) {
   const int slots = heads + 2 * kv_heads;
   const int64_t head_row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (head_row >= tokens * slots) return;
@@ -125,7 +128,8 @@ __global__ void __launch_bounds__(128)
     inv = rsqrtf(warp_sum(sq) / d + eps);
   }
   T* dst;
-  if (which == 0) dst = q + (token * heads + slot) * d;
+  if (in_place) dst = const_cast<T*>(src);
+  else if (which == 0) dst = q + (token * heads + slot) * d;
   else if (which == 1) dst = k + (token * kv_heads + (slot - heads)) * d;
   else dst = v + (token * kv_heads + (slot - heads - kv_heads)) * d;
   const int64_t trow = per_batch_tables ? token : token % t_len;
@@ -152,7 +156,7 @@ void run(const HeadsArgs& a, cudaStream_t s) {
   const unsigned blocks = (unsigned)((threads + 255) / 256);
   heads_kernel<T, LPH><<<blocks, 256, 0, s>>>((const T*)a.qkv, (const T*)a.q_w, (const T*)a.k_w, (const T*)a.cos,
                                               (const T*)a.sin, (T*)a.q, (T*)a.k, (T*)a.v, tokens, a.t, a.heads,
-                                              a.kv_heads, a.eps, a.per_batch_tables);
+                                              a.kv_heads, a.eps, a.per_batch_tables, a.in_place);
 }
 
 template <typename T>
@@ -173,7 +177,7 @@ void run_generic(const HeadsArgs& a, cudaStream_t s) {
   const int64_t head_rows = tokens * (a.heads + 2 * a.kv_heads);
   heads_generic_kernel<T><<<(unsigned)((head_rows + 3) / 4), 128, 0, s>>>(
       (const T*)a.qkv, (const T*)a.q_w, (const T*)a.k_w, (const T*)a.cos, (const T*)a.sin, (T*)a.q, (T*)a.k, (T*)a.v,
-      tokens, a.t, a.heads, a.kv_heads, a.d, a.eps, a.per_batch_tables);
+      tokens, a.t, a.heads, a.kv_heads, a.d, a.eps, a.per_batch_tables, a.in_place);
 }
 
 }  // namespace

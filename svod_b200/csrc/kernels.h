@@ -40,6 +40,7 @@ struct HeadsArgs {
   float eps;
   int per_batch_tables;
   int dtype;
+  int in_place;  // write each head back where it was read (q, k, v unused)
 };
 int launch_heads(const HeadsArgs& a, cudaStream_t s);
 
@@ -148,6 +149,13 @@ struct GemmArgs {
   const void* rope_sin;
   int rope_heads, rope_head_dim;
   int64_t rope_seq;
+  // Per-head RMSNorm in the store (tensor-core path only): weight [head_dim] for
+  // the first norm_q_heads heads, another for the next norm_k_heads; the head
+  // size is rope_head_dim. Nullable.
+  const void* norm_q;
+  const void* norm_k;
+  int norm_q_heads, norm_k_heads;
+  float norm_eps;
   int dtype;
   uint32_t* status;
 };

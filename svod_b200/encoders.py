@@ -129,9 +129,10 @@ class XlmRobertaEncoder:
 
 # --------------------------------------------------------------------------- Qwen3
 class Qwen3Embedder:
-    def __init__(self, cfg: Qwen3Config, params: Dict):
+    def __init__(self, cfg: Qwen3Config, params: Dict, fused_prologue: bool = True):
         self.cfg, self.p = cfg, params
         self._rope = {}
+        self.fused_prologue = fused_prologue
 
     @staticmethod
     def random_init(cfg: Qwen3Config, seed: int = 0, device="cuda") -> "Qwen3Embedder":
@@ -162,9 +163,16 @@ class Qwen3Embedder:
         rope = rope or self.rope(L, x.device)
         for lp in p["layers"]:
             xn = ops.rms_norm(x, lp["in_w"], c.rms_norm_eps)
-            qkv = ops.linear(xn, lp["qkv_w"])
-            q, k, v = ops.heads(qkv, Qkv(H, Hkv, hd, lp["qn_w"], lp["kn_w"], c.rms_norm_eps, rope))
-            a = ops.attention(q, k, v, Attn(causal=True, seg_start=seg_start)).view(B, L, H * hd)
+            prologue = Qkv(H, Hkv, hd, lp["qn_w"], lp["kn_w"], c.rms_norm_eps, rope)
+            if self.fused_prologue:
+                # q/k norm and rotation in the projection's store; attention reads
+                # the packed projection in place (no q, k, v copies).
+                qkv = ops.linear(xn, lp["qkv_w"], Linear(qkv=prologue))
+                a = ops.attention_packed(qkv, H, Hkv, Attn(causal=True, seg_start=seg_start)).view(B, L, H * hd)
+            else:
+                # the reference's op sequence (model/src/qwen3/attention.rs:69-113)
+                q, k, v = ops.heads(ops.linear(xn, lp["qkv_w"]), prologue)
+                a = ops.attention(q, k, v, Attn(causal=True, seg_start=seg_start)).view(B, L, H * hd)
             h = ops.linear(a, lp["o_w"], Linear(residual=x))
             hn = ops.rms_norm(h, lp["post_w"], c.rms_norm_eps)
             g = ops.linear(hn, lp["gu_w"], Linear(act=Act.SILU, gated=True))

@@ -64,6 +64,10 @@ class Linear:
     scale: Optional[float] = None
     rope: Optional[Rotary] = None
     into: Optional[Tuple[torch.Tensor, int]] = None
+    # Not in the reference's `Linear`: the `ops::heads` prologue (per-head RMSNorm
+    # of q and k, rotation) applied in this projection's store; the result stays
+    # the packed `[B, T, (H + 2*Hkv)*D]` projection for `attention_packed`.
+    qkv: Optional["Qkv"] = None
 
 
 @dataclass
@@ -215,6 +219,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, opts: Optional[Linear] = None) -> t
         o.rope_heads = opts.rope.heads
         o.rope_head_dim = opts.rope.head_dim
     o.into_at = opts.into[1] if opts.into else 0
+    if opts.qkv is not None:
+        qo = _qkv_opts(opts.qkv, keep)
+        keep.append(qo)
+        o.qkv = C.cast(C.pointer(qo), C.c_void_p)
     xd, wd, yd = _desc(x), _desc(w), _desc(y)
     _check(lib.svodb_linear(_p(xd), _p(wd), C.byref(o), _p(yd), _stream()))
     return opts.into[0] if opts.into is not None else y
@@ -311,6 +319,21 @@ def combine_splits(o_part: torch.Tensor, m_part: torch.Tensor, l_part: torch.Ten
 
 
 # ---------------------------------------------------------------------------- heads
+def _qkv_opts(opts: Qkv, keep: list):
+    o = L.QkvOpts()
+    o.heads, o.kv_heads, o.head_dim, o.eps = opts.heads, opts.kv_heads, opts.head_dim, float(opts.eps)
+    descs = [_desc(opts.q_norm), _desc(opts.k_norm),
+             _desc(opts.rope[0]) if opts.rope else None, _desc(opts.rope[1]) if opts.rope else None]
+    keep.extend(descs)
+    if descs[0] is not None:
+        o.q_norm = C.pointer(descs[0])
+    if descs[1] is not None:
+        o.k_norm = C.pointer(descs[1])
+    if opts.rope:
+        o.rope_cos, o.rope_sin = C.pointer(descs[2]), C.pointer(descs[3])
+    return o
+
+
 def heads(qkv: torch.Tensor, opts: Qkv):
     """`ops::heads` (tk/src/ops/heads.rs:37-102): `(q, k, v)`."""
     if qkv.dim() != 3:
@@ -318,16 +341,8 @@ def heads(qkv: torch.Tensor, opts: Qkv):
     B, T = qkv.shape[:2]
     mk = lambda h: torch.empty(B, T, h, opts.head_dim, dtype=qkv.dtype, device=qkv.device)
     q, k, v = mk(opts.heads), mk(opts.kv_heads), mk(opts.kv_heads)
-    o = L.QkvOpts()
-    o.heads, o.kv_heads, o.head_dim, o.eps = opts.heads, opts.kv_heads, opts.head_dim, float(opts.eps)
-    keep = [_desc(opts.q_norm), _desc(opts.k_norm),
-            _desc(opts.rope[0]) if opts.rope else None, _desc(opts.rope[1]) if opts.rope else None]
-    if keep[0] is not None:
-        o.q_norm = C.pointer(keep[0])
-    if keep[1] is not None:
-        o.k_norm = C.pointer(keep[1])
-    if opts.rope:
-        o.rope_cos, o.rope_sin = C.pointer(keep[2]), C.pointer(keep[3])
+    keep: list = []
+    o = _qkv_opts(opts, keep)
     xd, qd, kd, vd = _desc(qkv), _desc(q), _desc(k), _desc(v)
     _check(L.load().svodb_heads(_p(xd), C.byref(o), _p(qd), _p(kd), _p(vd), _stream()))
     return q, k, v

@@ -144,3 +144,59 @@ def test_full_size_gemm_is_linear_in_its_input():
     rows = torch.tensor([0, 777, 32767], device="cuda")
     ref = x[rows].float() @ w.float().t()
     assert float((y1[rows].float() - ref).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("dt,B,T,k,H,Hkv,hd,qn,kn,rope,kernel", [
+    (O.BF16, 2, 200, 256, 4, 2, 128, True, True, "shared", True),     # Qwen3's layout: in the store
+    (O.BF16, 2, 130, 128, 2, 1, 128, True, False, "per_batch", True),  # per-row tables, no k norm
+    (O.F16, 1, 77, 128, 2, 2, 128, False, False, "shared", True),      # rotation only
+    (O.BF16, 1, 64, 128, 2, 2, 128, True, True, None, True),           # norm only
+    (O.F16, 2, 50, 128, 4, 2, 64, True, True, "shared", False),        # 64-wide heads: projection, then in place
+    (O.F32, 1, 9, 40, 2, 1, 16, True, True, "shared", False),          # f32: exact projection, then in place
+])
+def test_qkv_prologue_in_the_projection_store(dt, B, T, k, H, Hkv, hd, qn, kn, rope, kernel):
+    """`Linear(qkv=...)`: the `ops::heads` prologue applied to the projection's
+    accumulator; the packed result equals `heads(linear(x, w))` laid back side
+    by side (the oracle rounds between the two ops, the fused store does not:
+    the tolerance of the heads recipe covers it)."""
+    rng = np.random.default_rng(B * 1000 + T)
+    n = (H + 2 * Hkv) * hd
+    x = O.round_to(dt, rng.standard_normal((B, T, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    qw = O.round_to(dt, 1 + 0.2 * rng.standard_normal(hd)) if qn else None
+    kw = O.round_to(dt, 1 + 0.2 * rng.standard_normal(hd)) if kn else None
+    cos = sin = None
+    if rope == "shared":
+        cos, sin = O.rope_table(1e6, np.arange(T), hd, dt)
+    elif rope == "per_batch":
+        pos = np.stack([(np.arange(T) * (b + 2)) % 97 for b in range(B)])
+        cos, sin = O.rope_table(1e6, pos.reshape(-1), hd, dt)
+        cos, sin = cos.reshape(B, T, hd // 2), sin.reshape(B, T, hd // 2)
+    q, kk, v = O.heads(O.linear(x, w, dtype=dt), H, Hkv, hd, qw, kw, 1e-6, cos, sin, dt)
+    want = np.concatenate([q.reshape(B, T, -1), kk.reshape(B, T, -1), v.reshape(B, T, -1)], axis=-1)
+    tabs = None
+    if cos is not None:
+        tabs = (dev(cos, dt).view(-1, T, 1, hd // 2), dev(sin, dt).view(-1, T, 1, hd // 2))
+    o = ops.Linear(qkv=ops.Qkv(H, Hkv, hd, dev(qw, dt) if qn else None, dev(kw, dt) if kn else None, 1e-6, tabs))
+    got = host(ops.linear(dev(x, dt), dev(w, dt), o))
+    assert ("kernel gemm" in ops.chosen()) == (dt != O.F32)
+    tol = 1e-4 if dt == O.F32 else 2e-2
+    assert rel_close(got, want, 1e-3 if dt == O.F32 else 2e-2)
+    assert mean_rel(got, want) < (1e-5 if dt == O.F32 else 5e-3)
+    assert rel_close(got[..., (H + Hkv) * hd:], want[..., (H + Hkv) * hd:], tol)  # v: the plain projection
+    # attention reads the packed projection in place
+    a = host(ops.attention_packed(dev(got, dt), H, Hkv, ops.Attn(causal=True)))
+    a_want = O.attention(q, kk, v, causal=True, dtype=dt)
+    assert max_abs(a, a_want) < (1e-3 if dt == O.F32 else 2e-2)
+
+
+def test_qkv_prologue_excludes_the_other_epilogues():
+    dt = O.BF16
+    x, w = dev(np.zeros((1, 8, 64)), dt), dev(np.zeros((4 * 64, 64)), dt)
+    for bad in (dict(gated=True), dict(act=ops.Act.SILU), dict(scale=2.0), dict(residual=dev(np.zeros((1, 8, 256)), dt))):
+        with pytest.raises(ops.OpsError) as e:
+            ops.linear(x, w, ops.Linear(qkv=ops.Qkv(2, 1, 64), **bad))
+        assert e.value.kind in ("Graph", "Shape")
+    with pytest.raises(ops.OpsError) as e:
+        ops.linear(x, w, ops.Linear(qkv=ops.Qkv(3, 1, 64)))
+    assert e.value.kind == "Shape"
