@@ -80,6 +80,19 @@ int svodb_supported(int device);
  * "attention: graph dtype" (generic kernel and why). */
 const char* svodb_last_chosen(void);
 
+/* Shape-keyed config choice, the seam of a tune store (tk/src/tune.rs: a
+ * measured config per shape, kept in the process and on disk). The library keeps
+ * the process map; the host owns measurement and the file.
+ * `svodb_last_config_key`: the key of the last `svodb_linear` on this thread that
+ * reached the tensor-core kernel, "gemm|<dtype>|<m>|<n>|<k>|<epilogue>" ("" when
+ * none did). `svodb_config_set(key, bn)`: later calls with that key use tile
+ * width bn (64, 128 or 256; a width the epilogue cannot take is ignored);
+ * bn = 0 forgets the key. `svodb_config_get` returns 0 when the key is unset. */
+const char* svodb_last_config_key(void);
+int svodb_config_set(const char* key, int32_t value);
+int32_t svodb_config_get(const char* key);
+void svodb_config_clear(void);
+
 /* Reads and clears the device status word bounded waits report into
  * (0 = ok). Synchronises `stream`. Returns SVODB_ERR_TIMEOUT when a wait ran
  * out since the last call. */
@@ -135,6 +148,19 @@ typedef struct svodb_attn_opts {
   svodb_tensor* lse;            /* optional out: [B,H,T] f32, ln-sum-exp of the masked scaled scores */
   void* workspace;              /* device scratch for key splits (f32 partials) */
   size_t workspace_bytes;
+  /* `ops::Cache` (tk/src/ops/attention.rs:39-55): k and v are caches
+   * [rows, Tk, H_all, D] holding several layers' heads; this attention reads
+   * heads [head_start, head_start + kv_heads) of cache row row_map[b] (row b
+   * without a map), then the appended keys. The masks apply to cached keys; an
+   * appended key is hidden only past app_lens[b]. */
+  int32_t has_cache;
+  int32_t cache_head_start;
+  int32_t cache_kv_heads;
+  const svodb_tensor* cache_row_map;  /* [B] i32 or NULL */
+  const svodb_tensor* cache_app_k;    /* [B, n, kv_heads, D] keys scored after the cached prefix
+                                         (needs key_lens), or NULL */
+  const svodb_tensor* cache_app_v;
+  const svodb_tensor* cache_app_lens; /* [B] i32 visible appended rows, or NULL = all */
 } svodb_attn_opts;
 
 /* Bytes of `workspace` a split attention of this shape needs

@@ -299,7 +299,7 @@ def linear(x, w, bias=None, act=ACT_NONE, gated=False, residual=None, scale=None
 
 
 def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=None, chunk=None,
-              seg_start=None, scale=None, bias=None, dtype=BF16, return_lse=False):
+              seg_start=None, scale=None, bias=None, dtype=BF16, return_lse=False, cache=None):
     """`softmax(q.k^T*scale + bias) . v` over `q [B,T,H,D]`, `k,v [B,Tk,Hkv,D]`.
 
     Masks apply together: causal `j<=i`; `j < key_lens[b]`; window
@@ -311,10 +311,34 @@ def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=Non
     `lse[b,h,i] = max + ln(sum exp(s - max))` of the masked scaled scores
     (`-inf` for an empty row): the natural-log form of the `(m, l)` statistics
     the reference keeps in log2 units (kernels/attention.rs:910-920).
+
+    `cache = dict(head_start, kv_heads, row_map=None, k_app=None, v_app=None,
+    app_lens=None)` (`ops::Cache`, tk/src/ops/attention.rs:39-55; graph at
+    :496-535): `k, v` are `[rows, Tk, H_all, D]`; this attention reads heads
+    `head_start .. head_start+kv_heads` of cache row `row_map[b]` (row `b`
+    without a map), then the appended `[B, n, kv_heads, D]` keys. The masks
+    above apply to the cached keys only; an appended key is hidden only past
+    `app_lens[b]` (tk/src/test/unit/attention.rs:112-135). `bias` spans
+    `Tk + n` columns, the appended ones last.
     """
     q = np.asarray(q, dtype=np.float64)
     k = np.asarray(k, dtype=np.float64)
     v = np.asarray(v, dtype=np.float64)
+    n_app = 0
+    cached_keys = k.shape[1]
+    if cache is not None:
+        hs, kvh = cache["head_start"], cache["kv_heads"]
+        k, v = k[:, :, hs:hs + kvh], v[:, :, hs:hs + kvh]
+        if cache.get("row_map") is not None:
+            rm = np.asarray(cache["row_map"]).astype(np.int64)
+            k, v = k[rm], v[rm]
+        else:
+            k, v = k[:q.shape[0]], v[:q.shape[0]]  # lane b reads row b
+        if cache.get("k_app") is not None:
+            ka = np.asarray(cache["k_app"], dtype=np.float64)
+            va = np.asarray(cache["v_app"], dtype=np.float64)
+            n_app = ka.shape[1]
+            k, v = np.concatenate([k, ka], axis=1), np.concatenate([v, va], axis=1)
     B, T, H, D = q.shape
     _, Tk, Hkv, _ = k.shape
     group = H // Hkv
@@ -345,9 +369,16 @@ def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=Non
         if left is not None:
             hidden |= (j // size + left) < (i // size)
     if key_mask is not None:
-        hidden |= (np.asarray(key_mask).reshape(B, 1, 1, Tk) == 0)
+        km = np.asarray(key_mask).reshape(B, 1, 1, cached_keys) == 0
+        if n_app:
+            km = np.concatenate([km, np.zeros((B, 1, 1, n_app), dtype=bool)], axis=-1)
+        hidden |= km
     if seg_start is not None:
         hidden |= j < np.asarray(seg_start).reshape(B, 1, T, 1)
+    if n_app:
+        # appended keys answer to their own count alone
+        seen = np.full(B, n_app) if cache.get("app_lens") is None else np.asarray(cache["app_lens"])
+        hidden = np.where(j >= cached_keys, (j - cached_keys) >= seen.reshape(B, 1, 1, 1), hidden)
     s = np.where(hidden, -np.inf, s)
     mx = s.max(axis=-1, keepdims=True)
     empty = ~np.isfinite(mx)

@@ -74,6 +74,13 @@ class AttnOpts(C.Structure):
         ("lse", TensorP),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("has_cache", C.c_int32),
+        ("cache_head_start", C.c_int32),
+        ("cache_kv_heads", C.c_int32),
+        ("cache_row_map", TensorP),
+        ("cache_app_k", TensorP),
+        ("cache_app_v", TensorP),
+        ("cache_app_lens", TensorP),
     ]
 
 
@@ -100,6 +107,10 @@ SYMBOLS = [
     ("svodb_last_error", C.c_char_p, []),
     ("svodb_supported", C.c_int, [C.c_int]),
     ("svodb_last_chosen", C.c_char_p, []),
+    ("svodb_last_config_key", C.c_char_p, []),
+    ("svodb_config_set", C.c_int, [C.c_char_p, C.c_int32]),
+    ("svodb_config_get", C.c_int32, [C.c_char_p]),
+    ("svodb_config_clear", None, []),
     ("svodb_device_status", C.c_int, [C.c_void_p]),
     ("svodb_linear", C.c_int, [TensorP, TensorP, C.POINTER(LinearOpts), TensorP, C.c_void_p]),
     ("svodb_attention_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),

@@ -11,6 +11,8 @@
 #include <string.h>
 
 #include <mutex>
+#include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "kernels.h"
@@ -214,6 +216,37 @@ const char* svodb_version(void) { return "svodb 0.1 (sm_100a)"; }
 const char* svodb_last_error(void) { return g_error; }
 const char* svodb_last_chosen(void) { return g_chosen; }
 
+// ---------------------------------------------------------------------------
+// shape-keyed configs (the process half of a tune store)
+// ---------------------------------------------------------------------------
+namespace {
+thread_local char g_config_key[160] = "";
+std::mutex g_config_mutex;
+std::unordered_map<std::string, int32_t>& config_map() {
+  static std::unordered_map<std::string, int32_t> m;
+  return m;
+}
+int32_t config_lookup(const char* key) {
+  std::lock_guard<std::mutex> lock(g_config_mutex);
+  auto it = config_map().find(key);
+  return it == config_map().end() ? 0 : it->second;
+}
+}  // namespace
+
+const char* svodb_last_config_key(void) { return g_config_key; }
+int svodb_config_set(const char* key, int32_t value) {
+  if (key == nullptr || key[0] == 0) return fail(SVODB_ERR_GRAPH, "config: an empty key");
+  std::lock_guard<std::mutex> lock(g_config_mutex);
+  if (value == 0) config_map().erase(key);
+  else config_map()[key] = value;
+  return SVODB_OK;
+}
+int32_t svodb_config_get(const char* key) { return key == nullptr ? 0 : config_lookup(key); }
+void svodb_config_clear(void) {
+  std::lock_guard<std::mutex> lock(g_config_mutex);
+  config_map().clear();
+}
+
 int svodb_supported(int device) {
   int major = 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
@@ -396,6 +429,16 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
   }
   cudaStream_t s = (cudaStream_t)stream;
   char cfg[128];
+  // The config store's key of this call and the tile width it holds for it.
+  g_config_key[0] = 0;
+  {
+    const char* epi = qo != nullptr ? "qkv" : rope ? "rope" : opts->gated ? "gated" : "plain";
+    char key[160];
+    snprintf(key, sizeof key, "gemm|%s|%lld|%lld|%lld|%s%s%s", dtype_name(x->dtype), (long long)a.m, (long long)n,
+             (long long)k, epi, opts->residual != nullptr ? "+res" : "", opts->act != SVODB_ACT_NONE ? "+act" : "");
+    a.force_bn = config_lookup(key);
+    if (gemm_tc_covers(a)) snprintf(g_config_key, sizeof g_config_key, "%s", key);
+  }
   if (qo != nullptr) {
     // In the store when the tensor-core kernel covers it (dense y rows of 128-
     // column heads); else a plain projection and the prologue over y in place.
@@ -450,17 +493,54 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
   svodb_attn_opts none{};
   if (opts == nullptr) opts = &none;
   if (q->rank != 4) return shape_err(OP, "q", q, "[B, T, H, D]");
-  if (!(k->rank == 4 && k->shape[0] == q->shape[0] && k->shape[3] == q->shape[3]))
-    return shape_err(OP, "k", k, "[B, Tk, H_kv, D]");
+  const bool cached = opts->has_cache != 0;
+  const bool mapped = cached && opts->cache_row_map != nullptr;
+  if (cached && packed) return fail(SVODB_ERR_GRAPH, "%s: a packed projection is not a cache", OP);
+  if (!(k->rank == 4 && (k->shape[0] == q->shape[0] || mapped) && k->shape[3] == q->shape[3]))
+    return shape_err(OP, "k", k, mapped ? "[rows, Tk, H_kv, D]" : "[B, Tk, H_kv, D]");
   if (!same_shape(v, k)) return shape_err(OP, "v", v, "the shape of k");
   if (!is_float(q->dtype)) return fail(SVODB_ERR_GRAPH, "%s: q is %s, not a float type", OP, dtype_name(q->dtype));
   if (k->dtype != q->dtype) return dtype_err(OP, "k", k->dtype, q->dtype);
   if (v->dtype != q->dtype) return dtype_err(OP, "v", v->dtype, q->dtype);
   const int64_t B = q->shape[0], T = q->shape[1], H = q->shape[2], D = q->shape[3];
-  const int64_t Tk = k->shape[1], Hkv = k->shape[2];
+  const int64_t Tk = k->shape[1], Hkv = cached ? opts->cache_kv_heads : k->shape[2];
   if (!(Hkv > 0 && H % Hkv == 0))
     return fail(SVODB_ERR_HEADS, "%s: %lld query heads are not a multiple of %lld key/value heads", OP, (long long)H,
                 (long long)Hkv);
+  // `ops::Cache` (tk/src/ops/attention.rs:148-170)
+  int64_t n_app = 0;
+  if (cached) {
+    if (opts->cache_head_start < 0 || opts->cache_head_start + Hkv > k->shape[2])
+      return shape_err(OP, "k", k, "[rows, Tk, >= head_start + kv_heads, D]");
+    if (mapped) {
+      TRY(realized(OP, "row map", opts->cache_row_map));
+      const svodb_tensor* m = opts->cache_row_map;
+      if (m->rank != 1 || m->shape[0] != B) return shape_err(OP, "row map", m, "[B]");
+      if (m->dtype != SVODB_I32) return dtype_err(OP, "row map", m->dtype, SVODB_I32);
+    }
+    if ((opts->cache_app_k != nullptr) != (opts->cache_app_v != nullptr))
+      return fail(SVODB_ERR_GRAPH, "%s: appended keys and values come together", OP);
+    if (opts->cache_app_k != nullptr) {
+      const svodb_tensor* ap[2] = {opts->cache_app_k, opts->cache_app_v};
+      const char* names[2] = {"appended k", "appended v"};
+      for (int i = 0; i < 2; ++i) {
+        TRY(realized(OP, names[i], ap[i]));
+        const svodb_tensor* t = ap[i];
+        const bool fits = t->rank == 4 && t->shape[0] == B && t->shape[1] > 0 && t->shape[1] == ap[0]->shape[1] &&
+                          t->shape[2] == Hkv && t->shape[3] == D && contiguous(t);
+        if (!fits) return shape_err(OP, names[i], t, "[B, n, kv_heads, D]");
+        if (t->dtype != q->dtype) return dtype_err(OP, names[i], t->dtype, q->dtype);
+      }
+      if (opts->key_lens == nullptr) return fail(SVODB_ERR_SHAPE, "%s: key lens has shape [], expected [B] with appended rows", OP);
+      n_app = opts->cache_app_k->shape[1];
+    }
+    if (opts->cache_app_lens != nullptr) {
+      TRY(realized(OP, "appended lens", opts->cache_app_lens));
+      const svodb_tensor* t = opts->cache_app_lens;
+      if (n_app == 0 || t->rank != 1 || t->shape[0] != B) return shape_err(OP, "appended lens", t, "[B] with appended rows");
+      if (t->dtype != SVODB_I32) return dtype_err(OP, "appended lens", t->dtype, SVODB_I32);
+    }
+  }
   if (opts->key_lens != nullptr && opts->key_mask != nullptr)
     return fail(SVODB_ERR_GRAPH, "%s: key lengths and a key mask are alternatives (KeyMask)", OP);
   if (opts->key_lens != nullptr) {
@@ -487,8 +567,8 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
     TRY(realized(OP, "bias", opts->bias));
     const svodb_tensor* bs = opts->bias;
     const bool fits = bs->rank == 4 && (bs->shape[0] == B || bs->shape[0] == 1) && bs->shape[1] == H &&
-                      bs->shape[2] == T && bs->shape[3] == Tk && contiguous(bs);
-    if (!fits) return shape_err(OP, "bias", bs, "[B | 1, H, T, Tk]");
+                      bs->shape[2] == T && bs->shape[3] == Tk + n_app && contiguous(bs);
+    if (!fits) return shape_err(OP, "bias", bs, "[B | 1, H, T, Tk (+ appended)]");
     if (bs->dtype != q->dtype) return dtype_err(OP, "bias", bs->dtype, q->dtype);
     bias_per_batch = bs->shape[0] != 1 || B == 1;
   }
@@ -510,6 +590,19 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
 
   AttnArgs a{};
   a.q = q->data, a.k = k->data, a.v = v->data, a.o = o->data;
+  a.kv_rows = k->shape[0];
+  if (cached) {
+    // the first head this attention reads
+    a.k = (const char*)k->data + (size_t)opts->cache_head_start * k->stride[2] * esize(k->dtype);
+    a.v = (const char*)v->data + (size_t)opts->cache_head_start * v->stride[2] * esize(v->dtype);
+    a.row_map = mapped ? (const int32_t*)opts->cache_row_map->data : nullptr;
+    if (n_app > 0) {
+      a.k_app = opts->cache_app_k->data;
+      a.v_app = opts->cache_app_v->data;
+      a.n_app = (int)n_app;
+      a.app_lens = opts->cache_app_lens ? (const int32_t*)opts->cache_app_lens->data : nullptr;
+    }
+  }
   a.q_sb = q->stride[0], a.q_st = q->stride[1], a.q_sh = q->stride[2];
   a.k_sb = k->stride[0], a.k_st = k->stride[1], a.k_sh = k->stride[2];
   a.v_sb = v->stride[0], a.v_st = v->stride[1], a.v_sh = v->stride[2];
@@ -538,7 +631,7 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
     return SVODB_OK;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  if (Tk == 0) {
+  if (Tk + n_app == 0) {
     // No key at all: every row attends to nothing (zeros), as the graph writes it.
     for (int64_t b = 0; b < B; ++b)
       for (int64_t t = 0; t < T; ++t)
@@ -548,7 +641,7 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
     return check_launch(OP);
   }
   if (a.splits > 1) {
-    const int64_t tiles = (Tk + 31) / 32;
+    const int64_t tiles = (Tk + n_app + 31) / 32;
     if (a.splits > tiles) a.splits = (int)tiles;  // capped at the key block count
   }
   if (a.splits > 1) {

@@ -65,8 +65,15 @@ __global__ void __launch_bounds__(256) attention_generic_kernel(const AttnArgs a
   const int hk = h / (a.heads / a.kv_heads);
   const int64_t i0 = qt * BQ;
   const T* q = (const T*)a.q + b * a.q_sb + h * a.q_sh;
-  const T* k = (const T*)a.k + b * a.k_sb + hk * a.k_sh;
-  const T* v = (const T*)a.v + b * a.v_sb + hk * a.v_sh;
+  // `ops::Cache`: lane b reads cache row row_map[b]; keys tk .. tk+n_app-1 are
+  // the appended rows, hidden only past app_lens[b].
+  const int64_t kv_row = a.row_map != nullptr ? (int64_t)a.row_map[b] : b;
+  const T* k = (const T*)a.k + kv_row * a.k_sb + hk * a.k_sh;
+  const T* v = (const T*)a.v + kv_row * a.v_sb + hk * a.v_sh;
+  const int64_t keys = a.tk + a.n_app;
+  const T* k_app = a.n_app > 0 ? (const T*)a.k_app + (b * a.n_app * a.kv_heads + hk) * (int64_t)a.d : nullptr;
+  const T* v_app = a.n_app > 0 ? (const T*)a.v_app + (b * a.n_app * a.kv_heads + hk) * (int64_t)a.d : nullptr;
+  const int64_t app_seen = a.app_lens != nullptr ? (int64_t)a.app_lens[b] : a.n_app;
   const float sc = a.scale * kLog2e;
   int64_t len = a.tk;
   if (a.key_lens != nullptr) {
@@ -90,7 +97,7 @@ __global__ void __launch_bounds__(256) attention_generic_kernel(const AttnArgs a
   for (int c = 0; c < 32; ++c) oacc[c] = 0.f;
 
   // This split's share of the key tiles.
-  const int64_t tiles = (a.tk + BKV - 1) / BKV;
+  const int64_t tiles = (keys + BKV - 1) / BKV;
   const int64_t per = (tiles + splits - 1) / splits;
   const int64_t tile_lo = split * per;
   const int64_t tile_hi = tile_lo + per < tiles ? tile_lo + per : tiles;
@@ -101,9 +108,17 @@ __global__ void __launch_bounds__(256) attention_generic_kernel(const AttnArgs a
     for (int e = tid; e < BKV * D; e += 256) {
       const int r = e / D, c = e % D;
       const int64_t j = j0 + r;
-      const bool in = j < a.tk;
-      Ks[r * DP + c] = in ? Elem<T>::to_f(k[j * a.k_st + c]) : 0.f;
-      Vs[r * D + c] = in ? Elem<T>::to_f(v[j * a.v_st + c]) : 0.f;
+      float kf = 0.f, vf = 0.f;
+      if (j < a.tk) {
+        kf = Elem<T>::to_f(k[j * a.k_st + c]);
+        vf = Elem<T>::to_f(v[j * a.v_st + c]);
+      } else if (j < keys) {
+        const int64_t at = (j - a.tk) * a.kv_heads * D + c;
+        kf = Elem<T>::to_f(k_app[at]);
+        vf = Elem<T>::to_f(v_app[at]);
+      }
+      Ks[r * DP + c] = kf;
+      Vs[r * D + c] = vf;
     }
     __syncthreads();
     // Scores: thread -> row tid/8, keys (tid%8) + 8*jj.
@@ -115,13 +130,14 @@ __global__ void __launch_bounds__(256) attention_generic_kernel(const AttnArgs a
         const int c = (tid & 7) + 8 * jj;
         const int64_t j = j0 + c;
         float s = -INFINITY;
-        if (i < a.t && j < a.tk && !key_hidden(a, b, i, j, len)) {
+        const bool visible = j < a.tk ? !key_hidden(a, b, i, j, len) : (j < keys && j - a.tk < app_seen);
+        if (i < a.t && visible) {
           float dot = 0.f;
           for (int dd = 0; dd < D; ++dd) dot = fmaf(Qs[r * DP + dd], Ks[c * DP + dd], dot);
           s = dot * sc;
           if (a.bias != nullptr) {
             const int64_t bb = a.bias_per_batch ? b : 0;
-            s = fmaf(Elem<T>::to_f(((const T*)a.bias)[((bb * a.heads + h) * a.t + i) * a.tk + j]), kLog2e, s);
+            s = fmaf(Elem<T>::to_f(((const T*)a.bias)[((bb * a.heads + h) * a.t + i) * keys + j]), kLog2e, s);
           }
         }
         Ss[r * (BKV + 1) + c] = s;

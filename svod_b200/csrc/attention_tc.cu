@@ -87,6 +87,7 @@ struct FaParams {
   int has_chunk;
   int64_t chunk_size, chunk_left, chunk_right;
   const int32_t* seg_start;
+  const int32_t* row_map;  // `ops::Cache`: cache row of batch lane b, or null
   float* lse;
   int n_qt;  // query tile pairs per (head, batch)
   uint32_t* status;
@@ -334,6 +335,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
+        const int kv_b = p.row_map != nullptr ? p.row_map[b] : (int)b;
         for (int j = u_lo; j < u_hi; ++j) {
           if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) {
             ok = false;
@@ -341,14 +343,14 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           }
           mbar_expect_tx(&k_full[s], KB);
           for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(k_s + s * KB + c * KBOX, &tmap_k, &k_full[s], c * 64, hk, j * kBKV, (int)b);
+            tma_load_4d(k_s + s * KB + c * KBOX, &tmap_k, &k_full[s], c * 64, hk, j * kBKV, kv_b);
           if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) {
             ok = false;
             break;
           }
           mbar_expect_tx(&v_full[s], KB);
           for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(v_s + s * KB + c * KBOX, &tmap_v, &v_full[s], c * 64, hk, j * kBKV, (int)b);
+            tma_load_4d(v_s + s * KB + c * KBOX, &tmap_v, &v_full[s], c * 64, hk, j * kBKV, kv_b);
           if (++s == S) {
             s = 0;
             ph ^= 1;
@@ -797,7 +799,7 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     if (!make_tmap(&tq, a.q, a.dtype, 4, dims, st, box)) return -1;
   }
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.batch};
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
     const uint64_t stk[3] = {(uint64_t)a.k_sh, (uint64_t)a.k_st, (uint64_t)a.k_sb};
     const uint64_t stv[3] = {(uint64_t)a.v_sh, (uint64_t)a.v_st, (uint64_t)a.v_sb};
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
@@ -825,6 +827,7 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.has_chunk = a.has_chunk;
   p.chunk_size = a.chunk_size, p.chunk_left = a.chunk_left, p.chunk_right = a.chunk_right;
   p.seg_start = a.seg_start;
+  p.row_map = a.row_map;
   p.lse = a.lse;
   p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
   p.status = a.status;
@@ -844,7 +847,7 @@ bool attention_tc_covers(const AttnArgs& a) {
   // because the running maximum is kept in raw-score units.
   if (a.dtype != SVODB_BF16 && a.dtype != SVODB_F16) return false;
   if (a.d != 64 && a.d != 128) return false;
-  if (a.bias != nullptr || a.splits > 1) return false;
+  if (a.bias != nullptr || a.splits > 1 || a.n_app > 0) return false;
   if (!(a.scale > 0.f)) return false;
   if (a.batch <= 0 || a.t <= 0 || a.tk <= 0 || a.batch > 65535 || a.heads > 65535) return false;
   if (a.t > 0x7fffff00LL || a.tk > 0x7fffff00LL) return false;

@@ -771,6 +771,7 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len)
   const int min_bn = a.gated ? 128 : (per_head ? 2 * a.rope_head_dim : 64);
   while (bn > min_bn && tiles(bn) < sms) bn /= 2;
   if (bn < min_bn) bn = min_bn;
+  if ((a.force_bn == 64 || a.force_bn == 128 || a.force_bn == 256) && a.force_bn >= min_bn) bn = a.force_bn;
   if (bn > 256) return 1;
   int rc;
   if (a.dtype == SVODB_BF16) {

@@ -111,6 +111,14 @@ struct AttnArgs {
   float* l_part;
   uint32_t* status;
   int packed;                // q,k,v are views of one fused projection
+  // `ops::Cache`: k, v point at the first head this attention reads of cache
+  // row 0; batch lane b reads row row_map[b] (b without a map) of kv_rows.
+  int64_t kv_rows;
+  const int32_t* row_map;    // [B] or null
+  const void* k_app;         // [B, n_app, kv_heads, D] contiguous, or null
+  const void* v_app;
+  int n_app;
+  const int32_t* app_lens;   // [B] or null
 };
 // Exact CUDA-core path (any float dtype, any D <= 256, every mask, bias, splits).
 int launch_attention_generic(const AttnArgs& a, cudaStream_t s);
@@ -158,6 +166,7 @@ struct GemmArgs {
   float norm_eps;
   int dtype;
   uint32_t* status;
+  int force_bn;  // 0 = the launcher's choice, else the tile width a config store asked for
 };
 int launch_gemm_generic(const GemmArgs& a, cudaStream_t s);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);

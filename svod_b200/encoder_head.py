@@ -88,6 +88,12 @@ class HeadPlans:
         return out_h[:len(batch)].numpy().copy()
 
 
+# the head interface the text pipeline drives (`EncoderHead::capacity` / `run_batch`,
+# model/src/encoder_head.rs:46-70)
+HeadPlans.capacity = lambda self: (self.max_batch, self.max_seq)
+HeadPlans.run_batch = lambda self, encodings: self.run(encodings)
+
+
 def embed_chunks(plans: HeadPlans, chunks: Sequence[Sequence[int]]) -> np.ndarray:
     """`run_chunks_flat` (arch/src/pipelines/text.rs:968-985): chunks sorted
     longest first, cut into sub-batches of `max_batch`, results restored to

@@ -96,6 +96,18 @@ class Chunk:
 
 
 @dataclass
+class Cache:
+    """`ops::Cache` (tk/src/ops/attention.rs:39-55): `k`, `v` are caches
+    `[rows, Tk, H_all, D]`; `appended = (k, v)` of `[B, n, kv_heads, D]` are
+    scored after the cached prefix that `KeyMask.Lens` names."""
+    head_start: int
+    kv_heads: int
+    row_map: Optional[torch.Tensor] = None
+    appended: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+    app_lens: Optional[torch.Tensor] = None
+
+
+@dataclass
 class Attn:
     """`ops::Attn` (tk/src/ops/attention.rs:59-86)."""
     causal: bool = False
@@ -106,6 +118,7 @@ class Attn:
     splits: Optional[int] = None
     scale: Optional[float] = None
     bias: Optional[torch.Tensor] = None
+    cache: Optional[Cache] = None
     want_lse: bool = False  # also return ln-sum-exp `[B, H, T]` f32
 
 
@@ -262,6 +275,23 @@ def _attn_opts(opts: Attn, q_shape, dtype, device, keep: list):
         t = opts.bias.contiguous()
         keep.append(_desc(t)), keep.append(t)
         o.bias = C.pointer(keep[-2])
+    if opts.cache is not None:
+        c = opts.cache
+        o.has_cache, o.cache_head_start, o.cache_kv_heads = 1, int(c.head_start), int(c.kv_heads)
+        i32 = lambda t: (t if t.dtype == torch.int32 else t.to(torch.int32)).contiguous()
+        if c.row_map is not None:
+            t = i32(c.row_map)
+            keep.append(_desc(t)), keep.append(t)
+            o.cache_row_map = C.pointer(keep[-2])
+        if c.appended is not None:
+            for name, t in (("cache_app_k", c.appended[0]), ("cache_app_v", c.appended[1])):
+                t = t.contiguous()
+                keep.append(_desc(t)), keep.append(t)
+                setattr(o, name, C.pointer(keep[-2]))
+        if c.app_lens is not None:
+            t = i32(c.app_lens)
+            keep.append(_desc(t)), keep.append(t)
+            o.cache_app_lens = C.pointer(keep[-2])
     lse = None
     B, T, H, D = q_shape
     if opts.want_lse:
@@ -283,6 +313,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, opts: Optional[
     opts = opts or Attn()
     if q.dim() != 4:
         raise OpsError(L.ERR_SHAPE, f"attention: q has shape {list(q.shape)}, expected [B, T, H, D]")
+    if opts.splits is None and not opts.want_lse:
+        # `splits: None` lets the tune store choose (tk/src/ops/attention.rs:74-80)
+        from . import tune
+        store = tune.active()
+        if store is not None:
+            hit = store.get(store.attention_key(q, k, opts))
+            if hit and hit > 1:
+                from dataclasses import replace
+                opts = replace(opts, splits=hit)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     keep: list = []
     o, lse = _attn_opts(opts, q.shape, q.dtype, q.device, keep)

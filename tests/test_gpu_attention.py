@@ -10,7 +10,7 @@ import torch
 
 from oracle import svod_oracle as O
 from svod_b200 import ops
-from tests.util import dev, host, max_abs, mean_rel
+from tests.util import dev, host, max_abs, mean_rel, normal
 
 pytestmark = pytest.mark.gpu
 
@@ -256,3 +256,104 @@ def test_full_size_attention_properties_at_seq_4096_d128():
         s = (kk @ q[b, i, h].float()) / math.sqrt(D)
         ref = torch.softmax(s, 0) @ vv
         assert float((o[b, i, h].float() - ref).abs().max()) < 2e-2
+
+
+# ---- decode-path reads: `ops::Cache` (tk/src/ops/attention.rs:39-55) -------------------------------
+# The reference's cached cases (tk/src/test/unit/attention.rs:395-410,488-505): batch 2, a cache of 3
+# rows holding 3*kv_heads heads of which this attention reads those from `kv_heads` on, lane b on
+# cache row 2-b under a row map, `appended` rows after the cached prefix of which lane b sees
+# `max(appended - b % 3, 1)` when counted, a per-batch bias of 2*x when biased; data from the LCG
+# (seed 5) in the order q, k, v, appended k, appended v, bias.
+CACHED_CASES = [
+    # name, t, tk, (heads, kv_heads, d), row_map, appended, splits, lens, counted, biased
+    ("cache slice", 1, 100, (4, 4, 64), False, 0, 1, [100, 37], False, False),
+    ("row map, appended, gqa", 1, 100, (4, 2, 64), True, 1, 1, [100, 37], False, False),
+    ("four splits", 1, 200, (4, 4, 64), True, 1, 4, [200, 70], False, False),
+    ("d 128, two splits, five queries", 5, 96, (2, 2, 128), False, 1, 2, [64, 96], False, False),
+    ("more splits than blocks for a row", 1, 64, (2, 2, 64), False, 0, 4, [64, 40], False, False),
+    ("appended row only, one split", 1, 7, (6, 6, 64), False, 1, 1, [0, 7], False, False),
+    ("appended row only, two splits", 1, 7, (6, 6, 64), False, 1, 2, [0, 3], False, False),
+    ("eight queries, eight appended, d 48", 8, 128, (4, 4, 48), False, 8, 1, [128, 40], False, False),
+    ("sixteen appended, two splits", 16, 128, (2, 2, 64), True, 16, 2, [128, 0], False, False),
+    ("counted appended rows", 8, 128, (4, 4, 48), False, 8, 1, [128, 40], True, False),
+    ("counted appended rows only, three splits", 16, 96, (2, 2, 64), False, 16, 3, [0, 96], True, False),
+    ("biased: row map, appended, gqa", 1, 100, (4, 2, 64), True, 1, 1, [100, 37], False, True),
+    ("biased: d 128, two splits", 5, 96, (2, 2, 128), False, 1, 2, [64, 96], False, True),
+    ("biased: four splits", 1, 200, (4, 4, 64), False, 0, 4, [200, 70], False, True),
+    ("biased: counted appended rows", 8, 64, (2, 2, 64), False, 8, 2, [64, 20], True, True),
+    ("a cached lane with no keys", 1, 100, (4, 4, 64), False, 0, 1, [100, 0], False, False),
+]
+
+
+@pytest.mark.parametrize("name,t,tk,hhd,row_map,appended,splits,lens,counted,biased", CACHED_CASES,
+                         ids=[c[0] for c in CACHED_CASES])
+def test_cached_attention_matches_the_reference_recipe(name, t, tk, hhd, row_map, appended, splits, lens, counted,
+                                                       biased):
+    dt, B, rows = O.BF16, 2, 3
+    H, Hkv, D = hhd
+    g = O.Lcg(5)
+    q = g.rounded(dt, B * t * H * D).reshape(B, t, H, D)
+    k = g.rounded(dt, rows * tk * 3 * Hkv * D).reshape(rows, tk, 3 * Hkv, D)
+    v = g.rounded(dt, rows * tk * 3 * Hkv * D).reshape(rows, tk, 3 * Hkv, D)
+    k_app = g.rounded(dt, B * appended * Hkv * D).reshape(B, appended, Hkv, D)
+    v_app = g.rounded(dt, B * appended * Hkv * D).reshape(B, appended, Hkv, D)
+    bias = 2.0 * g.rounded(dt, B * H * t * (tk + appended)).reshape(B, H, t, tk + appended) if biased else None
+    rm = np.array([rows - 1 - b for b in range(B)]) if row_map else None
+    seen = np.array([max(appended - b % 3, 1) for b in range(B)]) if counted else None
+    cache = dict(head_start=Hkv, kv_heads=Hkv, row_map=rm, k_app=k_app if appended else None,
+                 v_app=v_app if appended else None, app_lens=seen)
+    want = O.attention(q, k, v, key_lens=np.array(lens), bias=bias, cache=cache, dtype=dt)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    c = ops.Cache(Hkv, Hkv, i32(rm) if row_map else None,
+                  (dev(k_app, dt), dev(v_app, dt)) if appended else None, i32(seen) if counted else None)
+    a = ops.Attn(keys=ops.KeyMask.Lens(i32(lens)), cache=c, splits=splits if splits > 1 else None,
+                 bias=dev(bias, dt) if biased else None)
+    if not row_map:  # lane b reads cache row b: the op takes the batch's own rows
+        k, v = k[:B], v[:B]
+    got = host(ops.attention(dev(q, dt), dev(k, dt), dev(v, dt), a))
+    assert max_abs(got, want) < 2e-2
+    if name == "a cached lane with no keys":
+        assert np.all(got[1] == 0.0) and np.any(got[0] != 0.0)
+
+
+@pytest.mark.parametrize("D,T,Tk", [(128, 256, 320), (64, 130, 200)])
+def test_cache_slices_and_row_maps_stay_on_the_tensor_core_kernel(D, T, Tk):
+    """Without appended rows a cache read is a strided view plus a row lookup in
+    the loader: same kernel, same numbers as attention over the gathered rows."""
+    dt, B, rows, H, Hkv = O.BF16, 3, 5, 4, 2
+    rng = np.random.default_rng(D + T)
+    q = normal(rng, (B, T, H, D), 1.0, dt)
+    k = normal(rng, (rows, Tk, 3 * Hkv, D), 1.0, dt)
+    v = normal(rng, (rows, Tk, 3 * Hkv, D), 1.0, dt)
+    rm = np.array([4, 0, 2])
+    lens = np.array([Tk, 77, Tk - 1])
+    cache = dict(head_start=2 * Hkv, kv_heads=Hkv, row_map=rm)
+    want = O.attention(q, k, v, causal=True, key_lens=lens, cache=cache, dtype=dt)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    a = ops.Attn(causal=True, keys=ops.KeyMask.Lens(i32(lens)), cache=ops.Cache(2 * Hkv, Hkv, i32(rm)))
+    got = host(ops.attention(dev(q, dt), dev(k, dt), dev(v, dt), a))
+    assert "kernel flash_attention" in ops.chosen()
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+
+
+def test_cache_options_are_validated():
+    dt = O.BF16
+    z = lambda *s: dev(np.zeros(s), dt)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    q, k = z(2, 1, 4, 64), z(3, 16, 6, 64)
+    lens = ops.KeyMask.Lens(i32([16, 16]))
+    with pytest.raises(ops.OpsError) as e:  # rows != B without a row map
+        ops.attention(q, k, k, ops.Attn(cache=ops.Cache(0, 2)))
+    assert e.value.kind == "Shape"
+    with pytest.raises(ops.OpsError) as e:  # heads past the cache row
+        ops.attention(q, k, k, ops.Attn(cache=ops.Cache(5, 2, i32([0, 1]))))
+    assert e.value.kind == "Shape"
+    with pytest.raises(ops.OpsError) as e:  # appended rows need key lengths
+        ops.attention(q, k, k, ops.Attn(cache=ops.Cache(0, 2, i32([0, 1]), (z(2, 1, 2, 64), z(2, 1, 2, 64)))))
+    assert e.value.kind == "Shape"
+    with pytest.raises(ops.OpsError) as e:  # counted rows without appended rows
+        ops.attention(q, k, k, ops.Attn(keys=lens, cache=ops.Cache(0, 2, i32([0, 1]), None, i32([1, 1]))))
+    assert e.value.kind == "Shape"
+    with pytest.raises(ops.OpsError) as e:  # 4 query heads over 3 kv heads
+        ops.attention(q, k, k, ops.Attn(keys=lens, cache=ops.Cache(0, 3, i32([0, 1]))))
+    assert e.value.kind == "Heads"

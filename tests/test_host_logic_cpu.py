@@ -4,6 +4,7 @@ import os
 import socket
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -97,3 +98,106 @@ def test_packed_inputs_positions_segments_and_pool_slots():
     assert list(seg[0, :7]) == [0, 0, 0, 3, 3, 5, 6]   # padding: each token its own segment
     assert list(pool[0, :3]) == [2, 4, 5]
     assert list(seg[1, :3]) == [0, 1, 2] and np.all(ids[1] == 0)
+
+
+# ---- config store (the small stand-in for tk/src/tune.rs) ----------------------------------------
+def test_tune_store_round_trips_and_tolerates_bad_files(tmp_path, monkeypatch):
+    from svod_b200 import tune
+    from svod_b200 import _lib as L
+    lib = L.load()
+    lib.svodb_config_clear()
+    st = tune.TuneStore("NVIDIA B200", "0.1", tmp_path)
+    assert st.load() == 0  # no file: a miss, not an error
+    st.put("gemm|bf16|1024|4096|1024|plain", 128, 1234.5)
+    st.put("attention|bfloat16|2|1|4096|16|128|cache", 8, 99.0)
+    assert lib.svodb_config_get(b"gemm|bf16|1024|4096|1024|plain") == 128
+    assert lib.svodb_config_get(b"attention|bfloat16|2|1|4096|16|128|cache") == 0  # host-side entry
+    lib.svodb_config_clear()
+    st2 = tune.TuneStore("NVIDIA B200", "0.1", tmp_path)
+    assert st2.load() == 2 and st2.get("gemm|bf16|1024|4096|1024|plain") == 128
+    assert lib.svodb_config_get(b"gemm|bf16|1024|4096|1024|plain") == 128  # pushed into the library on load
+    # a line that does not parse is dropped at the next write
+    with open(st2.path, "a") as f:
+        f.write("garbage line\nkey notanumber 1\n")
+    st3 = tune.TuneStore("NVIDIA B200", "0.1", tmp_path)
+    assert st3.load() == 2 and st3.dropped == 2
+    st3.save()
+    assert "garbage" not in st3.path.read_text()
+    # another format orphans the file
+    st3.path.write_text("format 0\nx 1 1\n")
+    assert tune.TuneStore("NVIDIA B200", "0.1", tmp_path).load() == 0
+    # one file per device and version; the directory comes from the environment
+    monkeypatch.setenv("SVODB_TUNE_DIR", str(tmp_path / "elsewhere"))
+    other = tune.TuneStore("NVIDIA H100", "0.1")
+    assert other.path.parent == tmp_path / "elsewhere" and other.path.name != st3.path.name
+    # an unwritable store is a miss
+    ro = tune.TuneStore("x", "0.1", "/proc/definitely/not/writable")
+    ro.put("gemm|bf16|1|8|16|plain", 64, 1.0)
+    assert ro.get("gemm|bf16|1|8|16|plain") == 64 and not ro.save()
+    lib.svodb_config_set(b"gemm|bf16|1|8|16|plain", 0)
+    assert lib.svodb_config_get(b"gemm|bf16|1|8|16|plain") == 0
+    lib.svodb_config_clear()
+
+
+# ---- text pipeline front end (arch/src/pipelines/text.rs:575-667, 883-1134) ----------------------
+class _WordTokenizer:
+    """[CLS] word ids [SEP]; offsets = byte position of each word."""
+    def encode(self, text):
+        from svod_b200.pipeline import Encoding
+        ids, offs, at = [0], [0], 0
+        for w in text.split(" "):
+            ids.append(100 + len(w)), offs.append(at)
+            at += len(w) + 1
+        return Encoding(ids + [2], [1] + [0] * (len(ids) - 1) + [1], offs + [at])
+
+
+class _FakeHead:
+    def __init__(self, max_batch, max_seq):
+        self.cap, self.batches = (max_batch, max_seq), []
+    def capacity(self):
+        return self.cap
+    def run_batch(self, encodings):
+        self.batches.append([len(e) for e in encodings])
+        return [np.array([len(e), sum(e)], dtype=np.float32) for e in encodings]
+
+
+def test_sliding_window_chunker_geometry():
+    from svod_b200.pipeline import ChunkerError, Encoding, SlidingWindowChunker
+    enc = Encoding([0] + list(range(10, 20)) + [2], [1] + [0] * 10 + [1])
+    ch = SlidingWindowChunker(6, 3).chunk(enc)  # 4 content tokens per window, step 3
+    assert [c.first_token for c in ch] == [0, 3, 6]
+    assert [c.encoding.ids for c in ch] == [[0, 10, 11, 12, 13, 2], [0, 13, 14, 15, 16, 2], [0, 16, 17, 18, 19, 2]]
+    ch = SlidingWindowChunker(6, 4).chunk(enc)
+    assert [c.encoding.ids for c in ch][-1] == [0, 18, 19, 2]  # a short last window
+    ch = SlidingWindowChunker(6, 4, full_last_window=True).chunk(enc)
+    assert [c.encoding.ids for c in ch][-1] == [0, 16, 17, 18, 19, 2]  # backed up to a whole one
+    assert SlidingWindowChunker(6, 3).chunk(Encoding([])) == []
+    only_specials = SlidingWindowChunker(2, 1).chunk(Encoding([0, 2], [1, 1]))
+    assert len(only_specials) == 1 and only_specials[0].encoding.ids == [0, 2]
+    with pytest.raises(ChunkerError):
+        SlidingWindowChunker(2, 1).chunk(enc)  # no room past the two specials
+    with pytest.raises(ChunkerError):
+        SlidingWindowChunker(4, 5)
+
+
+def test_encoder_pipeline_batches_longest_first_and_restores_order():
+    from svod_b200.pipeline import EncoderPipeline, PipelineBuildError, SlidingWindowChunker
+    head = _FakeHead(max_batch=3, max_seq=8)
+    with pytest.raises(PipelineBuildError):
+        EncoderPipeline(_WordTokenizer(), SlidingWindowChunker(9, 4), head)
+    pipe = EncoderPipeline(_WordTokenizer(), SlidingWindowChunker(6, 4), head)
+    texts = ["a bb ccc dddd eeeee ffffff", "x", "one two three four five six seven eight nine"]
+    out = pipe.embed_texts(texts)
+    assert [len(o) for o in out] == [2, 1, 3]
+    # sub-batches of at most 3, each sorted longest first
+    assert all(len(b) <= 3 and b == sorted(b, reverse=True) for b in head.batches)
+    assert max(head.batches[0]) >= max(head.batches[-1])
+    for chunks in out:
+        for chunk, value in chunks:  # each output belongs to its own chunk
+            assert value[0] == len(chunk.encoding) and value[1] == sum(chunk.encoding.ids)
+    assert out[0][1][0].byte_offset == len("a bb ccc dddd ")  # second window starts at its 5th word
+    assert pipe.embed("x")[0][1][0] == 3
+    built = EncoderPipeline.assemble(_WordTokenizer(), SlidingWindowChunker(5, 2), lambda n: _FakeHead(2, n))
+    assert built.head.capacity() == (2, 5)
+    built.warm_up([(2, 5)])
+    assert built.head.batches == [[5, 5]]

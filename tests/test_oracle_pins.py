@@ -336,3 +336,53 @@ def test_l2_normalize_keeps_a_zero_row_zero():
     x = np.array([[3.0, 4.0], [0.0, 0.0]])
     y = O.l2_normalize(x)
     assert np.allclose(y[0], [0.6, 0.8]) and np.all(y[1] == 0)
+
+
+# ---- cached reads: tk/src/test/unit/attention.rs:69-178 (`case`, `reference`) -----------------------
+@pytest.mark.parametrize("t,tk,hhd,row_map,appended,lens,counted,biased", [
+    (1, 100, (4, 2, 64), True, 1, [100, 37], False, False),
+    (8, 64, (2, 2, 64), False, 8, [64, 20], True, True),
+    (1, 7, (6, 6, 64), False, 1, [0, 7], False, False),
+    (5, 96, (2, 2, 128), False, 1, [64, 96], False, True),
+])
+def test_cached_attention_matches_a_scalar_restatement(t, tk, hhd, row_map, appended, lens, counted, biased):
+    """The oracle's `cache=` against loops written from the reference test's own
+    f64 `reference`: head_start = kv_heads, lane b on cache row 2-b under a row
+    map, masks on cached keys only, appended keys hidden past the lane's count."""
+    B, rows = 2, 3
+    H, Hkv, D = hhd
+    g = O.Lcg(5)
+    q = g.rounded(O.BF16, B * t * H * D).reshape(B, t, H, D)
+    k = g.rounded(O.BF16, rows * tk * 3 * Hkv * D).reshape(rows, tk, 3 * Hkv, D)
+    v = g.rounded(O.BF16, rows * tk * 3 * Hkv * D).reshape(rows, tk, 3 * Hkv, D)
+    ka = g.rounded(O.BF16, B * appended * Hkv * D).reshape(B, appended, Hkv, D)
+    va = g.rounded(O.BF16, B * appended * Hkv * D).reshape(B, appended, Hkv, D)
+    bias = 2.0 * g.rounded(O.BF16, B * H * t * (tk + appended)).reshape(B, H, t, tk + appended) if biased else None
+    rm = [rows - 1 - b for b in range(B)] if row_map else None
+    seen = [max(appended - b % 3, 1) for b in range(B)] if counted else None
+    cache = dict(head_start=Hkv, kv_heads=Hkv, row_map=rm, k_app=ka if appended else None,
+                 v_app=va if appended else None, app_lens=seen)
+    got = O.attention(q, k, v, key_lens=np.array(lens), bias=bias, cache=cache, dtype=O.F32)
+    want = np.zeros_like(got)
+    group, scale = H // Hkv, float(np.float32(1.0 / math.sqrt(D)))
+    for b in range(B):
+        row = rm[b] if rm else b
+        sn = seen[b] if seen else appended
+        for h in range(H):
+            for i in range(t):
+                sc, vals = [], []
+                for j in range(tk + appended):
+                    if j < tk:
+                        if j >= lens[b]:
+                            continue
+                        kk, vv = k[row, j, Hkv + h // group], v[row, j, Hkv + h // group]
+                    else:
+                        if j - tk >= sn:
+                            continue
+                        kk, vv = ka[b, j - tk, h // group], va[b, j - tk, h // group]
+                    sc.append(float(q[b, i, h] @ kk) * scale + (bias[b, h, i, j] if biased else 0.0))
+                    vals.append(vv)
+                if sc:
+                    w = np.exp(np.array(sc) - max(sc))
+                    want[b, i, h] = (w / w.sum()) @ np.array(vals)
+    assert np.abs(got - want).max() < 1e-6
