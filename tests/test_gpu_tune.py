@@ -21,7 +21,7 @@ def test_linear_tile_width_is_measured_once_and_replayed(tmp_path):
     x, w = dev(normal(rng, (2048, 512), 1.0, dt), dt), dev(normal(rng, (1024, 512), 0.05, dt), dt)
     base = host(ops.linear(x, w))
     key = lib.svodb_last_config_key().decode()
-    assert key == "gemm|bf16|2048|1024|512|plain"
+    assert key == "gemm|BFloat16|2048|1024|512|plain"
     store = tune.TuneStore(torch.cuda.get_device_name(0), directory=tmp_path)
     bn = store.tune_linear(x, w)
     assert bn in tune.GEMM_WIDTHS and store.get(key) == bn and lib.svodb_config_get(key.encode()) == bn
