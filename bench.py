@@ -43,6 +43,17 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch and batch
+# row, from the ncu captures summarised under profiles/: the captures run the
+# bench's per-launch shape at batch 4 (a full launch is too large to capture
+# under a profiler), and the traffic of both kernels grows in proportion to the
+# rows (every CTA works on one batch row's tiles).
+NCU_DRAM_BYTES_PER_ROW = {
+    ("qwen3", "flash_attention"): 173.6e6 / 4,   # algorithmic 100.7 MB at batch 4
+    ("qwen3", "gemm"): 101.7e6 / 4,              # algorithmic 96.5 MB at batch 4 (M = 16384)
+}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -389,7 +400,9 @@ def gpu_arm(args):
         top = max(ks, key=lambda n: ks[n]["ms"] * ks[n]["launches_per_step"])
         line["roofline"] = {
             "kernel": top, "bound": "tensor", "achieved": ks[top]["tflops"], "peak": peaks["sustained"],
-            "unit": "TFLOP/s", "frac": ks[top]["tflops"] / peaks["sustained"], "traffic": None,
+            "unit": "TFLOP/s", "frac": ks[top]["tflops"] / peaks["sustained"],
+            "traffic": NCU_DRAM_BYTES_PER_ROW.get((kind, top), 0) * batch or None,
+            "traffic_note": "dram read+write bytes of one ncu capture at batch 4, scaled by rows (profiles/)",
             "peak_source": f"{peaks['source']} bf16 sustained (kernel timed back to back)",
         }
         line["kernels"] = ks

@@ -86,8 +86,8 @@ const char* svodb_last_chosen(void);
  * `svodb_last_config_key`: the key of the last `svodb_linear` on this thread that
  * reached the tensor-core kernel, "gemm|<dtype>|<m>|<n>|<k>|<epilogue>" ("" when
  * none did). `svodb_config_set(key, bn)`: later calls with that key use tile
- * width bn (64, 128 or 256; a width the epilogue cannot take is ignored);
- * bn = 0 forgets the key. `svodb_config_get` returns 0 when the key is unset. */
+ * width bn (64, 128 or 256 on one CTA, 512 = the CTA-pair kernel; a choice the
+ * shape or epilogue cannot take is ignored); bn = 0 forgets the key. `svodb_config_get` returns 0 when the key is unset. */
 const char* svodb_last_config_key(void);
 int svodb_config_set(const char* key, int32_t value);
 int32_t svodb_config_get(const char* key);

@@ -467,6 +467,15 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
     if (any && !contiguous(y))
       return fail(SVODB_ERR_GRAPH, "%s: the qkv prologue outside the kernel needs a contiguous y", OP);
   }
+  if (a.force_bn == 512 ? gemm_tc2_covers(a) : (a.force_bn == 0 && gemm_tc2_preferred(a))) {
+    int rc = launch_gemm_tc2(a, s, cfg, sizeof cfg);
+    if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+    if (rc == 0) {
+      chose_kernel(OP, "gemm", cfg);
+      if (qo != nullptr) heads_in_place(qo, y, qkv_per_batch, s);
+      return check_launch(OP);
+    }
+  }
   if (gemm_tc_covers(a)) {
     int rc = launch_gemm_tc(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);

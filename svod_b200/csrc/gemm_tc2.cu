@@ -1,0 +1,446 @@
+// tcgen05 GEMM on CTA pairs (cta_group::2): y = epilogue(x . w^T) for the large
+// projections. Same contract and epilogue order as gemm_tc.cu
+// (tk/src/kernels/gemm.rs:605-651: +bias -> act -> *up -> *scale -> +residual ->
+// one rounding); what changes is who loads what:
+//
+//   cluster of 2 CTAs = one 256-row x 256-column accumulator tile. Each CTA
+//   loads its own 128 rows of A and HALF of the W tile (128 of its 256 rows), so
+//   a k-block costs each SM 32 KiB of operand traffic from L2 instead of 48 KiB;
+//   the even CTA's MMA warp issues `tcgen05.mma.cta_group::2` (M = 256), which
+//   reads both CTAs' shared memory and writes 128 accumulator rows into each
+//   CTA's tensor memory. Both CTAs run the staged TMA-store epilogue on their
+//   own rows.
+//
+// Barriers: `full` lives in the even CTA and counts the bytes of both CTAs'
+// loads (the loads are plain, non-multicast TMA with the pair qualifier, which
+// lets their completion be counted on the partner's barrier); `empty` and
+// `acc_full` exist in both CTAs and are signalled by one tcgen05.commit each;
+// `acc_empty` lives in the even CTA and collects the epilogue warps of both.
+// Every mbarrier wait is bounded; the two cluster barriers are reached by every
+// thread of both CTAs on every path.
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "svodb.h"
+#include "tensormap.h"
+
+namespace svodb {
+
+namespace {
+
+constexpr int BM = 128;  // rows per CTA (the pair's tile has 256)
+constexpr int BN = 256;  // accumulator columns
+constexpr int BK = 64;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // A 16 KiB + this CTA's half of W 16 KiB
+constexpr int kStages = 6;
+constexpr int kStagingBytes = 2 * 128 * 128;
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTmemCols = 512;
+
+struct Params2 {
+  int64_t m;
+  int n, k;
+  int tiles_m, tiles_n;  // pair tiles: 256 rows x out_bn columns
+  int out_bn;            // 256, or 128 when gated
+  int gated;
+  int act;
+  int has_scale;
+  float scale;
+  const void* bias;
+  const void* residual;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mt, int& nt) {
+  const int per_group = 8 * tiles_n;
+  const int group = t / per_group;
+  const int first = group * 8;
+  const int gsize = tiles_m - first < 8 ? tiles_m - first : 8;
+  const int r = t - group * per_group;
+  mt = first + r % gsize;
+  nt = r / gsize;
+}
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, bool ok, float (&f)[8]) {
+  if (ok) {
+    uint4 u = ldg128(p);
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 v = Elem<T>::unpack(uu[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+  }
+}
+
+__device__ __forceinline__ void act32(float (&x)[32], int act) {
+  switch (act) {
+    case kActGelu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = gelu_f(x[i]);
+      break;
+    case kActSilu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = silu_f(x[i]);
+      break;
+    case kActGeluTanh:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = gelu_tanh_f(x[i]);
+      break;
+    default: break;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void acc32(uint32_t taddr, const T* bias, int n_at, int n_lim, float (&x)[32]) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
+  if (bias != nullptr) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      float b[8];
+      load8<T>(bias + n_at + v * 8, n_at + v * 8 < n_lim, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[v * 8 + i] += b[i];
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+                    const Params2 p) {
+  constexpr int S = kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + (size_t)S * kStageBytes;  // [2 halves][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  uint64_t* full = bars;                   // [S]  used in the even CTA
+  uint64_t* empty = bars + S;              // [S]  in both CTAs
+  uint64_t* acc_full = bars + 2 * S;       // [2]  in both CTAs
+  uint64_t* acc_empty = bars + 2 * S + 2;  // [2]  used in the even CTA
+  uint64_t* res_full = bars + 2 * S + 4;   // [2 halves] local: residual sub-tile landed in staging
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = the CTA that issues the MMAs
+  const int pair = blockIdx.x >> 1;
+  const int pairs = gridDim.x >> 1;
+  const int num_kb = (p.k + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 2 * kEpiWarps);  // the epilogue warps of both CTAs
+      mbar_init(&res_full[i], 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // The partner's barriers must exist before anything signals them.
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += pairs) {
+        int mt, nt;
+        tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
+        const int m0 = mt * 2 * BM + (int)rank * BM;
+        const int n0 = nt * p.out_bn;
+        // this CTA's 128 rows of the W tile: the lower / upper half of a plain
+        // tile's 256 rows; the gate rows / the up rows of a gated tile
+        const int w_row = p.gated ? (rank == 0 ? n0 : p.n + n0) : n0 + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + (size_t)s * kStageBytes;
+          uint8_t* b_dst = a_dst + BM * BK * 2;
+          const uint32_t full_addr = cluster_map(&full[s], 0);
+          if (rank == 0) mbar_expect_tx(&full[s], (uint32_t)(2 * kStageBytes));
+          tma_load_2d_pair(a_dst, &tmap_a, full_addr, kb * BK, m0);
+          tma_load_2d_pair(b_dst, &tmap_w, full_addr, kb * BK, w_row);
+          if (++s == S) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+      // Error path: a bounded pause lets copies already in flight land before
+      // the CTA's shared memory is released.
+      if (!ok)
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(Elem<T>::kUmmaFormat, 2 * BM, BN, 0, 0);
+      const bool leader = elect_one();
+      const uint64_t desc0 = umma_desc_sw128(smem_u32(smem), 16, 1024);
+      int s = 0;
+      uint32_t ph = 0;
+      int as = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += pairs) {
+        if (!mbar_wait(&acc_empty[as], aph ^ 1, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t a_desc = desc0 + (uint64_t)((s * kStageBytes) >> 4);
+          const uint64_t b_desc = a_desc + (uint64_t)((BM * BK * 2) >> 4);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            if (leader)
+              umma_ss_pair(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc,
+                           (kb | k4) != 0 ? 1u : 0u);
+          // the stage is free in both CTAs once these MMAs have read it
+          if (leader) {
+            tc_commit_pair(cluster_map(&empty[s], 0));
+            tc_commit_pair(cluster_map(&empty[s], 1));
+          }
+          if (++s == S) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (ok && leader) {
+          tc_commit_pair(cluster_map(&acc_full[as], 0));
+          tc_commit_pair(cluster_map(&acc_full[as], 1));
+        }
+        __syncwarp();
+        if (++as == 2) {
+          as = 0;
+          aph ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, each its 128 rows) ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int chalf = ew >> 2;
+    const T* bias = (const T*)p.bias;
+    int as = 0;
+    uint32_t aph = 0;
+    uint32_t res_phase = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += pairs) {
+      int mt, nt;
+      tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
+      const int n0 = nt * p.out_bn;
+      const int cols = p.out_bn / 2;
+      const int c_lo = chalf * cols;
+      if (!mbar_wait(&acc_full[as], aph, p.status)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
+      uint8_t* stg = staging + chalf * (128 * 128);
+      const bool chief = (ew & 3) == 0 && lane == 0;
+      const int r_tile = quarter * 32 + lane;
+      const int m0 = mt * 2 * BM + (int)rank * BM;
+      const bool rows_live = m0 < p.m;  // a ragged last tile may leave the odd CTA no row
+      for (int sub = 0; sub < cols / 64; ++sub) {
+        const int c0 = c_lo + sub * 64;
+        const int n_at = rows_live ? n0 + c0 : p.n;  // past N: nothing is loaded or stored
+        if (chief) tma_store_wait_read();
+        named_barrier(1 + chalf, 128);
+        if (p.residual != nullptr && chief && n_at < p.n) {
+          mbar_expect_tx(&res_full[chalf], 128 * 128);
+          tma_load_2d(stg, &tmap_r, &res_full[chalf], n_at, m0);
+        }
+        float x[64];
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          float (&xs)[32] = *reinterpret_cast<float (*)[32]>(&x[32 * hc]);
+          acc32<T>(t_acc + (uint32_t)(c0 + 32 * hc), bias, n_at + 32 * hc, p.n, xs);
+          act32(xs, p.act);
+          if (p.gated) {
+            float u[32];
+            acc32<T>(t_acc + (uint32_t)(BN / 2 + c0 + 32 * hc), bias != nullptr ? bias + p.n : nullptr,
+                     n_at + 32 * hc, p.n, u);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xs[i] *= u[i];
+          }
+          if (p.has_scale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xs[i] *= p.scale;
+          }
+        }
+        if (p.residual != nullptr && n_at < p.n) {
+          if (!mbar_wait(&res_full[chalf], res_phase, p.status)) ok = false;
+          res_phase ^= 1;
+        }
+        uint8_t* srow = stg + r_tile * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4* slot = reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4));
+          if (p.residual != nullptr && n_at < p.n) {
+            const uint4 rv = *slot;
+            const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = Elem<T>::unpack(rr[i]);
+              x[c * 8 + 2 * i] += f.x;
+              x[c * 8 + 2 * i + 1] += f.y;
+            }
+          }
+          *slot = make_uint4(Elem<T>::pack(x[c * 8 + 0], x[c * 8 + 1]), Elem<T>::pack(x[c * 8 + 2], x[c * 8 + 3]),
+                             Elem<T>::pack(x[c * 8 + 4], x[c * 8 + 5]), Elem<T>::pack(x[c * 8 + 6], x[c * 8 + 7]));
+        }
+        fence_proxy_async_smem();
+        named_barrier(1 + chalf, 128);
+        if (chief && n_at < p.n) {
+          tma_store_2d(&tmap_c, stg, n_at, m0);
+          tma_store_commit();
+        }
+      }
+      // This warp's TMEM reads of the tile are complete: one arrival on the even
+      // CTA's barrier, from either CTA.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_map(&acc_empty[as], 0));
+      if (++as == 2) {
+        as = 0;
+        aph ^= 1;
+      }
+    }
+  }
+
+  if (warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  // Neither CTA may leave while the other can still signal its barriers or the
+  // pair MMAs can still read its shared memory.
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T>
+int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) {
+  Params2 p{};
+  p.m = a.m, p.n = a.n, p.k = a.k;
+  p.gated = a.gated, p.act = a.act, p.has_scale = a.has_scale, p.scale = a.scale;
+  p.bias = a.bias, p.residual = a.residual, p.status = a.status;
+  p.out_bn = a.gated ? BN / 2 : BN;
+  p.tiles_m = (int)((a.m + 2 * BM - 1) / (2 * BM));
+  p.tiles_n = (a.n + p.out_bn - 1) / p.out_bn;
+  CUtensorMap ta, tw, tc, tr;
+  const int dt = a.dtype;
+  if (!make_tmap_2d(&ta, a.a, dt, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, BM)) return -1;
+  const uint64_t w_rows = (uint64_t)(a.gated ? 2 * a.n : a.n);
+  if (!make_tmap_2d(&tw, a.w, dt, (uint64_t)a.k, w_rows, (uint64_t)a.ldw, BK, BN / 2)) return -1;
+  if (!make_tmap_2d(&tc, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, BM)) return -1;
+  tr = tc;
+  if (a.residual != nullptr && !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
+    return -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
+        cudaSuccess)
+      return -1;
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.dynamicSmemBytes = kSmemBytes;
+  lc.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  if (cudaLaunchKernelEx(&lc, gemm_tc2_kernel<T>, ta, tw, tc, tr, p) != cudaSuccess) return -1;
+  if (cfg != nullptr)
+    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d,cta_pair:1}", 2 * BM, BN, BK, kStages,
+             a.gated, 2 * pairs);
+  return 0;
+}
+
+int sm_count2() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+}  // namespace
+
+// The pair kernel takes what the one-CTA kernel covers, minus per-head stores,
+// once the problem has at least one 256 x 256 tile per CTA pair.
+bool gemm_tc2_covers(const GemmArgs& a) {
+  if (!gemm_tc_covers(a)) return false;
+  if (a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr) return false;
+  const int out_bn = a.gated ? BN / 2 : BN;
+  if (a.n < out_bn || a.m < 2 * BM) return false;
+  const int64_t tiles = ((a.m + 2 * BM - 1) / (2 * BM)) * ((a.n + out_bn - 1) / out_bn);
+  return tiles >= sm_count2() / 2;
+}
+
+// Where the pair kernel is the default: long enough k loops to pay for the
+// pair's extra hand-shakes per tile (measured: ahead from K = 1024 on, behind
+// at K = 768); a config store may still choose either kernel per shape.
+bool gemm_tc2_preferred(const GemmArgs& a) { return gemm_tc2_covers(a) && a.k >= 1024; }
+
+int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
+  if (!gemm_tc2_covers(a)) return 1;
+  const int sms = sm_count2();
+  return a.dtype == SVODB_BF16 ? run2<__nv_bfloat16>(a, sms, s, cfg, cfg_len) : run2<__half>(a, sms, s, cfg, cfg_len);
+}
+
+}  // namespace svodb

@@ -166,11 +166,16 @@ struct GemmArgs {
   float norm_eps;
   int dtype;
   uint32_t* status;
-  int force_bn;  // 0 = the launcher's choice, else the tile width a config store asked for
+  int force_bn;  // 0 = the launcher's choice; 64/128/256 = that tile width on one CTA; 512 = the CTA-pair kernel
 };
 int launch_gemm_generic(const GemmArgs& a, cudaStream_t s);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 bool gemm_tc_covers(const GemmArgs& a);
+// The same GEMM on CTA pairs (cta_group::2, 256 x 256 tiles): the large
+// projections without per-head stores.
+int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
+bool gemm_tc2_covers(const GemmArgs& a);
+bool gemm_tc2_preferred(const GemmArgs& a);
 
 // Sets the calling thread's `svodb_last_error` text (printf-style).
 void set_last_error(const char* fmt, ...);

@@ -25,7 +25,7 @@ from typing import Callable, Dict, Iterable, Optional, Tuple
 from . import _lib as L
 
 FORMAT = 1
-GEMM_WIDTHS = (64, 128, 256)
+GEMM_WIDTHS = (64, 128, 256, 512)  # 512 = the CTA-pair kernel (256 x 256 tiles on two SMs)
 
 
 def enabled() -> bool:
@@ -148,7 +148,13 @@ class TuneStore:
             lib.svodb_config_set(key.encode(), bn)
             ops.linear(x, w, opts)
 
-        best = self.pick(key, GEMM_WIDTHS, run)
+        def takes(bn: int) -> bool:
+            # a choice the shape or the epilogue cannot take is ignored by the library
+            run(bn)
+            chosen = ops.chosen()
+            return ("cta_pair:1" in chosen) if bn == 512 else (f"bn:{bn}," in chosen and "cta_pair" not in chosen)
+
+        best = self.pick(key, [bn for bn in GEMM_WIDTHS if takes(bn)], run)
         lib.svodb_config_set(key.encode(), best)
         return best
 

@@ -200,3 +200,50 @@ def test_qkv_prologue_excludes_the_other_epilogues():
     with pytest.raises(ops.OpsError) as e:
         ops.linear(x, w, ops.Linear(qkv=ops.Qkv(3, 1, 64)))
     assert e.value.kind == "Shape"
+
+
+@pytest.mark.parametrize("m,n,k,kw", [
+    (4864, 1024, 256, dict()),                                   # 19 x 4 pair tiles
+    (4864, 1024, 320, dict(bias=True, act=1)),                   # bias + GELU, k not a multiple of 64... of 128
+    (4964, 1000, 256, dict(bias=True, residual=True, scale=0.5)),  # ragged rows (the odd CTA of the last tile is empty) and columns
+    (4864, 512, 256, dict(act=2, gated=True)),                   # SwiGLU: gate rows in the even CTA, up rows in the odd one
+    (9728, 512, 192, dict(bias=True, act=2, gated=True, residual=True)),
+])
+def test_cta_pair_gemm_matches_the_oracle(m, n, k, kw):
+    """Shapes with at least one 256 x 256 tile per CTA pair run the
+    `cta_group::2` kernel; same epilogue, same tolerance as the one-CTA kernel
+    (tk/src/test/unit/rows.rs:77-145: rel 1.6e-2)."""
+    dt = O.BF16
+    rng = np.random.default_rng(m + n + k)
+    gated = kw.get("gated", False)
+    x = O.round_to(dt, rng.standard_normal((m, k)))
+    w = O.round_to(dt, rng.standard_normal(((2 if gated else 1) * n, k)) / np.sqrt(k))
+    b = O.round_to(dt, rng.standard_normal((2 if gated else 1) * n)) if kw.get("bias") else None
+    r = O.round_to(dt, rng.standard_normal((m, n))) if kw.get("residual") else None
+    want = O.linear(x, w, b, act=kw.get("act", 0), gated=gated, residual=r, scale=kw.get("scale"), dtype=dt)
+    # short k loops default to the one-CTA kernel (same k order, same epilogue)
+    one = run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
+    assert "cta_pair" not in ops.chosen()
+    from svod_b200 import _lib as L
+    lib = L.load()
+    key = lib.svodb_last_config_key()
+    lib.svodb_config_set(key, 512)  # the config store's code for the pair kernel
+    try:
+        got = run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
+        assert "cta_pair:1" in ops.chosen(), ops.chosen()
+    finally:
+        lib.svodb_config_set(key, 0)
+    assert rel_close(got, want, 1.6e-2)
+    assert mean_rel(got, want) < 5e-3
+    assert max_abs(got, one) == 0.0
+
+
+def test_long_k_projections_take_the_cta_pair_kernel_by_default():
+    dt = O.BF16
+    rng = np.random.default_rng(11)
+    m, n, k = 5120, 1024, 1024
+    x = O.round_to(dt, rng.standard_normal((m, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    got = run_linear(x, w, dt)
+    assert "cta_pair:1" in ops.chosen()
+    assert rel_close(got, O.linear(x, w, dtype=dt), 1.6e-2)

@@ -29,9 +29,12 @@ def test_linear_tile_width_is_measured_once_and_replayed(tmp_path):
     assert f"bn:{bn}" in ops.chosen()
     assert max_abs(got, base) == 0.0  # the k order does not depend on the tile width
     # every width gives the same numbers
-    for cand in tune.GEMM_WIDTHS:
+    for cand in (64, 128, 256):
         lib.svodb_config_set(key.encode(), cand)
         assert max_abs(host(ops.linear(x, w)), base) == 0.0 and f"bn:{cand}" in ops.chosen()
+    # the CTA-pair kernel needs a 256 x 256 tile per pair of SMs: ignored for this shape
+    lib.svodb_config_set(key.encode(), 512)
+    assert max_abs(host(ops.linear(x, w)), base) == 0.0 and "cta_pair" not in ops.chosen()
     # a fresh process state reads the choice back from the file
     lib.svodb_config_clear()
     again = tune.TuneStore(torch.cuda.get_device_name(0), directory=tmp_path)
