@@ -456,6 +456,14 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
     f.norm_k_heads = qo->kv_heads;
     f.norm_eps = (float)qo->eps;
     const bool any = f.rope_cos != nullptr || f.norm_q != nullptr || f.norm_k != nullptr;
+    if (any && (f.force_bn == 512 ? gemm_tc2_covers(f) : (f.force_bn == 0 && gemm_tc2_preferred(f)))) {
+      int rc = launch_gemm_tc2(f, s, cfg, sizeof cfg);
+      if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+      if (rc == 0) {
+        chose_kernel(OP, "gemm", cfg);
+        return check_launch(OP);
+      }
+    }
     if (any && gemm_tc_covers(f)) {
       int rc = launch_gemm_tc(f, s, cfg, sizeof cfg);
       if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);

@@ -36,10 +36,17 @@ constexpr int BK = 64;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // A 16 KiB + this CTA's half of W 16 KiB
-constexpr int kStages = 6;
 constexpr int kStagingBytes = 2 * 128 * 128;
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTableBytes = 2 * 128 * 128;  // head variant: this CTA's 128 rows of cos and of sin
 constexpr int kTmemCols = 512;
+// The head variant (attention prologue in the store) gives one pipeline stage up
+// for the rotation tables.
+template <bool HEADS>
+struct Cfg2 {
+  static constexpr int kStages = HEADS ? 5 : 6;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kStagingBytes + (HEADS ? kTableBytes : 0) +
+                                       1024 /*align*/ + 256 /*barriers*/ + (HEADS ? 1024 : 0) /*norm weights*/;
+};
 
 struct Params2 {
   int64_t m;
@@ -53,6 +60,14 @@ struct Params2 {
   const void* bias;
   const void* residual;
   uint32_t* status;
+  // head variant: per-head RMSNorm (weights norm_q below norm_q_cols, norm_k
+  // below norm_cols) and rotation (columns below rope_width) of 128-wide heads
+  const void* norm_q;
+  const void* norm_k;
+  int norm_q_cols, norm_cols;
+  float norm_eps;
+  int rope_width;
+  int64_t rope_seq;  // table rows; a tile's 128 rows never wrap around it
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mt, int& nt) {
@@ -118,22 +133,27 @@ __device__ __forceinline__ void acc32(uint32_t taddr, const T* bias, int n_at, i
   }
 }
 
-template <typename T>
+template <typename T, bool HEADS>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+                    const __grid_constant__ CUtensorMap tmap_cos, const __grid_constant__ CUtensorMap tmap_sin,
                     const Params2 p) {
-  constexpr int S = kStages;
+  constexpr int S = Cfg2<HEADS>::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + (size_t)S * kStageBytes;  // [2 halves][128 rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  uint8_t* tables = staging + kStagingBytes;          // head variant: [cos | sin][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tables + (HEADS ? kTableBytes : 0));
   uint64_t* full = bars;                   // [S]  used in the even CTA
   uint64_t* empty = bars + S;              // [S]  in both CTAs
   uint64_t* acc_full = bars + 2 * S;       // [2]  in both CTAs
   uint64_t* acc_empty = bars + 2 * S + 2;  // [2]  used in the even CTA
   uint64_t* res_full = bars + 2 * S + 4;   // [2 halves] local: residual sub-tile landed in staging
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+  uint64_t* tab_full = bars + 2 * S + 6;   // local: this tile's table rows landed
+  uint64_t* tab_empty = bars + 2 * S + 7;  // local: every epilogue warp has read them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 8);
+  float* head_w = reinterpret_cast<float*>(bars + 32);  // head variant: [2][128] norm weights as f32
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -153,6 +173,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&acc_empty[i], 2 * kEpiWarps);  // the epilogue warps of both CTAs
       mbar_init(&res_full[i], 1);
     }
+    mbar_init(tab_full, 1);
+    mbar_init(tab_empty, kEpiWarps);
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_w);
@@ -160,6 +182,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
     tmem_relinquish_pair();
+  }
+  if (HEADS && threadIdx.x < 256) {
+    const T* wsrc = (const T*)(threadIdx.x < 128 ? p.norm_q : p.norm_k);
+    head_w[threadIdx.x] = wsrc != nullptr ? Elem<T>::to_f(wsrc[threadIdx.x & 127]) : 1.0f;
   }
   tc_fence_before();
   __syncthreads();
@@ -173,6 +199,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
+      uint32_t tab_ph = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += pairs) {
         int mt, nt;
@@ -197,6 +224,21 @@ __global__ void __launch_bounds__(kThreads, 1)
             s = 0;
             ph ^= 1;
           }
+        }
+        if (HEADS && ok && n0 < p.rope_width) {
+          // The rotation tables of this CTA's 128 rows, whole 128-byte rows by TMA
+          // (per-row 16-byte reads of them would compete with the operand stream).
+          // Issued after the tile's operands: the previous tile's epilogue has had
+          // the whole k loop to finish with the buffer.
+          if (!mbar_wait(tab_empty, tab_ph ^ 1, p.status)) {
+            ok = false;
+            break;
+          }
+          tab_ph ^= 1;
+          const int row0 = (int)((int64_t)m0 % p.rope_seq);
+          mbar_expect_tx(tab_full, (uint32_t)kTableBytes);
+          tma_load_2d(tables, &tmap_cos, tab_full, 0, row0);
+          tma_load_2d(tables + kTableBytes / 2, &tmap_sin, tab_full, 0, row0);
         }
       }
       // Error path: a bounded pause lets copies already in flight land before
@@ -283,6 +325,112 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int r_tile = quarter * 32 + lane;
       const int m0 = mt * 2 * BM + (int)rank * BM;
       const bool rows_live = m0 < p.m;  // a ragged last tile may leave the odd CTA no row
+      if constexpr (HEADS) {
+        // One 128-column head per column half: sum of squares over the head, then
+        // both halves of the head at once (a rotated column needs its partner 64
+        // columns away); the first half goes to the staging buffer, the second
+        // waits packed in registers until the first sub-tile's store has read it.
+        const int h_col = n0 + c_lo;
+        const bool tile_tables = n0 < p.rope_width;
+        const bool turned = h_col < p.rope_width;
+        const float* nw = h_col < p.norm_q_cols ? head_w : (h_col < p.norm_cols ? head_w + 128 : nullptr);
+        const uint32_t t_head = t_acc + (uint32_t)c_lo;
+        float inv = 1.f;
+        if (nw != nullptr) {
+          float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld32(t_head + (uint32_t)c, r0);
+            tmem_ld32(t_head + (uint32_t)(c + 32), r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              ss0 = fmaf(__uint_as_float(r0[i]), __uint_as_float(r0[i]), ss0);
+              ss1 = fmaf(__uint_as_float(r1[i]), __uint_as_float(r1[i]), ss1);
+            }
+          }
+          inv = rsqrtf((ss0 + ss1) * (1.0f / 128.0f) + p.norm_eps);
+        }
+        if (tile_tables) {
+          if (!mbar_wait(tab_full, res_phase, p.status)) ok = false;
+          res_phase ^= 1;  // the head variant has no residual: the phase bit serves the tables
+        }
+        if (chief) tma_store_wait_read();
+        named_barrier(1 + chalf, 128);
+        uint8_t* srow = stg + r_tile * 128;
+        const uint8_t* crow = tables + r_tile * 128;
+        const uint8_t* nrow = crow + kTableBytes / 2;
+        uint32_t keep[32];
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t_head + (uint32_t)(32 * hc), ra);
+          tmem_ld32(t_head + (uint32_t)(64 + 32 * hc), rb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int chunk = hc * 4 + v;  // 16-byte chunk of a 64-column row
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              a[i] = __uint_as_float(ra[v * 8 + i]);
+              b[i] = __uint_as_float(rb[v * 8 + i]);
+            }
+            if (nw != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                a[i] = a[i] * inv * nw[32 * hc + v * 8 + i];
+                b[i] = b[i] * inv * nw[64 + 32 * hc + v * 8 + i];
+              }
+            }
+            if (turned) {
+              const uint4 c4 = *reinterpret_cast<const uint4*>(crow + ((chunk ^ (r_tile & 7)) << 4));
+              const uint4 s4 = *reinterpret_cast<const uint4*>(nrow + ((chunk ^ (r_tile & 7)) << 4));
+              const uint32_t cu[4] = {c4.x, c4.y, c4.z, c4.w};
+              const uint32_t su[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 c2 = Elem<T>::unpack(cu[i]), s2 = Elem<T>::unpack(su[i]);
+                const float a0 = a[2 * i], a1 = a[2 * i + 1], b0 = b[2 * i], b1 = b[2 * i + 1];
+                a[2 * i] = a0 * c2.x - b0 * s2.x;
+                b[2 * i] = a0 * s2.x + b0 * c2.x;
+                a[2 * i + 1] = a1 * c2.y - b1 * s2.y;
+                b[2 * i + 1] = a1 * s2.y + b1 * c2.y;
+              }
+            }
+            *reinterpret_cast<uint4*>(srow + ((chunk ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(a[0], a[1]), Elem<T>::pack(a[2], a[3]), Elem<T>::pack(a[4], a[5]),
+                           Elem<T>::pack(a[6], a[7]));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) keep[chunk * 4 + i] = Elem<T>::pack(b[2 * i], b[2 * i + 1]);
+          }
+        }
+        if (tile_tables) {
+          // this warp has read its table rows
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tab_empty);
+        }
+        fence_proxy_async_smem();
+        named_barrier(1 + chalf, 128);
+        const bool live = rows_live && h_col < p.n;
+        if (chief && live) {
+          tma_store_2d(&tmap_c, stg, h_col, m0);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        named_barrier(1 + chalf, 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4)) =
+              make_uint4(keep[c * 4], keep[c * 4 + 1], keep[c * 4 + 2], keep[c * 4 + 3]);
+        fence_proxy_async_smem();
+        named_barrier(1 + chalf, 128);
+        if (chief && live && h_col + 64 < p.n) {
+          tma_store_2d(&tmap_c, stg, h_col + 64, m0);
+          tma_store_commit();
+        }
+      } else
       for (int sub = 0; sub < cols / 64; ++sub) {
         const int c0 = c_lo + sub * 64;
         const int n_at = rows_live ? n0 + c0 : p.n;  // past N: nothing is loaded or stored
@@ -362,8 +510,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-template <typename T>
+template <typename T, bool HEADS>
 int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) {
+  using C = Cfg2<HEADS>;
   Params2 p{};
   p.m = a.m, p.n = a.n, p.k = a.k;
   p.gated = a.gated, p.act = a.act, p.has_scale = a.has_scale, p.scale = a.scale;
@@ -380,10 +529,24 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   tr = tc;
   if (a.residual != nullptr && !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
     return -1;
+  CUtensorMap tcos = tc, tsin = tc;
+  if (HEADS) {
+    p.norm_q = a.norm_q, p.norm_k = a.norm_k;
+    p.norm_q_cols = a.norm_q != nullptr ? a.norm_q_heads * 128 : 0;
+    p.norm_cols = a.norm_k != nullptr ? (a.norm_q_heads + a.norm_k_heads) * 128 : p.norm_q_cols;
+    p.norm_eps = a.norm_eps;
+    p.rope_width = a.rope_cos != nullptr ? a.rope_heads * 128 : 0;
+    p.rope_seq = a.rope_seq > 0 ? a.rope_seq : 1;
+    if (a.rope_cos != nullptr) {
+      // [rope_seq rows, 64 columns] tables, one 128-row slab per CTA and tile
+      if (!make_tmap_2d(&tcos, a.rope_cos, dt, 64, (uint64_t)p.rope_seq, 64, 64, BM)) return -1;
+      if (!make_tmap_2d(&tsin, a.rope_sin, dt, 64, (uint64_t)p.rope_seq, 64, 64, BM)) return -1;
+    }
+  }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<T, HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)C::kSmemBytes) != cudaSuccess)
       return -1;
     attr_set = true;
   }
@@ -392,7 +555,7 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
   lc.blockDim = dim3(kThreads, 1, 1);
-  lc.dynamicSmemBytes = kSmemBytes;
+  lc.dynamicSmemBytes = C::kSmemBytes;
   lc.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -401,9 +564,9 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  if (cudaLaunchKernelEx(&lc, gemm_tc2_kernel<T>, ta, tw, tc, tr, p) != cudaSuccess) return -1;
+  if (cudaLaunchKernelEx(&lc, gemm_tc2_kernel<T, HEADS>, ta, tw, tc, tr, tcos, tsin, p) != cudaSuccess) return -1;
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d,cta_pair:1}", 2 * BM, BN, BK, kStages,
+    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d,cta_pair:1}", 2 * BM, BN, BK, C::kStages,
              a.gated, 2 * pairs);
   return 0;
 }
@@ -421,11 +584,17 @@ int sm_count2() {
 
 }  // namespace
 
-// The pair kernel takes what the one-CTA kernel covers, minus per-head stores,
-// once the problem has at least one 256 x 256 tile per CTA pair.
+// The pair kernel takes what the one-CTA kernel covers once the problem has at
+// least one 256 x 256 tile per CTA pair; per-head stores only for 128-wide heads
+// without a bias whose table rows never wrap inside a tile (the rest stays on the
+// one-CTA kernel).
 bool gemm_tc2_covers(const GemmArgs& a) {
   if (!gemm_tc_covers(a)) return false;
-  if (a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr) return false;
+  const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
+  if (heads) {
+    if (a.rope_head_dim != 128 || a.bias != nullptr) return false;
+    if (a.rope_cos != nullptr && (a.rope_seq <= 0 || a.rope_seq % BM != 0)) return false;
+  }
   const int out_bn = a.gated ? BN / 2 : BN;
   if (a.n < out_bn || a.m < 2 * BM) return false;
   const int64_t tiles = ((a.m + 2 * BM - 1) / (2 * BM)) * ((a.n + out_bn - 1) / out_bn);
@@ -440,7 +609,10 @@ bool gemm_tc2_preferred(const GemmArgs& a) { return gemm_tc2_covers(a) && a.k >=
 int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!gemm_tc2_covers(a)) return 1;
   const int sms = sm_count2();
-  return a.dtype == SVODB_BF16 ? run2<__nv_bfloat16>(a, sms, s, cfg, cfg_len) : run2<__half>(a, sms, s, cfg, cfg_len);
+  const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
+  if (a.dtype == SVODB_BF16)
+    return heads ? run2<__nv_bfloat16, true>(a, sms, s, cfg, cfg_len) : run2<__nv_bfloat16, false>(a, sms, s, cfg, cfg_len);
+  return heads ? run2<__half, true>(a, sms, s, cfg, cfg_len) : run2<__half, false>(a, sms, s, cfg, cfg_len);
 }
 
 }  // namespace svodb

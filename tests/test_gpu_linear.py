@@ -247,3 +247,49 @@ def test_long_k_projections_take_the_cta_pair_kernel_by_default():
     got = run_linear(x, w, dt)
     assert "cta_pair:1" in ops.chosen()
     assert rel_close(got, O.linear(x, w, dtype=dt), 1.6e-2)
+
+
+@pytest.mark.parametrize("dt,B,T,k,H,Hkv,qn,kn,rope", [
+    (O.BF16, 4, 1280, 1024, 4, 2, True, True, "shared"),      # 20 x 4 pair tiles, Qwen3's layout
+    (O.F16, 3, 2560, 1024, 2, 2, True, False, "per_batch"),   # tables per row of the batch
+    (O.BF16, 4, 1280, 1024, 4, 2, True, True, None),           # norm only
+    (O.BF16, 3, 1664, 1024, 4, 2, False, False, "shared"),     # rotation only, ragged last row tile
+])
+def test_qkv_prologue_on_the_cta_pair_kernel(dt, B, T, k, H, Hkv, qn, kn, rope):
+    """The attention prologue in the store of the CTA-pair kernel (rotation tables
+    TMA-loaded per tile) against `heads(linear(x, w))`, and against the one-CTA
+    head epilogue bit for bit."""
+    hd = 128
+    rng = np.random.default_rng(T + k)
+    n = (H + 2 * Hkv) * hd
+    x = O.round_to(dt, rng.standard_normal((B, T, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    qw = O.round_to(dt, 1 + 0.2 * rng.standard_normal(hd)) if qn else None
+    kw = O.round_to(dt, 1 + 0.2 * rng.standard_normal(hd)) if kn else None
+    cos = sin = None
+    if rope == "shared":
+        cos, sin = O.rope_table(1e6, np.arange(T), hd, dt)
+    elif rope == "per_batch":
+        pos = np.stack([(np.arange(T) * (b + 2)) % 997 for b in range(B)])
+        cos, sin = O.rope_table(1e6, pos.reshape(-1), hd, dt)
+        cos, sin = cos.reshape(B, T, hd // 2), sin.reshape(B, T, hd // 2)
+    q, kk, v = O.heads(O.linear(x, w, dtype=dt), H, Hkv, hd, qw, kw, 1e-6, cos, sin, dt)
+    want = np.concatenate([q.reshape(B, T, -1), kk.reshape(B, T, -1), v.reshape(B, T, -1)], axis=-1)
+    tabs = None
+    if cos is not None:
+        tabs = (dev(cos, dt).view(-1, T, 1, hd // 2), dev(sin, dt).view(-1, T, 1, hd // 2))
+    o = ops.Linear(qkv=ops.Qkv(H, Hkv, hd, dev(qw, dt) if qn else None, dev(kw, dt) if kn else None, 1e-6, tabs))
+    X, W = dev(x, dt), dev(w, dt)
+    got = host(ops.linear(X, W, o))
+    assert "cta_pair:1" in ops.chosen(), ops.chosen()
+    assert rel_close(got, want, 2e-2) and mean_rel(got, want) < 5e-3
+    from svod_b200 import _lib as L
+    lib = L.load()
+    key = lib.svodb_last_config_key()
+    lib.svodb_config_set(key, 256)
+    try:
+        one = host(ops.linear(X, W, o))
+        assert "cta_pair" not in ops.chosen() and "kernel gemm" in ops.chosen()
+    finally:
+        lib.svodb_config_set(key, 0)
+    assert max_abs(got, one) == 0.0
