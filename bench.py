@@ -459,6 +459,48 @@ def kernel_case(args):
                       "tflops": flops / ms / 1e9 if flops else None, "chosen": ops.chosen()}), flush=True)
 
 
+def sweep(args):
+    """The two kernel-level configurations of the baseline that are not model
+    steps: the f32 attention case (the exact CUDA-core path, with log-sum-exp)
+    and the GEMM sweep M in {512, 4096, 32768} x N=K in {768, 1024, 4096} with the
+    bias+GELU, bias+tanh-GELU and bias+SwiGLU epilogues. One JSON line per case."""
+    import torch
+    from svod_b200 import ops
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    stream = torch.cuda.current_stream()
+    if args.sweep == "attention-f32":
+        B, H, T, D = 2, 8, 512, 64
+        q, k, v = (torch.randn(B, T, H, D, generator=g, device="cuda") for _ in range(3))
+        lens = torch.randint(256, 513, (B,), generator=g, device="cuda", dtype=torch.int32)
+        a = ops.Attn(keys=ops.KeyMask.Lens(lens), scale=0.125, want_lse=True)
+        ms = time_kernel(lambda: ops.attention(q, k, v, a), stream, 20)
+        flops = 4 * H * D * T * int(lens.sum().item())
+        print(json.dumps({"case": "attention f32 B2 H8 T512 D64 key_lens + lse", "ms": ms,
+                          "gflops": flops / ms / 1e6, "chosen": ops.chosen()}), flush=True)
+        return
+    for m in (512, 4096, 32768):
+        for nk in (768, 1024, 4096):
+            x = (torch.randn(m, nk, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+            for name, act, gated in (("bias+gelu", ops.Act.GELU, False), ("bias+gelu_tanh", ops.Act.GELU_TANH, False),
+                                     ("bias+swiglu", ops.Act.SILU, True)):
+                rows = 2 * nk if gated else nk
+                w = (torch.randn(rows, nk, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+                b = (torch.randn(rows, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+                o = ops.Linear(bias=b, act=act, gated=gated)
+                ms = time_kernel(lambda: ops.linear(x, w, o), stream, 20)
+                flops = 2 * m * rows * nk
+                nbytes = 2 * (m * nk + rows * nk + m * nk) + 2 * rows
+                tf = flops / ms / 1e9
+                print(json.dumps({"case": f"gemm {name} M{m} N{nk} K{nk}", "ms": round(ms, 4), "tflops": round(tf, 1),
+                                  "min_gbs": round(nbytes / ms / 1e6, 1),
+                                  "frac_of_burst": round(tf / peaks["burst"], 3),
+                                  "frac_of_nominal_2250": round(tf / 2250.0, 3),
+                                  "chosen": ops.chosen().split("kernel gemm ")[-1]}), flush=True)
+    ops.device_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -473,9 +515,13 @@ def main():
     ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "rms_norm", "heads"],
                     help="run a few launches of one kernel on a small case (for profiler captures) and exit")
     ap.add_argument("--case-batch", type=int, default=4)
+    ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32"],
+                    help="time the kernel-level baseline configurations (one JSON line per case) and exit")
     args = ap.parse_args()
     if args.kernel_case:
         return kernel_case(args)
+    if args.sweep:
+        return sweep(args)
     if args.impl == "reference":
         reference_arm(args)
     else:
