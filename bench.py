@@ -371,6 +371,33 @@ def gpu_arm(args):
     ops.device_status()
     finite = bool(torch.isfinite(mine).all())
 
+    # The same step through the library's native runner (C ABI, host buffers in,
+    # host pooled rows out): no Python between the copies and the graph launch.
+    native = None
+    if kind == "qwen3" and rank == 0:
+        from svod_b200.native import NativeQwen3
+        ref_rows = mine.detach().cpu().numpy().copy()
+        del plan
+        plan = None
+        torch.cuda.empty_cache()
+        runner = NativeQwen3(model, reference_ops=args.reference_ops)
+        ids_np, len_np, out_np = ids_host.numpy(), aux_host.numpy(), out_host.numpy()
+        for _ in range(2):
+            runner.run(ids_np, len_np, out_np)
+        nstream = runner.stream(batch, seq)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(nstream)
+        for _ in range(args.steps):
+            runner.run(ids_np, len_np, out_np)
+        e1.record(nstream)
+        nstream.synchronize()
+        nms = e0.elapsed_time(e1) / args.steps
+        native = {"value": batch * seq / (nms * 1e-3), "unit": UNIT, "ms_per_step": nms,
+                  "api": "svodb_plan_run: host ids/lengths -> captured graph -> host pooled rows",
+                  "matches_python_stack": bool((out_np == ref_rows).all())}
+        runner.close()
+        ops.device_status()
+
     line = None
     if rank == 0:
         gemm_fl, attn_fl = step_flops(kind, batch, seq)
@@ -391,6 +418,8 @@ def gpu_arm(args):
             "step_tflops": (gemm_fl + attn_fl) / ms_step / 1e9,
             "output_finite": finite,
         }
+        if native is not None:
+            line["e2e_native"] = native
     del plan
     if world > 1:
         dist.barrier()

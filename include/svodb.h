@@ -252,6 +252,50 @@ int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, 
 int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,
                      svodb_tensor* sin, void* stream);
 
+/* ---- native model runner ------------------------------------------------------
+ * The Qwen3 embedding stack driven from compiled code, for hosts without a
+ * Python layer: what `Qwen3Model` + `HeadPlans` do in the reference
+ * (model/src/qwen3/{model,decoder_layer,attention,feed_forward}.rs;
+ * model/src/encoder_head.rs:384-500). A model borrows the caller's device
+ * weights; a plan owns one arena of activations, the RoPE tables and one captured
+ * CUDA graph for a `(rows, len)` shape on its own stream. */
+typedef struct svodb_qwen3_config {
+  int32_t vocab, hidden, layers, heads, kv_heads, head_dim, ffn;
+  int32_t dtype;    /* SVODB_BF16 / SVODB_F16 / SVODB_F32 of every weight */
+  double eps;       /* RMSNorm epsilon */
+  double rope_theta;
+} svodb_qwen3_config;
+
+/* Device pointers, dense row-major: in_w [hidden], qkv_w [(heads+2*kv_heads)*head_dim, hidden],
+ * qn_w, kn_w [head_dim], o_w [hidden, heads*head_dim], post_w [hidden],
+ * gu_w [2*ffn, hidden] (gate rows first), down_w [hidden, ffn]. */
+typedef struct svodb_qwen3_layer {
+  const void *in_w, *qkv_w, *qn_w, *kn_w, *o_w, *post_w, *gu_w, *down_w;
+} svodb_qwen3_layer;
+
+typedef struct svodb_qwen3_weights {
+  const void* embed;               /* [vocab, hidden] */
+  const svodb_qwen3_layer* layers; /* [cfg.layers] */
+  const void* norm_w;              /* [hidden] */
+} svodb_qwen3_weights;
+
+typedef struct svodb_qwen3 svodb_qwen3;
+typedef struct svodb_plan svodb_plan;
+
+int svodb_qwen3_create(const svodb_qwen3_config* cfg, const svodb_qwen3_weights* weights, svodb_qwen3** out);
+void svodb_qwen3_free(svodb_qwen3* model);
+/* Prepares the plan of one shape: allocates, runs once eagerly, captures.
+ * reference_ops != 0 keeps the reference's op sequence (projection, heads
+ * kernel, attention) instead of the prologue fused into the projection's store. */
+int svodb_qwen3_plan(svodb_qwen3* model, int64_t rows, int64_t len, int32_t reference_ops, svodb_plan** out);
+/* One batch: ids [rows, len] i32 and lengths [rows] i32 from host memory (NULL =
+ * keep what the plan holds), graph replay, pooled unit-norm rows [rows, hidden]
+ * f32 to host memory (NULL = leave them on the device and do not wait). */
+int svodb_plan_run(svodb_plan* plan, const int32_t* host_ids, const int32_t* host_lengths, float* host_out);
+void* svodb_plan_stream(svodb_plan* plan);   /* the plan's CUstream */
+float* svodb_plan_output(svodb_plan* plan);  /* device [rows, hidden] f32 */
+void svodb_plan_free(svodb_plan* plan);
+
 /* ---- device seam: what the `device` crate binds ----------------------------- */
 
 typedef struct svodb_program svodb_program;

@@ -97,6 +97,20 @@ class QkvOpts(C.Structure):
     ]
 
 
+class Qwen3Config(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("hidden", C.c_int32), ("layers", C.c_int32), ("heads", C.c_int32),
+                ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("ffn", C.c_int32), ("dtype", C.c_int32),
+                ("eps", C.c_double), ("rope_theta", C.c_double)]
+
+
+class Qwen3Layer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("in_w", "qkv_w", "qn_w", "kn_w", "o_w", "post_w", "gu_w", "down_w")]
+
+
+class Qwen3Weights(C.Structure):
+    _fields_ = [("embed", C.c_void_p), ("layers", C.POINTER(Qwen3Layer)), ("norm_w", C.c_void_p)]
+
+
 class AbiParam(C.Structure):
     _fields_ = [("slot", C.c_int32), ("kind", C.c_int32)]
 
@@ -112,6 +126,13 @@ SYMBOLS = [
     ("svodb_config_get", C.c_int32, [C.c_char_p]),
     ("svodb_config_clear", None, []),
     ("svodb_device_status", C.c_int, [C.c_void_p]),
+    ("svodb_qwen3_create", C.c_int, [C.POINTER(Qwen3Config), C.POINTER(Qwen3Weights), C.POINTER(C.c_void_p)]),
+    ("svodb_qwen3_free", None, [C.c_void_p]),
+    ("svodb_qwen3_plan", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
+    ("svodb_plan_run", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    ("svodb_plan_stream", C.c_void_p, [C.c_void_p]),
+    ("svodb_plan_output", C.c_void_p, [C.c_void_p]),
+    ("svodb_plan_free", None, [C.c_void_p]),
     ("svodb_linear", C.c_int, [TensorP, TensorP, C.POINTER(LinearOpts), TensorP, C.c_void_p]),
     ("svodb_attention_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     ("svodb_attention", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),

@@ -380,10 +380,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_expect_tx(&res_full[chalf], 128 * 128);
           tma_load_2d(stg, &tmap_r, &res_full[chalf], n_at, m0);
         }
-        float x[64];
+        // 32 columns at a time: accumulator -> epilogue math -> (+ residual) ->
+        // four 16-byte chunks of the swizzled staging row.
+        uint8_t* srow = stg + r_tile * 128;
+        const bool with_res = p.residual != nullptr && n_at < p.n;
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
-          float (&xs)[32] = *reinterpret_cast<float (*)[32]>(&x[32 * hc]);
+          float xs[32];
           acc32<T>(t_acc + (uint32_t)(c0 + 32 * hc), bias, n_at + 32 * hc, p.n, xs);
           act32(xs, p.act);
           if (p.gated) {
@@ -397,27 +400,29 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int i = 0; i < 32; ++i) xs[i] *= p.scale;
           }
-        }
-        if (p.residual != nullptr && n_at < p.n) {
-          if (!mbar_wait(&res_full[chalf], res_phase, p.status)) ok = false;
-          res_phase ^= 1;
-        }
-        uint8_t* srow = stg + r_tile * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4* slot = reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4));
-          if (p.residual != nullptr && n_at < p.n) {
-            const uint4 rv = *slot;
-            const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = Elem<T>::unpack(rr[i]);
-              x[c * 8 + 2 * i] += f.x;
-              x[c * 8 + 2 * i + 1] += f.y;
-            }
+          if (hc == 0 && with_res) {
+            // A timed-out wait is only recorded here: every thread of the half
+            // still walks both named barriers below, then leaves the tile loop.
+            if (!mbar_wait(&res_full[chalf], res_phase, p.status)) ok = false;
+            res_phase ^= 1;
           }
-          *slot = make_uint4(Elem<T>::pack(x[c * 8 + 0], x[c * 8 + 1]), Elem<T>::pack(x[c * 8 + 2], x[c * 8 + 3]),
-                             Elem<T>::pack(x[c * 8 + 4], x[c * 8 + 5]), Elem<T>::pack(x[c * 8 + 6], x[c * 8 + 7]));
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int c = hc * 4 + c4;  // chunk c of row r sits at (c ^ (r & 7))
+            uint4* slot = reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4));
+            if (with_res) {
+              const uint4 rv = *slot;
+              const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = Elem<T>::unpack(rr[i]);
+                xs[c4 * 8 + 2 * i] += f.x;
+                xs[c4 * 8 + 2 * i + 1] += f.y;
+              }
+            }
+            *slot = make_uint4(Elem<T>::pack(xs[c4 * 8 + 0], xs[c4 * 8 + 1]), Elem<T>::pack(xs[c4 * 8 + 2], xs[c4 * 8 + 3]),
+                               Elem<T>::pack(xs[c4 * 8 + 4], xs[c4 * 8 + 5]), Elem<T>::pack(xs[c4 * 8 + 6], xs[c4 * 8 + 7]));
+          }
         }
         fence_proxy_async_smem();
         named_barrier(1 + chalf, 128);

@@ -25,9 +25,17 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
                      const T* __restrict__ b, T* __restrict__ out, T* __restrict__ sum, int64_t rows, float eps,
                      int layer) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (row >= rows) return;
   constexpr int D = SPANS * 256;
+  // The weights (and bias) stay in registers across the rows a warp walks: read
+  // per row they would cost the load path as much as the row itself.
+  uint4 wreg[SPANS], breg[SPANS];
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    wreg[s] = ldg128(w + s * 256 + lane * 8);
+    breg[s] = b != nullptr ? ldg128(b + s * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+  }
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  for (int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); row < rows; row += stride) {
   const T* xr = x + row * D;
   float v[SPANS][8];
 #pragma unroll
@@ -77,13 +85,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 #pragma unroll
   for (int s = 0; s < SPANS; ++s) {
     const int off = s * 256 + lane * 8;
-    uint4 wu = ldg128(w + off);
-    const uint32_t ww[4] = {wu.x, wu.y, wu.z, wu.w};
-    uint32_t bb[4] = {0, 0, 0, 0};
-    if (b != nullptr) {
-      uint4 bu = ldg128(b + off);
-      bb[0] = bu.x, bb[1] = bu.y, bb[2] = bu.z, bb[3] = bu.w;
-    }
+    const uint32_t ww[4] = {wreg[s].x, wreg[s].y, wreg[s].z, wreg[s].w};
+    const uint32_t bb[4] = {breg[s].x, breg[s].y, breg[s].z, breg[s].w};
     uint32_t packed[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -98,6 +101,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
       packed[i] = Elem<T>::pack(y0, y1);
     }
     stg128(out + row * D + off, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+  }
   }
 }
 
@@ -152,7 +156,16 @@ __global__ void __launch_bounds__(256)
 
 template <typename T, int SPANS>
 void run_rows(const NormArgs& a, cudaStream_t s) {
-  const unsigned blocks = (unsigned)((a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  // A few resident blocks per SM walk the rows with a grid stride.
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int64_t want = (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const unsigned blocks = (unsigned)(want < (int64_t)sms * 6 ? want : (int64_t)sms * 6);
   norm_rows_kernel<T, SPANS><<<blocks, kWarpsPerBlock * 32, 0, s>>>(
       (const T*)a.x, (const T*)a.residual, (const T*)a.w, (const T*)a.b, (T*)a.out, (T*)a.sum, a.rows, a.eps, a.layer);
 }

@@ -190,3 +190,33 @@ def test_head_plans_bucket_capture_once_and_return_live_rows():
         assert max_abs(got, host(alone)[0]) < 2e-2
     out2 = EH.embed_chunks(plans, chunks[:2])          # another bucket: (2, 128)
     assert len(plans.plans) == 2 and max_abs(out2, out[:2]) < 2e-2
+
+
+@pytest.mark.parametrize("reference_ops", [False, True])
+def test_native_runner_equals_the_python_stack(reference_ops):
+    """`svodb_qwen3_*` / `svodb_plan_run`: the same ops in the same order issued
+    from compiled code under one captured graph give the same bits as the Python
+    stack, for host inputs changed between replays."""
+    from svod_b200.native import NativeQwen3
+    V, D, H, Hkv, hd, F, L, B, NL = 500, 256, 4, 2, 128, 384, 256, 3, 2
+    cfg = E.Qwen3Config(vocab_size=V, hidden_size=D, num_hidden_layers=NL, num_attention_heads=H,
+                        num_key_value_heads=Hkv, head_dim=hd, intermediate_size=F)
+    m = E.Qwen3Embedder.random_init(cfg, seed=3)
+    for lp in m.p["layers"]:  # non-trivial norm weights
+        for name in ("in_w", "post_w", "qn_w", "kn_w"):
+            lp[name].add_(torch.randn_like(lp[name]) * 0.05)
+    m.fused_prologue = not reference_ops
+    runner = NativeQwen3(m, reference_ops=reference_ops)
+    rng = np.random.default_rng(9)
+    for trial in range(2):
+        ids = rng.integers(0, V, (B, L)).astype(np.int32)
+        lengths = np.array([L, 17 + trial, 200], dtype=np.int32)
+        got = runner.run(ids, lengths)
+        want = m.forward(torch.from_numpy(ids).cuda(), torch.from_numpy(lengths).cuda()).cpu().numpy()
+        assert got.shape == (B, D) and np.array_equal(got, want)
+        assert np.allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-5)
+    runner.replay(B, L)
+    ops.device_status()
+    with pytest.raises(ops.OpsError):
+        NativeQwen3(m).plan(0, 16)
+    runner.close()
