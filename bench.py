@@ -488,6 +488,30 @@ def kernel_case(args):
                       "tflops": flops / ms / 1e9 if flops else None, "chosen": ops.chosen()}), flush=True)
 
 
+def time_graphed(fn, reps: int = 20):
+    """ms per call of `fn` with the host call path taken out: `reps` calls are
+    captured into one CUDA graph (after an eager warm-up) and the replay is timed."""
+    import torch
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            fn()
+    st.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        for _ in range(reps):
+            fn()
+    with torch.cuda.stream(st):
+        g.replay()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        g.replay()
+        e1.record(st)
+    st.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
 def sweep(args):
     """The two kernel-level configurations of the baseline that are not model
     steps: the f32 attention case (the exact CUDA-core path, with log-sum-exp)
@@ -504,7 +528,7 @@ def sweep(args):
         q, k, v = (torch.randn(B, T, H, D, generator=g, device="cuda") for _ in range(3))
         lens = torch.randint(256, 513, (B,), generator=g, device="cuda", dtype=torch.int32)
         a = ops.Attn(keys=ops.KeyMask.Lens(lens), scale=0.125, want_lse=True)
-        ms = time_kernel(lambda: ops.attention(q, k, v, a), stream, 20)
+        ms = time_graphed(lambda: ops.attention(q, k, v, a))
         flops = 4 * H * D * T * int(lens.sum().item())
         print(json.dumps({"case": "attention f32 B2 H8 T512 D64 key_lens + lse", "ms": ms,
                           "gflops": flops / ms / 1e6, "chosen": ops.chosen()}), flush=True)
@@ -518,7 +542,7 @@ def sweep(args):
                 w = (torch.randn(rows, nk, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
                 b = (torch.randn(rows, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
                 o = ops.Linear(bias=b, act=act, gated=gated)
-                ms = time_kernel(lambda: ops.linear(x, w, o), stream, 20)
+                ms = time_graphed(lambda: ops.linear(x, w, o))
                 flops = 2 * m * rows * nk
                 nbytes = 2 * (m * nk + rows * nk + m * nk) + 2 * rows
                 tf = flops / ms / 1e9

@@ -386,3 +386,19 @@ def test_cached_attention_matches_a_scalar_restatement(t, tk, hhd, row_map, appe
                     w = np.exp(np.array(sc) - max(sc))
                     want[b, i, h] = (w / w.sum()) @ np.array(vals)
     assert np.abs(got - want).max() < 1e-6
+
+
+# ---- committed fixtures -----------------------------------------------------------------------------
+def test_oracle_reproduces_the_committed_fixtures():
+    """`tests/golden/ops_golden.npz` (written by tests/golden/make_golden.py):
+    the oracle's outputs for seeded inputs, bit for bit."""
+    from tests.golden import make_golden as G
+    want, got = G.load(), G.build()
+    fresh = {}
+    for key, val in got.items():
+        fresh[key[2:] if key.startswith("i_") else key] = val
+    assert set(want) == set(fresh)
+    for key in want:
+        a = fresh[key]
+        a = (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64) if a.dtype == np.uint16 else a
+        assert np.array_equal(a, want[key]), key
