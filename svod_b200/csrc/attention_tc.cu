@@ -137,44 +137,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// 2^x for a pair of finite x <= ~2^7 on the FMA pipe (no MUFU): Cody-Waite
-// split x = n + f with n = round(x), |f| <= 0.5, a degree-3 minimax polynomial
-// for 2^f (max relative error 7.5e-5, below the 16-bit rounding of P) and n
-// added into the exponent field. The magic constant 1.5*2^23 leaves round(x) in
-// the low mantissa bits of r. Inputs below -126 give 2^-126 rather than 0, which
-// is why blocks that hide keys (whose hidden scores are -inf and must yield an
-// exact 0) do not use this path.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 r = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
-  const float2 n = __fadd2_rn(r, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.05517132207751274f, 0.05517132207751274f),
-                        make_float2(0.24261054396629333f, 0.24261054396629333f));
-  p = __ffma2_rn(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
-  p = __ffma2_rn(p, f, make_float2(0.9999281167984009f, 0.9999281167984009f));
-  p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
-  p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
-  return p;
-}
-
-#ifndef SVODB_FA_TURNS
-#define SVODB_FA_TURNS 1  // the two query tiles take turns on the MUFU unit
-#endif
-
-#ifndef SVODB_FA_HANDOVER
-#define SVODB_FA_HANDOVER 32  // score pairs (of 32) after which the MUFU unit is handed to the other tile
-#endif
-
-#ifndef SVODB_FA_PREFETCH_S
-#define SVODB_FA_PREFETCH_S 1  // request the next block's scores before publishing P
-#endif
-
-#ifndef SVODB_FA_POLY
-#define SVODB_FA_POLY 0  // of every 4 score pairs, how many take the polynomial 2^x
-#endif
-
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -516,7 +478,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     // A named barrier has no timeout, so a warp that gives up (a bounded wait
     // ran out) still walks the rest of the hand-over sequence below the loop
     // and its partner is never left waiting.
-    const int n_paired = SVODB_FA_TURNS ? min(r0.hi - r0.lo, r1.hi - r1.lo) : 0;
+    const int n_paired = min(r0.hi - r0.lo, r1.hi - r1.lo);
     const int my_turn = 1 + i * 4 + quarter;
     const int other_turn = 1 + (1 - i) * 4 + quarter;
     int turns_done = 0;  // hand-over steps this warp has completed
@@ -628,7 +590,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[32];
-#if SVODB_FA_POLY == 0
       // The MUFU unit takes one warp instruction every 8 cycles and returns its
       // result some tens of cycles later. All scaled scores are formed first,
       // then the 64 exponentials are issued back to back while the sums and the
@@ -647,13 +608,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           xs[k].x = ex2_approx(xs[k].x);
           xs[k].y = ex2_approx(xs[k].y);
         }
-        if (k == SVODB_FA_HANDOVER - 1 && SVODB_FA_HANDOVER < 32) {
-          // hand the MUFU unit over part-way: the other tile's first exponentials
-          // overlap this tile's last ones (the operand ties the arrival to the
-          // exponential it follows)
-          if (n < n_paired && (i == 0 || n + 1 < n_paired))
-            asm volatile("bar.arrive %0, 64;" ::"r"(other_turn), "f"(xs[k].y) : "memory");
-        }
         if (k >= kLag) {
           const int d = k - kLag;
           if (d & 1) lb = __fadd2_rn(lb, xs[d]);
@@ -661,45 +615,15 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
         }
       }
-#else
-      // The exponentials are split between the MUFU unit and a polynomial on the
-      // FMA pipe, which are otherwise the softmax's two unevenly loaded pipes.
-      // Blocks that hide keys keep every exponential on MUFU (exact zeros).
-      const bool poly = !need_mask;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 8) {
-          float2 x[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            x[q] = __ffma2_rn(make_float2(__uint_as_float(sr[c][e + 2 * q]), __uint_as_float(sr[c][e + 2 * q + 1])),
-                              sl2_2, nm_2);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (q < SVODB_FA_POLY && poly) {
-              x[q] = ex2_poly2(x[q]);
-            } else {
-              x[q].x = ex2_approx(x[q].x);
-              x[q].y = ex2_approx(x[q].y);
-            }
-          }
-          la = __fadd2_rn(la, __fadd2_rn(x[0], x[1]));
-          lb = __fadd2_rn(lb, __fadd2_rn(x[2], x[3]));
-#pragma unroll
-          for (int q = 0; q < 4; ++q) pk[16 * c + e / 2 + q] = Elem<T>::pack(x[q].x, x[q].y);
-        }
-      }
-#endif
       tmem_st32(s_tmem, pk);
       // tile 0 waits for tile 1's block n only if it has a paired block n+1
-      if (SVODB_FA_HANDOVER >= 32 && n < n_paired && (i == 0 || n + 1 < n_paired))
+      if (n < n_paired && (i == 0 || n + 1 < n_paired))
         named_barrier_arrive(other_turn, 64);
       turns_done = n + 1;
       l_run += (la.x + la.y) + (lb.x + lb.y);
       TRACE(warp - 3, n, 3);
       requested = false;
-      if (SVODB_FA_PREFETCH_S && n + 1 < nblk &&
+      if (n + 1 < nblk &&
           mbar_test_wait(&s_full[i * 2 + (buf ^ 1)], (uint32_t)(((n + 1) >> 1) & 1))) {
         tc_fence_after();
         const uint32_t next_tmem = tmem_base + (uint32_t)((i * 2 + (buf ^ 1)) * kBKV) + lane_addr;
