@@ -34,17 +34,21 @@ namespace {
 constexpr int BM = 128;  // rows per CTA (the pair's tile has 256)
 constexpr int BN = 256;  // accumulator columns
 constexpr int BK = 64;
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
+// Epilogue warps per CTA: 8 (two groups of four, 128 accumulator columns each)
+// or, where the epilogue math is heavy (an activation on a plain projection), 16
+// (four groups, 64 columns each) so that it stays shorter than the k loop.
 constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // A 16 KiB + this CTA's half of W 16 KiB
-constexpr int kStagingBytes = 2 * 128 * 128;
+constexpr int kGroupStaging = 128 * 128;  // one 128-row x 64-column sub-tile per epilogue group
 constexpr int kTableBytes = 2 * 128 * 128;  // head variant: this CTA's 128 rows of cos and of sin
 constexpr int kTmemCols = 512;
 // The head variant (attention prologue in the store) gives one pipeline stage up
 // for the rotation tables.
-template <bool HEADS>
+template <bool HEADS, int EW>
 struct Cfg2 {
-  static constexpr int kStages = HEADS ? 5 : 6;
+  static constexpr int kGroups = EW / 4;
+  static constexpr int kThreads = 32 * (2 + EW);
+  static constexpr int kStagingBytes = kGroups * kGroupStaging;
+  static constexpr int kStages = (HEADS || EW == 16) ? 5 : 6;
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kStagingBytes + (HEADS ? kTableBytes : 0) +
                                        1024 /*align*/ + 256 /*barriers*/ + (HEADS ? 1024 : 0) /*norm weights*/;
 };
@@ -73,13 +77,16 @@ struct Params2 {
 
 using namespace gemm_parts;
 
-template <typename T, bool HEADS>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, bool HEADS, int EW>
+__global__ void __launch_bounds__(32 * (2 + EW), 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
                     const __grid_constant__ CUtensorMap tmap_cos, const __grid_constant__ CUtensorMap tmap_sin,
                     const Params2 p) {
-  constexpr int S = Cfg2<HEADS>::kStages;
+  using C = Cfg2<HEADS, EW>;
+  constexpr int S = C::kStages;
+  constexpr int kEpiWarps = EW;
+  constexpr int kStagingBytes = C::kStagingBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + (size_t)S * kStageBytes;  // [2 halves][128 rows][128 B]
@@ -89,10 +96,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* empty = bars + S;              // [S]  in both CTAs
   uint64_t* acc_full = bars + 2 * S;       // [2]  in both CTAs
   uint64_t* acc_empty = bars + 2 * S + 2;  // [2]  used in the even CTA
-  uint64_t* res_full = bars + 2 * S + 4;   // [2 halves] local: residual sub-tile landed in staging
-  uint64_t* tab_full = bars + 2 * S + 6;   // local: this tile's table rows landed
-  uint64_t* tab_empty = bars + 2 * S + 7;  // local: every epilogue warp has read them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 8);
+  uint64_t* res_full = bars + 2 * S + 4;   // [4 groups] local: residual sub-tile landed in staging
+  uint64_t* tab_full = bars + 2 * S + 8;   // local: this tile's table rows landed
+  uint64_t* tab_empty = bars + 2 * S + 9;  // local: every epilogue warp has read them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 10);
   float* head_w = reinterpret_cast<float*>(bars + 32);  // head variant: [2][128] norm weights as f32
 
   const int warp = threadIdx.x >> 5;
@@ -111,8 +118,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 2 * kEpiWarps);  // the epilogue warps of both CTAs
-      mbar_init(&res_full[i], 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&res_full[i], 1);
     mbar_init(tab_full, 1);
     mbar_init(tab_empty, kEpiWarps);
     mbar_fence_init();
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- epilogue (both CTAs, each its 128 rows) ----------------
     const int ew = warp - 2;
     const int quarter = warp & 3;
-    const int chalf = ew >> 2;
+    const int chalf = ew >> 2;  // epilogue group: which slice of the tile's output columns
     const T* bias = (const T*)p.bias;
     int as = 0;
     uint32_t aph = 0;
@@ -252,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int mt, nt;
       tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
       const int n0 = nt * p.out_bn;
-      const int cols = p.out_bn / 2;
+      const int cols = p.out_bn / C::kGroups;
       const int c_lo = chalf * cols;
       if (!mbar_wait(&acc_full[as], aph, p.status)) {
         ok = false;
@@ -260,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
-      uint8_t* stg = staging + chalf * (128 * 128);
+      uint8_t* stg = staging + chalf * kGroupStaging;
       const bool chief = (ew & 3) == 0 && lane == 0;
       const int r_tile = quarter * 32 + lane;
       const int m0 = mt * 2 * BM + (int)rank * BM;
@@ -455,9 +462,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-template <typename T, bool HEADS>
+template <typename T, bool HEADS, int EW>
 int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) {
-  using C = Cfg2<HEADS>;
+  using C = Cfg2<HEADS, EW>;
   Params2 p{};
   p.m = a.m, p.n = a.n, p.k = a.k;
   p.gated = a.gated, p.act = a.act, p.has_scale = a.has_scale, p.scale = a.scale;
@@ -490,7 +497,7 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tc2_kernel<T, HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<T, HEADS, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)
       return -1;
     attr_set = true;
@@ -499,7 +506,7 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.blockDim = dim3(C::kThreads, 1, 1);
   lc.dynamicSmemBytes = C::kSmemBytes;
   lc.stream = s;
   cudaLaunchAttribute attr[1];
@@ -509,10 +516,10 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  if (cudaLaunchKernelEx(&lc, gemm_tc2_kernel<T, HEADS>, ta, tw, tc, tr, tcos, tsin, p) != cudaSuccess) return -1;
+  if (cudaLaunchKernelEx(&lc, gemm_tc2_kernel<T, HEADS, EW>, ta, tw, tc, tr, tcos, tsin, p) != cudaSuccess) return -1;
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d,cta_pair:1}", 2 * BM, BN, BK, C::kStages,
-             a.gated, 2 * pairs);
+    snprintf(cfg, cfg_len, "{bm:%d,bn:%d,bk:%d,stages:%d,gated:%d,grid:%d,cta_pair:1,epi_warps:%d}", 2 * BM, BN, BK,
+             C::kStages, a.gated, 2 * pairs, EW);
   return 0;
 }
 
@@ -549,15 +556,26 @@ bool gemm_tc2_covers(const GemmArgs& a) {
 // Where the pair kernel is the default: long enough k loops to pay for the
 // pair's extra hand-shakes per tile (measured: ahead from K = 1024 on, behind
 // at K = 768); a config store may still choose either kernel per shape.
-bool gemm_tc2_preferred(const GemmArgs& a) { return gemm_tc2_covers(a) && a.k >= 1024; }
+bool gemm_tc2_preferred(const GemmArgs& a) {
+  if (!gemm_tc2_covers(a)) return false;
+  // an activation on a plain projection runs the sixteen-warp epilogue, which pays from shorter k loops on
+  const bool wide = !a.gated && a.act != kActNone && a.rope_cos == nullptr && a.norm_q == nullptr && a.norm_k == nullptr;
+  return a.k >= 1024 || (wide && a.k >= 512);
+}
 
 int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!gemm_tc2_covers(a)) return 1;
   const int sms = sm_count2();
   const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
+  // sixteen epilogue warps where each output value costs an activation
+  const bool wide = !heads && !a.gated && a.act != kActNone;
   if (a.dtype == SVODB_BF16)
-    return heads ? run2<__nv_bfloat16, true>(a, sms, s, cfg, cfg_len) : run2<__nv_bfloat16, false>(a, sms, s, cfg, cfg_len);
-  return heads ? run2<__half, true>(a, sms, s, cfg, cfg_len) : run2<__half, false>(a, sms, s, cfg, cfg_len);
+    return heads  ? run2<__nv_bfloat16, true, 8>(a, sms, s, cfg, cfg_len)
+           : wide ? run2<__nv_bfloat16, false, 16>(a, sms, s, cfg, cfg_len)
+                  : run2<__nv_bfloat16, false, 8>(a, sms, s, cfg, cfg_len);
+  return heads  ? run2<__half, true, 8>(a, sms, s, cfg, cfg_len)
+         : wide ? run2<__half, false, 16>(a, sms, s, cfg, cfg_len)
+                : run2<__half, false, 8>(a, sms, s, cfg, cfg_len);
 }
 
 }  // namespace svodb

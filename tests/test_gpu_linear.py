@@ -208,6 +208,8 @@ def test_qkv_prologue_excludes_the_other_epilogues():
     (4964, 1000, 256, dict(bias=True, residual=True, scale=0.5)),  # ragged rows (the odd CTA of the last tile is empty) and columns
     (4864, 512, 256, dict(act=2, gated=True)),                   # SwiGLU: gate rows in the even CTA, up rows in the odd one
     (9728, 512, 192, dict(bias=True, act=2, gated=True, residual=True)),
+    (4964, 1000, 512, dict(bias=True, act=1, residual=True, scale=0.5)),  # sixteen epilogue warps, ragged, residual
+    (4864, 1024, 512, dict(act=3)),                                        # tanh GELU, four column groups
 ])
 def test_cta_pair_gemm_matches_the_oracle(m, n, k, kw):
     """Shapes with at least one 256 x 256 tile per CTA pair run the
@@ -221,12 +223,14 @@ def test_cta_pair_gemm_matches_the_oracle(m, n, k, kw):
     b = O.round_to(dt, rng.standard_normal((2 if gated else 1) * n)) if kw.get("bias") else None
     r = O.round_to(dt, rng.standard_normal((m, n))) if kw.get("residual") else None
     want = O.linear(x, w, b, act=kw.get("act", 0), gated=gated, residual=r, scale=kw.get("scale"), dtype=dt)
-    # short k loops default to the one-CTA kernel (same k order, same epilogue)
-    one = run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
-    assert "cta_pair" not in ops.chosen()
+    # the one-CTA kernel (config code 256): same k order, same epilogue
     from svod_b200 import _lib as L
     lib = L.load()
+    run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
     key = lib.svodb_last_config_key()
+    lib.svodb_config_set(key, 256)
+    one = run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
+    assert "cta_pair" not in ops.chosen()
     lib.svodb_config_set(key, 512)  # the config store's code for the pair kernel
     try:
         got = run_linear(x, w, dt, b, kw.get("act", 0), gated, r, kw.get("scale"))
