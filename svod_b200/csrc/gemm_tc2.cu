@@ -568,7 +568,8 @@ int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len
   const int sms = sm_count2();
   const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
   // sixteen epilogue warps where each output value costs an activation
-  const bool wide = !heads && !a.gated && a.act != kActNone;
+  // (long k loops hide the epilogue anyway and prefer the deeper ring of the eight-warp variant)
+  const bool wide = !heads && !a.gated && a.act != kActNone && a.k <= 2048;
   if (a.dtype == SVODB_BF16)
     return heads  ? run2<__nv_bfloat16, true, 8>(a, sms, s, cfg, cfg_len)
            : wide ? run2<__nv_bfloat16, false, 16>(a, sms, s, cfg, cfg_len)
