@@ -171,6 +171,50 @@ def time_cpu(kind: str, steps: int, warmup: int, seq: int = 512, layers: int = 4
     return tokens / full, full * 1e3, sample
 
 
+def time_torch_cpu(seq: int = 512, layers: int = 4, full_layers: int = 28, steps: int = 1):
+    """A second, separately labelled CPU reference point (not svod, not the
+    oracle): the Qwen3-shaped layer in plain PyTorch f32 CPU ops
+    (`F.linear`, `F.scaled_dot_product_attention`) on the same bounded sample,
+    with all the threads torch will use."""
+    import torch
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(7)
+    D, H, Hkv, hd, Fn = 1024, 16, 8, 128, 3072
+    r = lambda *sh: torch.randn(*sh, generator=g) * 0.02
+    ws = [dict(qkv=r((H + 2 * Hkv) * hd, D), o=r(D, H * hd), gu=r(2 * Fn, D), down=r(D, Fn)) for _ in range(layers)]
+    x0 = torch.randn(1, seq, D, generator=g)
+    ang = torch.arange(seq)[:, None] * (1e6 ** (-torch.arange(0, hd, 2) / hd))[None, :]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    rms = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6)
+
+    def rot(t):
+        a, b = t[..., :hd // 2], t[..., hd // 2:]
+        return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+
+    def run():
+        x = x0
+        with torch.no_grad():
+            for w in ws:
+                qkv = F.linear(rms(x), w["qkv"]).view(1, seq, H + 2 * Hkv, hd)
+                q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+                q, k = rot(rms(q)), rot(rms(k))
+                k, v = k.repeat_interleave(H // Hkv, 2), v.repeat_interleave(H // Hkv, 2)
+                a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                   is_causal=True).transpose(1, 2).reshape(1, seq, H * hd)
+                h = x + F.linear(a, w["o"])
+                gu = F.linear(rms(h), w["gu"])
+                x = h + F.linear(F.silu(gu[..., :Fn]) * gu[..., Fn:], w["down"])
+        return x
+
+    run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / steps * full_layers / layers
+    return {"value": seq / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "torch f32 CPU ops (not svod)",
+            "sample": f"1 sequence x {seq} tokens, {layers} of {full_layers} layers timed and scaled"}
+
+
 def reference_arm(args):
     """`--impl reference`: the reference's own CPU path cannot be built here (no
     Rust toolchain), so the arm times the CPU restatement of the same path on
@@ -440,7 +484,7 @@ def gpu_arm(args):
             v, ms, sample = time_cpu("qwen3", 1, 0) if kind == "qwen3" else (None, None, None)
             if v is not None:
                 line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
-                                        "sample": sample}
+                                        "sample": sample, "second_point": time_torch_cpu()}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

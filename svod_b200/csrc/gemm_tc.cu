@@ -76,6 +76,7 @@ struct Params {
   // `norm_k` below norm_cols, none above; then the rotation for columns below
   // rope_width; staged and TMA-stored like the plain epilogue.
   int head_epilogue;
+  int head64_epilogue;  // the same for 64-wide heads: one head per 64-column sub-tile
   const void* norm_q;
   const void* norm_k;
   int norm_q_cols, norm_cols;
@@ -166,9 +167,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
-  if (p.head_epilogue && threadIdx.x < 256) {
+  if ((p.head_epilogue || p.head64_epilogue) && threadIdx.x < 256) {
     const T* wsrc = (const T*)(threadIdx.x < 128 ? p.norm_q : p.norm_k);
-    head_w[threadIdx.x] = wsrc != nullptr ? Elem<T>::to_f(wsrc[threadIdx.x & 127]) : 1.0f;
+    const int at = threadIdx.x & 127;
+    head_w[threadIdx.x] = (wsrc != nullptr && at < p.rope_head_dim) ? Elem<T>::to_f(wsrc[at]) : 1.0f;
   }
   tc_fence_before();
   __syncthreads();
@@ -385,6 +387,80 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (!ok) break;
+      } else if (p.head64_epilogue) {
+        // 64-wide heads: every 64-column sub-tile is one head with both rotation
+        // halves in it; norm and rotation from the accumulator, staged, TMA-stored.
+        uint8_t* stg = staging + chalf * (128 * 128);
+        const bool chief = (ew & 3) == 0 && lane == 0;
+        const int r_tile = quarter * 32 + lane;
+        const int m0 = mt * BM;
+        const T* cos = (const T*)p.rope_cos;
+        const T* sin = (const T*)p.rope_sin;
+        const int64_t pos = row_ok ? row % p.rope_seq : 0;
+        for (int sub = 0; sub < cols / 64; ++sub) {
+          const int c0 = c_lo + sub * 64;
+          const int h_col = n0 + c0;
+          const bool turned = h_col < p.rope_width;
+          const float* nw = h_col < p.norm_q_cols ? head_w : (h_col < p.norm_cols ? head_w + 128 : nullptr);
+          float a[32], b[32];
+          acc32<T>(t_acc + (uint32_t)c0, bias, h_col, p.n, a);
+          acc32<T>(t_acc + (uint32_t)(c0 + 32), bias, h_col + 32, p.n, b);
+          uint4 cs4[4], sn4[4];
+          if (turned) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              cs4[v] = ldg128(cos + pos * 32 + v * 8);
+              sn4[v] = ldg128(sin + pos * 32 + v * 8);
+            }
+          }
+          if (nw != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ss = fmaf(a[i], a[i], fmaf(b[i], b[i], ss));
+            const float inv = rsqrtf(ss * (1.0f / 64.0f) + p.norm_eps);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              a[i] = a[i] * inv * nw[i];
+              b[i] = b[i] * inv * nw[32 + i];
+            }
+          }
+          if (turned) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint32_t cu[4] = {cs4[v].x, cs4[v].y, cs4[v].z, cs4[v].w};
+              const uint32_t su[4] = {sn4[v].x, sn4[v].y, sn4[v].z, sn4[v].w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 c2 = Elem<T>::unpack(cu[i]), s2 = Elem<T>::unpack(su[i]);
+                const int e = v * 8 + 2 * i;
+                const float a0 = a[e], a1 = a[e + 1], b0 = b[e], b1 = b[e + 1];
+                a[e] = a0 * c2.x - b0 * s2.x;
+                b[e] = a0 * s2.x + b0 * c2.x;
+                a[e + 1] = a1 * c2.y - b1 * s2.y;
+                b[e + 1] = a1 * s2.y + b1 * c2.y;
+              }
+            }
+          }
+          // the previous store out of this buffer must have read it
+          if (chief) tma_store_wait_read();
+          named_barrier(1 + chalf, 128);
+          uint8_t* srow = stg + r_tile * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            *reinterpret_cast<uint4*>(srow + ((c ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(a[c * 8 + 0], a[c * 8 + 1]), Elem<T>::pack(a[c * 8 + 2], a[c * 8 + 3]),
+                           Elem<T>::pack(a[c * 8 + 4], a[c * 8 + 5]), Elem<T>::pack(a[c * 8 + 6], a[c * 8 + 7]));
+            *reinterpret_cast<uint4*>(srow + (((c + 4) ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(b[c * 8 + 0], b[c * 8 + 1]), Elem<T>::pack(b[c * 8 + 2], b[c * 8 + 3]),
+                           Elem<T>::pack(b[c * 8 + 4], b[c * 8 + 5]), Elem<T>::pack(b[c * 8 + 6], b[c * 8 + 7]));
+          }
+          fence_proxy_async_smem();
+          named_barrier(1 + chalf, 128);
+          if (chief && h_col < p.n) {
+            tma_store_2d(&tmap_c, stg, h_col, m0);
+            tma_store_commit();
+          }
+        }
       } else if (p.head_epilogue) {
         // One 128-column head per column half. A first pass over the accumulator
         // takes the sum of squares; the second forms both halves of the head at
@@ -570,7 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
-  if ((p.tma_epilogue || p.head_epilogue) && warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
+  if ((p.tma_epilogue || p.head_epilogue || p.head64_epilogue) && warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -598,8 +674,10 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
   p.tma_epilogue = (p.out_bn >= 128 && !per_head) ? 1 : 0;
   // Heads of 128 columns are one column half of a 256-wide tile: staged too.
   p.head_epilogue = (per_head && a.rope_head_dim == 128 && p.out_bn == 256) ? 1 : 0;
+  // Heads of 64 columns are one sub-tile each (the tile's column halves hold 1 or 2 of them).
+  p.head64_epilogue = (per_head && a.rope_head_dim == 64 && p.out_bn >= 128) ? 1 : 0;
   CUtensorMap tc = ta, tr = ta;
-  if (p.tma_epilogue || p.head_epilogue) {
+  if (p.tma_epilogue || p.head_epilogue || p.head64_epilogue) {
     if (!make_tmap_2d(&tc, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, BM)) return -1;
     tr = tc;
     if (a.residual != nullptr &&
@@ -666,8 +744,8 @@ bool gemm_tc_covers(const GemmArgs& a) {
     if (!aligned16(a.rope_cos) || !aligned16(a.rope_sin)) return false;
   }
   if (a.norm_q != nullptr || a.norm_k != nullptr) {
-    // The per-head norm lives in the staged head epilogue: 128-column heads.
-    if (a.rope_head_dim != 128) return false;
+    // The per-head norm lives in the staged head epilogues: 64- or 128-column heads.
+    if (a.rope_head_dim != 128 && a.rope_head_dim != 64) return false;
     if (a.gated || a.act != kActNone || a.residual != nullptr || a.has_scale) return false;
     if ((a.norm_q != nullptr && !aligned16(a.norm_q)) || (a.norm_k != nullptr && !aligned16(a.norm_k))) return false;
   }
