@@ -674,6 +674,14 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
       return fail(SVODB_ERR_GRAPH, "%s: a split attention writes a contiguous output", OP);
   }
   char cfg[128];
+  if (attention_tc_p_covers(a) && config_lookup("attention|one_item") == 0) {
+    int rc = launch_attention_tc_p(a, s, cfg, sizeof cfg);
+    if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+    if (rc == 0) {
+      chose_kernel(OP, packed ? "flash_attention_packed" : "flash_attention", cfg);
+      return check_launch(OP);
+    }
+  }
   if (attention_tc_covers(a)) {
     int rc = launch_attention_tc(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);

@@ -46,6 +46,7 @@
 #include <math.h>
 #include <stdio.h>
 
+#include "attention_parts.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "svodb.h"
@@ -55,93 +56,7 @@ namespace svodb {
 
 namespace {
 
-constexpr int kBQ = 128;   // rows per query tile (two tiles per CTA)
-constexpr int kBKV = 64;   // keys per block
-constexpr int kThreadsFa = 384;
-constexpr float kLog2eF = 1.4426950408889634f;
-constexpr float kLn2F = 0.6931471805599453f;
-constexpr float kRescaleAbove = 8.0f;
-constexpr int kMaxMaskWords = 2048;  // general key mask: up to 65536 keys
-
-template <int D>
-struct FaCfg {
-  static constexpr int kQTileBytes = 128 * D * 2;   // one 128-row Q tile
-  static constexpr int kKvBytes = kBKV * D * 2;     // one K or V block
-  static constexpr int kStages = 4;
-  static constexpr size_t kSmemBytes =
-      1024 + (size_t)2 * kQTileBytes + (size_t)2 * kStages * kKvBytes + (size_t)kMaxMaskWords * 4 + 512;
-};
-
-struct FaParams {
-  void* o;
-  int64_t o_sb, o_st, o_sh;
-  int64_t t, tk;
-  int heads, kv_heads;
-  float scale_log2;
-  int causal;
-  const int32_t* key_lens;
-  const void* key_mask;
-  int key_mask_i32;
-  int has_window;
-  int64_t win_left, win_right;
-  int has_chunk;
-  int64_t chunk_size, chunk_left, chunk_right;
-  const int32_t* seg_start;
-  const int32_t* row_map;  // `ops::Cache`: cache row of batch lane b, or null
-  float* lse;
-  int n_qt;  // query tile pairs per (head, batch)
-  uint32_t* status;
-};
-
-struct Range {
-  int lo, hi;  // key blocks [lo, hi)
-};
-
-// The mask context shared by every role of a CTA.
-struct Ctx {
-  int64_t len;       // visible key count bound: min(Tk, key_lens[b] or the prefix mask's length)
-  int general_mask;  // the key mask is not a prefix: consult the bitmask
-};
-
-__device__ __forceinline__ Range tile_range(const FaParams& p, const Ctx& c, int64_t b, int64_t i_first) {
-  Range r{0, 0};
-  if (i_first >= p.t) return r;
-  const int64_t i_last = (i_first + kBQ - 1 < p.t - 1) ? i_first + kBQ - 1 : p.t - 1;
-  int64_t lo = 0, hi = c.len;
-  if (p.causal && i_last + 1 < hi) hi = i_last + 1;
-  if (p.has_window) {
-    if (i_first - p.win_left > lo) lo = i_first - p.win_left;
-    if (i_last + p.win_right + 1 < hi) hi = i_last + p.win_right + 1;
-  }
-  if (p.has_chunk) {
-    const int64_t h2 = (i_last / p.chunk_size + p.chunk_right + 1) * p.chunk_size;
-    if (h2 < hi) hi = h2;
-    if (p.chunk_left >= 0) {
-      const int64_t l2 = (i_first / p.chunk_size - p.chunk_left) * p.chunk_size;
-      if (l2 > lo) lo = l2;
-    }
-  }
-  if (p.seg_start != nullptr) {
-    const int64_t s = p.seg_start[b * p.t + i_first];
-    if (s > lo) lo = s;
-  }
-  if (hi <= lo) return r;
-  r.lo = (int)(lo / kBKV);
-  r.hi = (int)((hi + kBKV - 1) / kBKV);
-  return r;
-}
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
+using namespace fa_parts;
 
 #ifdef SVODB_TRACE
 // Timeline probe (debug builds only): clock() stamps of CTA (0,0,0).

@@ -1,0 +1,689 @@
+// Persistent form of the tcgen05 flash-attention forward (attention_tc.cu): one
+// CTA per SM walks a queue of (256 query rows, head, batch) work items instead
+// of one item per CTA, so that an item's fixed costs — launch, barrier and TMEM
+// set-up, the first Q/K/V round trip, the pipeline ramp, the O read-out and
+// store — overlap the neighbouring items' work instead of adding to it. With
+// one CTA per SM (shared memory and tensor memory are both full) nothing else
+// can overlap them: at 4096 keys they are about a fifth of a causal item.
+//
+// Same math, same roles and the same TMEM / shared-memory layout as the
+// one-item kernel (see its header). What changes:
+//   * a work queue: the loader takes the next item off an atomic counter and
+//     publishes it through a two-slot ring (`item_full` / `item_empty`); items
+//     are ordered so that CTAs running together share K/V in L2 (batch, KV head,
+//     then query tiles from the heaviest) and the light tiles come last;
+//   * every barrier phase comes from running counters (blocks loaded, blocks
+//     per tile, tail commits, live items per tile) instead of the block index
+//     inside one item;
+//   * `q_empty` (the issuer's last QK of an item frees the Q tile for the
+//     loader) and `o_empty` (the softmax warps have read O out, the next item's
+//     first P.V may overwrite it): the loader and the issuers run into the next
+//     item while the softmax warps still finish the last one.
+// Covers what the one-item kernel covers except a bool key mask (its per-item
+// scan needs the whole CTA): those calls keep the one-item kernel.
+#include <cuda.h>
+#include <math.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "attention_parts.cuh"
+#include "common.cuh"
+#include "kernels.h"
+#include "svodb.h"
+#include "tensormap.h"
+
+namespace svodb {
+
+namespace {
+
+using namespace fa_parts;
+
+// Queue heads: items handed out so far by a running launch. Every launch takes
+// the next slot (zeroed on its stream just before it), so launches in flight at
+// the same time on different streams do not share a head as long as fewer than
+// kQueueSlots of them are alive at once.
+constexpr int kQueueSlots = 256;
+__device__ int g_next_item[kQueueSlots];
+
+struct Item {
+  int qt, h, b, valid;
+};
+
+// Work item w in queue order: batch, KV head, query head of the group, then
+// query tile pairs from the last (the heaviest under a causal mask) to the first.
+__device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads) {
+  Item it{0, 0, 0, 0};
+  if (w >= n_items) return it;
+  const int group = heads / kv_heads;
+  const int per_kv = group * n_qt;
+  const int kvb = w / per_kv;  // (batch, kv head)
+  const int r = w - kvb * per_kv;
+  it.qt = n_qt - 1 - r / group;
+  it.h = (kvb % kv_heads) * group + r % group;
+  it.b = kvb / kv_heads;
+  it.valid = 1;
+  return it;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreadsFa, 1)
+    attention_tc_p_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const int n_items,
+                          int* const queue) {
+  using C = FaCfg<D>;
+  constexpr int S = C::kStages;
+  constexpr int QB = C::kQTileBytes;
+  constexpr int KB = C::kKvBytes;
+  constexpr int KBOX = kBKV * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;                         // [2][QB]
+  uint8_t* k_s = q_s + 2 * QB;                 // [S][KB]
+  uint8_t* v_s = k_s + S * KB;                 // [S][KB]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + S * KB);
+  uint64_t* q_full = bars;                     // [2]
+  uint64_t* q_empty = bars + 2;                // [2]
+  uint64_t* k_full = bars + 4;                 // [S]
+  uint64_t* k_empty = k_full + S;
+  uint64_t* v_full = k_empty + S;
+  uint64_t* v_empty = v_full + S;
+  uint64_t* s_full = v_empty + S;              // [2 tiles][2 buffers]
+  uint64_t* p_full = s_full + 4;               // [2 tiles][2 buffers]
+  uint64_t* tail_done = p_full + 4;            // [2 tiles]
+  uint64_t* o_empty = tail_done + 2;           // [2 tiles]
+  uint64_t* item_full = o_empty + 2;           // [2 slots]
+  uint64_t* item_empty = item_full + 2;        // [2 slots]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_empty + 2);
+  Item* item_ring = reinterpret_cast<Item*>(tmem_slot + 4);  // [2]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&tail_done[i], 1);
+      mbar_init(&o_empty[i], 4);      // the tile's four softmax warps
+      mbar_init(&item_full[i], 1);
+      mbar_init(&item_empty[i], 10);  // two issuers + eight softmax warps
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+    }
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 2);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 2);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // What every role derives from an item: the key-block ranges of its two tiles.
+  struct Work {
+    int h, hk;
+    int64_t b, i0;
+    Ctx ctx;
+    Range r0, r1;
+    bool live0, live1;
+    int u_lo, u_hi;
+  };
+  auto plan = [&](const Item& it) -> Work {
+    Work w;
+    w.h = it.h;
+    w.hk = it.h / (p.heads / p.kv_heads);
+    w.b = it.b;
+    w.i0 = (int64_t)it.qt * 2 * kBQ;
+    w.ctx.len = p.tk;
+    w.ctx.general_mask = 0;
+    if (p.key_lens != nullptr) {
+      const int64_t kl = p.key_lens[it.b];
+      w.ctx.len = kl < 0 ? 0 : (kl < w.ctx.len ? kl : w.ctx.len);
+    }
+    w.r0 = tile_range(p, w.ctx, w.b, w.i0);
+    w.r1 = tile_range(p, w.ctx, w.b, w.i0 + kBQ);
+    w.live0 = w.r0.hi > w.r0.lo;
+    w.live1 = w.r1.hi > w.r1.lo;
+    w.u_lo = 0, w.u_hi = 0;
+    if (w.live0 && w.live1) {
+      w.u_lo = w.r0.lo < w.r1.lo ? w.r0.lo : w.r1.lo;
+      w.u_hi = w.r0.hi > w.r1.hi ? w.r0.hi : w.r1.hi;
+    } else if (w.live0) {
+      w.u_lo = w.r0.lo, w.u_hi = w.r0.hi;
+    } else if (w.live1) {
+      w.u_lo = w.r1.lo, w.u_hi = w.r1.hi;
+    }
+    return w;
+  };
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 0) {
+      // ---------------- scheduler + TMA loader ----------------
+      if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;
+        uint32_t q_items[2] = {0, 0};  // live items so far, per tile
+        bool ok = true;
+        for (uint32_t n_it = 0; ok; ++n_it) {
+          const int slot = (int)(n_it & 1);
+          if (!mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) break;
+          const Item it = decode_item(atomicAdd(queue, 1), n_items, p.n_qt, p.heads, p.kv_heads);
+          item_ring[slot] = it;
+          __threadfence_block();
+          mbar_arrive(&item_full[slot]);
+          if (!it.valid) break;
+          const Work w = plan(it);
+          if (w.u_hi <= w.u_lo) continue;
+          for (int i = 0; i < 2; ++i) {
+            if (i == 0 ? w.live0 : w.live1) {
+              // the issuer's last QK of the tile's previous live item has read this Q tile
+              if (!mbar_wait(&q_empty[i], (q_items[i] & 1) ^ 1, p.status)) {
+                ok = false;
+                break;
+              }
+              ++q_items[i];
+              mbar_expect_tx(&q_full[i], QB);
+              for (int c = 0; c < D / 64; ++c)
+                tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, w.h, (int)(w.i0 + i * kBQ),
+                            (int)w.b);
+            }
+          }
+          const int kv_b = p.row_map != nullptr ? p.row_map[w.b] : (int)w.b;
+          for (int j = w.u_lo; j < w.u_hi && ok; ++j) {
+            if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&k_full[s], KB);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(k_s + s * KB + c * KBOX, &tmap_k, &k_full[s], c * 64, w.hk, j * kBKV, kv_b);
+            if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&v_full[s], KB);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(v_s + s * KB + c * KBOX, &tmap_v, &v_full[s], c * 64, w.hk, j * kBKV, kv_b);
+            if (++s == S) {
+              s = 0;
+              ph ^= 1;
+            }
+          }
+        }
+        if (!ok) {
+          // Error path: give copies in flight a bounded time to land.
+          for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+      }
+    } else if (warp == 1 || warp == 3) {
+      // ---------------- MMA issuers: warp 1 drives tile 0, warp 3 tile 1 ----------------
+      const int i = warp == 1 ? 0 : 1;
+      const bool leader = elect_one();
+      constexpr uint32_t idesc_qk = umma_idesc(Elem<T>::kUmmaFormat, 128, kBKV, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(Elem<T>::kUmmaFormat, 128, D, 0, 1);
+      const uint64_t qa = umma_desc_sw128(smem_u32(q_s) + i * QB, 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_s), 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_s), KBOX, 1024);
+      uint32_t kv_blocks = 0;  // K/V blocks of all earlier items (ring position)
+      uint32_t my_blocks = 0;  // blocks of this tile in all earlier items (S/P buffer and phase)
+      uint32_t my_items = 0;   // live items of this tile so far
+      bool ok = true;
+      for (uint32_t n_it = 0; ok; ++n_it) {
+        const int slot = (int)(n_it & 1);
+        if (!mbar_wait(&item_full[slot], (n_it >> 1) & 1, p.status)) break;
+        const Item it = item_ring[slot];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&item_empty[slot]);
+        if (!it.valid) break;
+        const Work w = plan(it);
+        if (w.u_hi <= w.u_lo) continue;
+        const Range r = i == 0 ? w.r0 : w.r1;
+        const int nblk = r.hi - r.lo;
+        const bool live = nblk > 0;
+        bool q_ready = false;
+        for (int t = w.u_lo - 1; t <= w.u_hi && ok; ++t) {
+          const int jq = t + 1;
+          const int jp = t - 1;
+          const bool have_k = jq >= w.u_lo && jq < w.u_hi;
+          const bool have_v = jp >= w.u_lo && jp < w.u_hi;
+          const uint32_t kpos = kv_blocks + (uint32_t)(have_k ? jq - w.u_lo : 0);
+          const uint32_t vpos = kv_blocks + (uint32_t)(have_v ? jp - w.u_lo : 0);
+          const int ks_slot = (int)(kpos % S), vs_slot = (int)(vpos % S);
+          const bool do_pv = have_v && jp >= r.lo && jp < r.hi;
+          const bool do_qk = have_k && jq >= r.lo && jq < r.hi;
+          // Every slot is waited for and released by both issuers, used or not.
+          if ((have_k && !mbar_wait(&k_full[ks_slot], (kpos / S) & 1, p.status)) ||
+              (have_v && !mbar_wait(&v_full[vs_slot], (vpos / S) & 1, p.status))) {
+            ok = false;
+            break;
+          }
+          if (do_pv) {
+            const uint32_t n = (uint32_t)(jp - r.lo);
+            const uint32_t N = my_blocks + n;  // this tile's running block counter
+            if (n == 0 && !mbar_wait(&o_empty[i], (my_items & 1) ^ 1, p.status)) {
+              ok = false;  // the previous item's O has not been read out
+              break;
+            }
+            if (!mbar_wait(&p_full[i * 2 + (N & 1)], (N >> 1) & 1, p.status)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + 256 + i * D;
+            const uint32_t a_tmem = tmem_base + (uint32_t)((i * 2 + (N & 1)) * kBKV);
+            const uint64_t vb = v_desc0 + (uint64_t)((vs_slot * KB) >> 4);
+            const uint32_t first = n != 0 ? 1u : 0u;
+#pragma unroll
+            for (int ks = 0; ks < kBKV / 16; ++ks)
+              if (leader)
+                umma_ts(d_tmem, a_tmem + ks * 8, vb + (uint64_t)(ks * (2048 >> 4)), idesc_pv,
+                        (first | (uint32_t)ks) != 0 ? 1u : 0u);
+            if (leader && (int)n + 2 >= nblk) tc_commit(&tail_done[i]);
+          }
+          if (do_qk) {
+            if (!q_ready) {
+              if (!mbar_wait(&q_full[i], my_items & 1, p.status)) {
+                ok = false;
+                break;
+              }
+              q_ready = true;
+            }
+            tc_fence_after();
+            const uint32_t N = my_blocks + (uint32_t)(jq - r.lo);
+            const uint32_t d_tmem = tmem_base + (uint32_t)((i * 2 + (N & 1)) * kBKV);
+            const uint64_t kb = k_desc0 + (uint64_t)((ks_slot * KB) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint64_t qoff = (uint64_t)((ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2);
+              const uint64_t koff = (uint64_t)((ks >> 2) * (KBOX >> 4) + (ks & 3) * 2);
+              if (leader) umma_ss(d_tmem, qa + qoff, kb + koff, idesc_qk, ks != 0 ? 1u : 0u);
+            }
+            if (leader) tc_commit(&s_full[i * 2 + (N & 1)]);
+            // the item's last QK has read the Q tile: the loader may bring the next one
+            if (leader && jq == r.hi - 1) tc_commit(&q_empty[i]);
+          }
+          if (leader && have_v) tc_commit(&v_empty[vs_slot]);
+          if (leader && have_k) tc_commit(&k_empty[ks_slot]);
+          __syncwarp();
+        }
+        kv_blocks += (uint32_t)(w.u_hi - w.u_lo);
+        if (live) {
+          my_blocks += (uint32_t)nblk;
+          ++my_items;
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    // ---------------- softmax + epilogue ----------------
+    const int i = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t o_tmem = tmem_base + 256 + i * D + lane_addr;
+    const float sl2 = p.scale_log2;
+    const int my_turn = 1 + i * 4 + quarter;
+    const int other_turn = 1 + (1 - i) * 4 + quarter;
+    uint32_t my_blocks = 0;   // blocks of this tile in all earlier items
+    uint32_t tail_count = 0;  // tail commits of this tile in all earlier items
+    // A warp whose bounded wait ran out stops computing but keeps walking the
+    // queue and the hand-over sequence of every later item (`ok` stays false):
+    // its partner on the named barriers, which sees the same items, is never
+    // left waiting. Both leave when the queue ends or stops being fed.
+    bool ok = true;
+    for (uint32_t n_it = 0;; ++n_it) {
+      const int slot = (int)(n_it & 1);
+      if (!mbar_wait(&item_full[slot], (n_it >> 1) & 1, p.status)) break;
+      const Item it = item_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&item_empty[slot]);
+      if (!it.valid) break;
+      const Work w = plan(it);
+      if (!ok) {
+        const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
+        for (int m = 0; m < pairs; ++m) {
+          if (i == 1 || m > 0) named_barrier(my_turn, 64);
+          if (i == 0 || m + 1 < pairs) named_barrier_arrive(other_turn, 64);
+        }
+        continue;
+      }
+      const Range r = i == 0 ? w.r0 : w.r1;
+      const int h = w.h;
+      const int64_t b = w.b;
+      const int64_t i_first = w.i0 + (int64_t)i * kBQ;
+      const int64_t row = i_first + quarter * 32 + lane;
+      const bool row_ok = row < p.t;
+      const int64_t i_last = (i_first + kBQ - 1 < p.t - 1) ? i_first + kBQ - 1 : p.t - 1;
+      int64_t seg_me = 0, seg_last = 0;
+      if (p.seg_start != nullptr && i_first < p.t) {
+        seg_me = p.seg_start[b * p.t + (row_ok ? row : i_last)];
+        seg_last = p.seg_start[b * p.t + i_last];
+      }
+      int64_t vis_lo64 = 0, vis_hi64 = w.ctx.len;
+      if (p.causal && row + 1 < vis_hi64) vis_hi64 = row + 1;
+      if (p.has_window) {
+        if (row - p.win_left > vis_lo64) vis_lo64 = row - p.win_left;
+        if (row + p.win_right + 1 < vis_hi64) vis_hi64 = row + p.win_right + 1;
+      }
+      if (p.has_chunk) {
+        const int64_t ci = row / p.chunk_size;
+        if ((ci + p.chunk_right + 1) * p.chunk_size < vis_hi64) vis_hi64 = (ci + p.chunk_right + 1) * p.chunk_size;
+        if (p.chunk_left >= 0 && (ci - p.chunk_left) * p.chunk_size > vis_lo64) vis_lo64 = (ci - p.chunk_left) * p.chunk_size;
+      }
+      if (p.seg_start != nullptr && seg_me > vis_lo64) vis_lo64 = seg_me;
+      const int vis_lo = (int)vis_lo64, vis_hi = (int)(vis_hi64 < vis_lo64 ? vis_lo64 : vis_hi64);
+      auto vis_word = [&](int base) -> uint32_t {
+        int a = vis_lo - base, bnd = vis_hi - base;
+        a = a < 0 ? 0 : a;
+        bnd = bnd > 32 ? 32 : bnd;
+        uint32_t wd = 0;
+        if (bnd > a) wd = (bnd == 32 ? 0xffffffffu : ((1u << bnd) - 1u)) & ~((1u << a) - 1u);
+        return wd;
+      };
+      float m_run = -INFINITY;
+      float l_run = 0.f;
+      const int nblk = r.hi - r.lo;
+      // The hand-over of the MUFU unit between the two tiles (see the one-item
+      // kernel): a named barrier per (tile, quarter); a warp that gave up still
+      // walks the rest of the item's sequence.
+      const int n_paired = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
+      int turns_done = 0;
+      uint32_t sr[2][32];
+      bool requested = false;
+      for (int j = r.lo; j < r.hi && ok; ++j) {
+        const int n = j - r.lo;
+        const uint32_t N = my_blocks + (uint32_t)n;
+        const int buf = (int)(N & 1);
+        turns_done = n;
+        const uint32_t s_tmem = tmem_base + (uint32_t)((i * 2 + buf) * kBKV) + lane_addr;
+        if (!requested) {
+          if (!mbar_wait(&s_full[i * 2 + buf], (N >> 1) & 1, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          tmem_ld32(s_tmem, sr[0]);
+          tmem_ld32(s_tmem + 32, sr[1]);
+        }
+        const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
+        bool need_mask = j1 >= w.ctx.len || p.has_chunk;
+        if (p.causal && j1 > i_first) need_mask = true;
+        if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
+        if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
+        tmem_ld_wait_for(sr[0]);
+        tmem_ld_wait_for(sr[1]);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const uint32_t vw = vis_word((int)j0 + 32 * c);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (((vw >> e) & 1u) == 0) sr[c][e] = 0xff800000u;
+          }
+        }
+        float mx;
+        {
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              m0 = max3(m0, __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+              m1 = max3(m1, __uint_as_float(sr[c][e + 2]), __uint_as_float(sr[c][e + 3]));
+              m2 = max3(m2, __uint_as_float(sr[c][e + 4]), __uint_as_float(sr[c][e + 5]));
+              m3 = max3(m3, __uint_as_float(sr[c][e + 6]), __uint_as_float(sr[c][e + 7]));
+            }
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        }
+        const float mx_t = mx * sl2;
+        float m_new = m_run;
+        if (mx_t > m_run + kRescaleAbove || m_run == -INFINITY) m_new = fmaxf(m_run, mx_t);
+        bool tail0_seen = false;
+        const bool moved = m_new != m_run && m_run != -INFINITY;
+        const float corr = moved ? ex2_approx(m_run - m_new) : 1.0f;
+        if (__any_sync(0xffffffffu, moved)) {
+          // the previous block's P.V has landed once the next block's S is
+          // complete (issue order); the tile's last block reads the tail barrier
+          const uint32_t Nn = N + 1;
+          const bool landed = n + 1 < nblk ? mbar_wait(&s_full[i * 2 + (int)(Nn & 1)], (Nn >> 1) & 1, p.status)
+                                           : mbar_wait(&tail_done[i], tail_count & 1, p.status);
+          if (!landed) {
+            ok = false;
+            break;
+          }
+          tail0_seen = n + 1 == nblk;
+          tc_fence_after();
+          l_run *= corr;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t orr[32];
+            tmem_ld32(o_tmem + c, orr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * corr);
+            tmem_st32(o_tmem + c, orr);
+          }
+          tmem_st_wait();
+        }
+        m_run = m_new;
+        float m_use = m_run == -INFINITY ? 0.f : m_run;
+        if (n < n_paired && (i == 1 || n > 0)) {
+          named_barrier(my_turn, 64);
+          asm volatile("" : "+f"(m_use));
+        }
+        const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+        uint32_t pk[32];
+        constexpr int kLag = 6;
+        float2 xs[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+          xs[k] = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
+                                         __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
+                             sl2_2, nm_2);
+#pragma unroll
+        for (int k = 0; k < 32 + kLag; ++k) {
+          if (k < 32) {
+            xs[k].x = ex2_approx(xs[k].x);
+            xs[k].y = ex2_approx(xs[k].y);
+          }
+          if (k >= kLag) {
+            const int d = k - kLag;
+            if (d & 1) lb = __fadd2_rn(lb, xs[d]);
+            else la = __fadd2_rn(la, xs[d]);
+            pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
+          }
+        }
+        tmem_st32(s_tmem, pk);
+        if (n < n_paired && (i == 0 || n + 1 < n_paired)) named_barrier_arrive(other_turn, 64);
+        turns_done = n + 1;
+        l_run += (la.x + la.y) + (lb.x + lb.y);
+        requested = false;
+        if (n + 1 < nblk) {
+          const uint32_t Nn = N + 1;
+          if (mbar_test_wait(&s_full[i * 2 + (int)(Nn & 1)], (Nn >> 1) & 1)) {
+            tc_fence_after();
+            const uint32_t next_tmem = tmem_base + (uint32_t)((i * 2 + (int)(Nn & 1)) * kBKV) + lane_addr;
+            tmem_ld32(next_tmem, sr[0]);
+            tmem_ld32(next_tmem + 32, sr[1]);
+            requested = true;
+          }
+        }
+        tmem_st_wait();
+        // the first of the tile's two tail commits is observed before the last P
+        // (which lets the second happen) is published
+        if (n + 1 == nblk && nblk >= 2 && !tail0_seen && !mbar_wait(&tail_done[i], tail_count & 1, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
+      }
+      if (!ok) {
+        for (int m = turns_done; m < n_paired; ++m) {
+          if (i == 1 || m > 0) named_barrier(my_turn, 64);
+          if (i == 0 || m + 1 < n_paired) named_barrier_arrive(other_turn, 64);
+        }
+        continue;
+      }
+      // ---- epilogue: O / l ----
+      T* orow = (T*)p.o + b * p.o_sb + row * p.o_st + (int64_t)h * p.o_sh;
+      if (nblk > 0) {
+        // the last P.V: the item's second tail commit (its only one for a one-block tile)
+        const uint32_t last = tail_count + (nblk >= 2 ? 1u : 0u);
+        if (!mbar_wait(&tail_done[i], last & 1, p.status)) {
+          ok = false;  // the item's hand-over sequence is complete: drain from the next item on
+          continue;
+        }
+        tc_fence_after();
+        const float inv = l_run == 0.f ? 0.f : 1.0f / l_run;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t orr[32];
+          tmem_ld32(o_tmem + c, orr);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t wv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                wv[e] = Elem<T>::pack(__uint_as_float(orr[v * 8 + 2 * e]) * inv,
+                                      __uint_as_float(orr[v * 8 + 2 * e + 1]) * inv);
+              stg128(orow + c + v * 8, make_uint4(wv[0], wv[1], wv[2], wv[3]));
+            }
+          }
+        }
+        // O is read out: the next live item's first P.V may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[i]);
+        my_blocks += (uint32_t)nblk;
+        tail_count += nblk >= 2 ? 2u : 1u;
+      } else if (row_ok) {
+        // No key block reaches this tile: zeros (attention.rs:971-980).
+        for (int c = 0; c < D; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
+      }
+      if (p.lse != nullptr && row_ok)
+        p.lse[(b * p.heads + h) * p.t + row] = l_run == 0.f ? -INFINITY : kLn2F * (m_run + log2f(l_run));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int* queue_head() {
+  static int* addr[64] = {};
+  static std::atomic<unsigned> next{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_next_item) != cudaSuccess) return nullptr;
+    addr[dev] = (int*)p;
+  }
+  return addr[dev] + (next.fetch_add(1) % kQueueSlots);
+}
+
+template <typename T, int D>
+int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
+  using C = FaCfg<D>;
+  CUtensorMap tq, tk, tv;
+  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint32_t kvbox[4] = {64, 1, kBKV, 1};
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
+    const uint64_t st[3] = {(uint64_t)a.q_sh, (uint64_t)a.q_st, (uint64_t)a.q_sb};
+    if (!make_tmap(&tq, a.q, a.dtype, 4, dims, st, box)) return -1;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
+    const uint64_t stk[3] = {(uint64_t)a.k_sh, (uint64_t)a.k_st, (uint64_t)a.k_sb};
+    const uint64_t stv[3] = {(uint64_t)a.v_sh, (uint64_t)a.v_st, (uint64_t)a.v_sb};
+    if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
+    if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, kvbox)) return -1;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_tc_p_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)C::kSmemBytes) != cudaSuccess)
+      return -1;
+    attr_set = true;
+  }
+  int* head = queue_head();
+  if (head == nullptr) return -1;
+  FaParams p{};
+  p.o = a.o;
+  p.o_sb = a.o_sb, p.o_st = a.o_st, p.o_sh = a.o_sh;
+  p.t = a.t, p.tk = a.tk;
+  p.heads = a.heads, p.kv_heads = a.kv_heads;
+  p.scale_log2 = a.scale * kLog2eF;
+  p.causal = a.causal;
+  p.key_lens = a.key_lens;
+  p.has_window = a.has_window;
+  p.win_left = a.win_left, p.win_right = a.win_right;
+  p.has_chunk = a.has_chunk;
+  p.chunk_size = a.chunk_size, p.chunk_left = a.chunk_left, p.chunk_right = a.chunk_right;
+  p.seg_start = a.seg_start;
+  p.row_map = a.row_map;
+  p.lse = a.lse;
+  p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
+  p.status = a.status;
+  const int64_t items = (int64_t)p.n_qt * a.heads * a.batch;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const int grid = (int)(items < sms ? items : sms);
+  if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
+  attention_tc_p_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, head);
+  if (cfg != nullptr)
+    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1,persistent:%d}", 2 * kBQ, kBKV, D, C::kStages, grid);
+  return 0;
+}
+
+}  // namespace
+
+// The persistent kernel takes what the one-item kernel takes, minus a bool key
+// mask, once there are more items than SMs (otherwise nothing would overlap).
+bool attention_tc_p_covers(const AttnArgs& a) {
+  if (!attention_tc_covers(a)) return false;
+  if (a.key_mask != nullptr) return false;
+  const int64_t n_qt = (a.t + 2 * kBQ - 1) / (2 * kBQ);
+  const int64_t items = n_qt * a.heads * a.batch;
+  return items > 148 && items < 0x7fffffffLL;
+}
+
+int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
+  if (!attention_tc_p_covers(a)) return 1;
+  if (a.dtype == SVODB_BF16)
+    return a.d == 128 ? run_p<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run_p<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
+  return a.d == 128 ? run_p<__half, 128>(a, s, cfg, cfg_len) : run_p<__half, 64>(a, s, cfg, cfg_len);
+}
+
+}  // namespace svodb

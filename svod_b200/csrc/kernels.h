@@ -126,6 +126,9 @@ int launch_attention_generic(const AttnArgs& a, cudaStream_t s);
 // shape is outside what it covers.
 int launch_attention_tc(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 bool attention_tc_covers(const AttnArgs& a);
+// The persistent form (one CTA per SM over a work queue); same contract.
+int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
+bool attention_tc_p_covers(const AttnArgs& a);
 
 struct CombineArgs {
   const float* o_part;

@@ -357,3 +357,55 @@ def test_cache_options_are_validated():
     with pytest.raises(ops.OpsError) as e:  # 4 query heads over 3 kv heads
         ops.attention(q, k, k, ops.Attn(keys=lens, cache=ops.Cache(0, 3, i32([0, 1]))))
     assert e.value.kind == "Heads"
+
+
+# ---- the persistent kernel (more work items than SMs, no bool key mask) ---------------------------
+PERSISTENT_CASES = [
+    ("causal", 128, dict(causal=True)),
+    ("causal d64", 64, dict(causal=True)),
+    ("plain", 128, dict()),
+    ("key lengths with empty rows", 128, dict(lens=[1300, 700, 0, 130])),
+    ("causal + lengths", 64, dict(causal=True, lens=[1300, 5, 900, 257])),
+    ("window", 128, dict(window=(100, 30), lens=[1300, 1000, 1300, 64])),
+    ("causal segments", 64, dict(causal=True, seg="seg")),
+    ("chunks", 128, dict(chunk=(96, 2, 0), lens=[1300, 1300, 400, 1300])),
+]
+
+
+@pytest.mark.parametrize("name,D,kw", PERSISTENT_CASES, ids=[c[0] for c in PERSISTENT_CASES])
+def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D, kw):
+    """192 work items (B4 x H8 x 6 tile pairs of a ragged T = 1300) on 148 SMs run
+    the persistent kernel: same numbers as the oracle within tolerance and as the
+    one-item kernel bit for bit."""
+    from svod_b200 import _lib as L
+    dt, B, T, H, Hkv = O.BF16, 4, 1300, 8, 4
+    rng = np.random.default_rng(len(name) + D)
+    q, k, v = normal(rng, (B, T, H, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt)
+    okw = dict(kw)
+    a = ops.Attn(causal=bool(kw.get("causal")), window=kw.get("window"))
+    if "lens" in kw:
+        okw["key_lens"] = np.array(okw.pop("lens"))
+        a.keys = ops.KeyMask.Lens(torch.tensor(kw["lens"], dtype=torch.int32).cuda())
+    if "seg" in kw:
+        seg = segments(B, T, 300)
+        okw["seg_start"] = seg
+        okw.pop("seg")
+        a.seg_start = torch.from_numpy(seg.astype(np.int32)).cuda()
+    if "chunk" in kw:
+        a.chunk = ops.Chunk(*kw["chunk"])
+    want = O.attention(q, k, v, dtype=dt, **okw)
+    Q, K, V = dev(q, dt), dev(k, dt), dev(v, dt)
+    got = host(ops.attention(Q, K, V, a))
+    assert "persistent" in ops.chosen(), ops.chosen()
+    ops.device_status()
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+    lib = L.load()
+    lib.svodb_config_set(b"attention|one_item", 1)
+    try:
+        one = host(ops.attention(Q, K, V, a))
+        assert "persistent" not in ops.chosen()
+    finally:
+        lib.svodb_config_set(b"attention|one_item", 0)
+    assert np.array_equal(got, one)
+    again = host(ops.attention(Q, K, V, a))  # a second launch takes another queue slot
+    assert np.array_equal(got, again)
