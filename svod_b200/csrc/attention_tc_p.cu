@@ -19,8 +19,9 @@
 //     loader) and `o_empty` (the softmax warps have read O out, the next item's
 //     first P.V may overwrite it): the loader and the issuers run into the next
 //     item while the softmax warps still finish the last one.
-// Covers what the one-item kernel covers except a bool key mask (its per-item
-// scan needs the whole CTA): those calls keep the one-item kernel.
+// A bool key mask needs no CTA-wide scan here: every warp scans the mask row of
+// its item's batch lane for itself (once per change of lane) and the softmax
+// gathers the bits of a block's keys with a ballot.
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
@@ -64,6 +65,35 @@ __device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int he
   it.b = kvb / kv_heads;
   it.valid = 1;
   return it;
+}
+
+// What a bool key mask row says about a batch lane: the keys past `len` are all
+// hidden; `general` when hidden keys also lie before it (then the softmax reads
+// the row's bits block by block). Every warp scans the row for itself, all lanes
+// taking part, when its item's batch lane changes.
+struct MaskRow {
+  int64_t b;
+  int len;
+  int general;
+};
+
+__device__ __forceinline__ void scan_mask_row(const FaParams& p, int64_t b, int lane, MaskRow& row) {
+  if (row.b == b) return;
+  int first_zero = 0x7fffffff, last_set = 0;
+  const int64_t base = b * p.tk;
+  for (int64_t j = lane; j < p.tk; j += 32) {
+    const int m = p.key_mask_i32 ? ((const int32_t*)p.key_mask)[base + j] : (int)((const uint8_t*)p.key_mask)[base + j];
+    if (m != 0) last_set = (int)j + 1;
+    else if ((int)j < first_zero) first_zero = (int)j;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    first_zero = min(first_zero, __shfl_xor_sync(0xffffffffu, first_zero, o));
+    last_set = max(last_set, __shfl_xor_sync(0xffffffffu, last_set, o));
+  }
+  row.b = b;
+  row.len = last_set;
+  row.general = first_zero < last_set ? 1 : 0;
 }
 
 template <typename T, int D>
@@ -142,7 +172,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     bool live0, live1;
     int u_lo, u_hi;
   };
-  auto plan = [&](const Item& it) -> Work {
+  auto plan = [&](const Item& it, const MaskRow& mrow) -> Work {
     Work w;
     w.h = it.h;
     w.hk = it.h / (p.heads / p.kv_heads);
@@ -153,6 +183,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     if (p.key_lens != nullptr) {
       const int64_t kl = p.key_lens[it.b];
       w.ctx.len = kl < 0 ? 0 : (kl < w.ctx.len ? kl : w.ctx.len);
+    }
+    if (p.key_mask != nullptr) {
+      w.ctx.general_mask = mrow.general;
+      if (mrow.len < w.ctx.len) w.ctx.len = mrow.len;
     }
     w.r0 = tile_range(p, w.ctx, w.b, w.i0);
     w.r1 = tile_range(p, w.ctx, w.b, w.i0 + kBQ);
@@ -174,21 +208,31 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     if (warp == 0) {
       // ---------------- scheduler + TMA loader ----------------
-      if (lane == 0) {
+      // The whole warp walks the queue (a key mask row is scanned by all lanes);
+      // lane 0 takes the items, publishes them and issues the copies.
+      {
         int s = 0;
         uint32_t ph = 0;
         uint32_t q_items[2] = {0, 0};  // live items so far, per tile
         bool ok = true;
+        MaskRow mrow{-1, 0, 0};
         for (uint32_t n_it = 0; ok; ++n_it) {
           const int slot = (int)(n_it & 1);
-          if (!mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) break;
-          const Item it = decode_item(atomicAdd(queue, 1), n_items, p.n_qt, p.heads, p.kv_heads);
-          item_ring[slot] = it;
-          __threadfence_block();
-          mbar_arrive(&item_full[slot]);
+          int wi = -1;
+          if (lane == 0 && mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) wi = atomicAdd(queue, 1);
+          wi = __shfl_sync(0xffffffffu, wi, 0);
+          if (wi < 0) break;  // the wait ran out
+          const Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads);
+          if (lane == 0) {
+            item_ring[slot] = it;
+            __threadfence_block();
+            mbar_arrive(&item_full[slot]);
+          }
           if (!it.valid) break;
-          const Work w = plan(it);
+          if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+          const Work w = plan(it, mrow);
           if (w.u_hi <= w.u_lo) continue;
+          if (lane == 0) {
           for (int i = 0; i < 2; ++i) {
             if (i == 0 ? w.live0 : w.live1) {
               // the issuer's last QK of the tile's previous live item has read this Q tile
@@ -224,6 +268,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
               ph ^= 1;
             }
           }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
         if (!ok) {
           // Error path: give copies in flight a bounded time to land.
@@ -242,6 +288,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       uint32_t kv_blocks = 0;  // K/V blocks of all earlier items (ring position)
       uint32_t my_blocks = 0;  // blocks of this tile in all earlier items (S/P buffer and phase)
       uint32_t my_items = 0;   // live items of this tile so far
+      MaskRow mrow{-1, 0, 0};
       bool ok = true;
       for (uint32_t n_it = 0; ok; ++n_it) {
         const int slot = (int)(n_it & 1);
@@ -250,7 +297,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&item_empty[slot]);
         if (!it.valid) break;
-        const Work w = plan(it);
+        if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+        const Work w = plan(it, mrow);
         if (w.u_hi <= w.u_lo) continue;
         const Range r = i == 0 ? w.r0 : w.r1;
         const int nblk = r.hi - r.lo;
@@ -340,6 +388,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     const int other_turn = 1 + (1 - i) * 4 + quarter;
     uint32_t my_blocks = 0;   // blocks of this tile in all earlier items
     uint32_t tail_count = 0;  // tail commits of this tile in all earlier items
+    MaskRow mrow{-1, 0, 0};
     // A warp whose bounded wait ran out stops computing but keeps walking the
     // queue and the hand-over sequence of every later item (`ok` stays false):
     // its partner on the named barriers, which sees the same items, is never
@@ -352,7 +401,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&item_empty[slot]);
       if (!it.valid) break;
-      const Work w = plan(it);
+      if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+      const Work w = plan(it, mrow);
       if (!ok) {
         const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
         for (int m = 0; m < pairs; ++m) {
@@ -420,7 +470,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           tmem_ld32(s_tmem + 32, sr[1]);
         }
         const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
-        bool need_mask = j1 >= w.ctx.len || p.has_chunk;
+        bool need_mask = j1 >= w.ctx.len || p.has_chunk || w.ctx.general_mask;
         if (p.causal && j1 > i_first) need_mask = true;
         if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
         if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
@@ -429,7 +479,16 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const uint32_t vw = vis_word((int)j0 + 32 * c);
+            uint32_t vw = vis_word((int)j0 + 32 * c);
+            if (w.ctx.general_mask) {
+              // the mask bits of these 32 keys: one key per lane, gathered by a ballot
+              const int64_t jk = j0 + 32 * c + lane;
+              int m = 0;
+              if (jk < p.tk)
+                m = p.key_mask_i32 ? ((const int32_t*)p.key_mask)[b * p.tk + jk]
+                                   : (int)((const uint8_t*)p.key_mask)[b * p.tk + jk];
+              vw &= __ballot_sync(0xffffffffu, m != 0);
+            }
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (((vw >> e) & 1u) == 0) sr[c][e] = 0xff800000u;
@@ -594,8 +653,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   }
 }
 
-bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
 int* queue_head() {
   static int* addr[64] = {};
   static std::atomic<unsigned> next{0};
@@ -645,6 +702,8 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.scale_log2 = a.scale * kLog2eF;
   p.causal = a.causal;
   p.key_lens = a.key_lens;
+  p.key_mask = a.key_mask;
+  p.key_mask_i32 = a.key_mask_i32;
   p.has_window = a.has_window;
   p.win_left = a.win_left, p.win_right = a.win_right;
   p.has_chunk = a.has_chunk;
@@ -669,11 +728,10 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
 
 }  // namespace
 
-// The persistent kernel takes what the one-item kernel takes, minus a bool key
-// mask, once there are more items than SMs (otherwise nothing would overlap).
+// The persistent kernel takes what the one-item kernel takes once there are more
+// items than SMs (otherwise nothing would overlap).
 bool attention_tc_p_covers(const AttnArgs& a) {
   if (!attention_tc_covers(a)) return false;
-  if (a.key_mask != nullptr) return false;
   const int64_t n_qt = (a.t + 2 * kBQ - 1) / (2 * kBQ);
   const int64_t items = n_qt * a.heads * a.batch;
   return items > 148 && items < 0x7fffffffLL;

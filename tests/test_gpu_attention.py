@@ -359,7 +359,12 @@ def test_cache_options_are_validated():
     assert e.value.kind == "Heads"
 
 
-# ---- the persistent kernel (more work items than SMs, no bool key mask) ---------------------------
+# ---- the persistent kernel (more work items than SMs) ---------------------------------------------
+def padding_mask(B, Tk, lens):
+    return np.array([[j < lens[b] for j in range(Tk)] for b in range(B)])
+
+
+
 PERSISTENT_CASES = [
     ("causal", 128, dict(causal=True)),
     ("causal d64", 64, dict(causal=True)),
@@ -369,6 +374,10 @@ PERSISTENT_CASES = [
     ("window", 128, dict(window=(100, 30), lens=[1300, 1000, 1300, 64])),
     ("causal segments", 64, dict(causal=True, seg="seg")),
     ("chunks", 128, dict(chunk=(96, 2, 0), lens=[1300, 1300, 400, 1300])),
+    ("bool mask with holes", 128, dict(mask=key_mask(4, 1300))),
+    ("bool mask with holes d64 causal", 64, dict(mask=key_mask(4, 1300), causal=True)),
+    ("bool padding mask", 64, dict(mask=padding_mask(4, 1300, [1300, 64, 0, 777]))),
+    ("bool padding mask + window", 128, dict(mask=padding_mask(4, 1300, [900, 1300, 1, 300]), window=(128, 128))),
 ]
 
 
@@ -386,6 +395,9 @@ def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D
     if "lens" in kw:
         okw["key_lens"] = np.array(okw.pop("lens"))
         a.keys = ops.KeyMask.Lens(torch.tensor(kw["lens"], dtype=torch.int32).cuda())
+    if "mask" in kw:
+        okw["key_mask"] = okw.pop("mask")
+        a.keys = ops.KeyMask.Bool(torch.from_numpy(np.asarray(kw["mask"])).cuda())
     if "seg" in kw:
         seg = segments(B, T, 300)
         okw["seg_start"] = seg
