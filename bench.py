@@ -18,7 +18,8 @@ HBM (CUDA-graph replay + all-gather, CUDA events on the launching stream, max
 over ranks); `e2e` adds the pinned-host -> device copy of every step's inputs
 and the device -> host read of the pooled result inside the timed region.
 `roofline` is measured live for the dominant kernel; `cpu_baseline` times the
-numpy oracle on a bounded sample of the same workload on this box's host cores.
+compiled C + OpenMP restatement on a bounded sample of the same workload on this
+box's host cores.
 """
 from __future__ import annotations
 
@@ -124,40 +125,44 @@ def visible_index(local_rank: int) -> int:
 
 # --------------------------------------------------------------------------- CPU legs
 def oracle_sample(kind: str, seq: int, layers: int, seed: int = 7):
-    """A bounded sample of the workload for the CPU restatement: one sequence of
-    `seq` tokens through `layers` layers of the same architecture. Returns a
-    closure that runs it and the number of tokens it processes."""
+    """A bounded sample of the workload for the compiled CPU restatement
+    (`oracle/svod_oracle.c`: f32, OpenMP over all host threads): one sequence of
+    `seq` tokens through `layers` decoder layers of the same architecture.
+    Returns a closure that runs it and the number of tokens it processes."""
     import numpy as np
+    from oracle import c_oracle as C
     from oracle import svod_oracle as O
+    try:
+        C.build()
+    except Exception:
+        pass  # a library built earlier still loads; `load()` reports a missing one
     rng = np.random.default_rng(seed)
     dt = O.BF16
-    w = lambda *s: O.round_to(dt, rng.standard_normal(s) * 0.02)
+    w = lambda *s: O.round_to(dt, rng.standard_normal(s) * 0.02).astype(np.float32)
     if kind != "qwen3":
         raise SystemExit("the CPU leg samples the default (qwen3) workload")
-    D, H, Hkv, hd, F, V = 1024, 16, 8, 128, 3072, 4096
-    ones = lambda n: np.ones(n)
+    D, H, Hkv, hd, F = 1024, 16, 8, 128, 3072
+    ones = lambda n: np.ones(n, dtype=np.float32)
     lp = dict(in_w=ones(D), qkv_w=w((H + 2 * Hkv) * hd, D), qn_w=ones(hd), kn_w=ones(hd), o_w=w(D, H * hd),
               post_w=ones(D), gu_w=w(2 * F, D), down_w=w(D, F))
-    p = dict(embed=w(V, D), layers=[lp] * layers, norm_w=ones(D))
-    ids = rng.integers(0, V, (1, seq))
-    lengths = np.array([seq])
+    hidden = w(1, seq, D)
+    C.load()
 
     def run():
-        return O.qwen3_forward(p, ids, lengths, heads_n=H, kv_heads=Hkv, head_dim=hd, dtype=dt)[0]
+        return C.qwen3_layers(hidden, [lp] * layers, heads_n=H, kv_heads=Hkv, head_dim=hd, dtype=C.BF16)
 
     return run, seq
 
 
 def cpu_threads() -> int:
-    try:
-        return len(os.sched_getaffinity(0))
-    except Exception:
-        return os.cpu_count() or 1
+    from oracle import c_oracle as C
+    return C.threads()
 
 
-def time_cpu(kind: str, steps: int, warmup: int, seq: int = 512, layers: int = 4, full_layers: int = 28):
-    """Times the oracle on `layers` of the `full_layers` layers and scales to the
-    full depth (every layer does identical work)."""
+def time_cpu(kind: str, steps: int, warmup: int, seq: int = 4096, layers: int = 4, full_layers: int = 28):
+    """Times the compiled CPU restatement on `layers` of the `full_layers` layers
+    of one full-length sequence and scales to the full depth (every layer does
+    identical work; the embedding lookup and the pooling are negligible)."""
     run, tokens = oracle_sample(kind, seq, layers)
     for _ in range(warmup):
         run()
@@ -166,12 +171,12 @@ def time_cpu(kind: str, steps: int, warmup: int, seq: int = 512, layers: int = 4
         run()
     dt = (time.perf_counter() - t0) / steps
     full = dt * full_layers / layers
-    sample = (f"numpy float64 oracle, 1 sequence x {seq} tokens, {layers} of {full_layers} layers timed "
+    sample = (f"C + OpenMP f32 restatement, 1 sequence x {seq} tokens, {layers} of {full_layers} layers timed "
               f"and scaled to {full_layers}, {steps} step(s)")
     return tokens / full, full * 1e3, sample
 
 
-def time_torch_cpu(seq: int = 512, layers: int = 4, full_layers: int = 28, steps: int = 1):
+def time_torch_cpu(seq: int = 4096, layers: int = 4, full_layers: int = 28, steps: int = 1):
     """A second, separately labelled CPU reference point (not svod, not the
     oracle): the Qwen3-shaped layer in plain PyTorch f32 CPU ops
     (`F.linear`, `F.scaled_dot_product_attention`) on the same bounded sample,
@@ -218,7 +223,7 @@ def time_torch_cpu(seq: int = 512, layers: int = 4, full_layers: int = 28, steps
 def reference_arm(args):
     """`--impl reference`: the reference's own CPU path cannot be built here (no
     Rust toolchain), so the arm times the CPU restatement of the same path on
-    the host cores, all threads BLAS will use, on a bounded sample per step."""
+    the host cores (C + OpenMP, f32, every host thread) on a bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -481,7 +486,7 @@ def gpu_arm(args):
         line["kernels"] = ks
         line["attention_fwd_tflops"] = ks["flash_attention"]["tflops"]
         if world == 1 and not args.no_cpu:
-            v, ms, sample = time_cpu("qwen3", 1, 0) if kind == "qwen3" else (None, None, None)
+            v, ms, sample = time_cpu("qwen3", 2, 1) if kind == "qwen3" else (None, None, None)
             if v is not None:
                 line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
                                         "sample": sample, "second_point": time_torch_cpu()}

@@ -52,16 +52,34 @@ struct Item {
 };
 
 // Work item w in queue order: batch, KV head, query head of the group, then
-// query tile pairs from the last (the heaviest under a causal mask) to the first.
-__device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads) {
+// query tile pairs from the last (the heaviest under a causal mask) to the first,
+// so that the items in flight at one time share few KV heads and their keys stay
+// in L2. The last `tail_groups` (batch, KV head) groups are interleaved instead:
+// tile pair first (heaviest first), then group, then query head. The queue then
+// ends on the lightest items of many groups rather than starting the heaviest
+// items of the last group when everything else is done.
+__device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads, int tail_groups) {
   Item it{0, 0, 0, 0};
   if (w >= n_items) return it;
   const int group = heads / kv_heads;
   const int per_kv = group * n_qt;
-  const int kvb = w / per_kv;  // (batch, kv head)
-  const int r = w - kvb * per_kv;
-  it.qt = n_qt - 1 - r / group;
-  it.h = (kvb % kv_heads) * group + r % group;
+  const int head_groups = n_items / per_kv - tail_groups;
+  int kvb, r, q;
+  if (w < head_groups * per_kv) {
+    kvb = w / per_kv;  // (batch, kv head)
+    r = w - kvb * per_kv;
+    q = r / group;
+    r -= q * group;
+  } else {
+    const int t = w - head_groups * per_kv;
+    const int per_qt = tail_groups * group;
+    q = t / per_qt;
+    const int r2 = t - q * per_qt;
+    kvb = head_groups + r2 / group;
+    r = r2 % group;
+  }
+  it.qt = n_qt - 1 - q;
+  it.h = (kvb % kv_heads) * group + r;
   it.b = kvb / kv_heads;
   it.valid = 1;
   return it;
@@ -100,7 +118,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsFa, 1)
     attention_tc_p_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const int n_items,
-                          int* const queue) {
+                          const int tail_groups, int* const queue) {
   using C = FaCfg<D>;
   constexpr int S = C::kStages;
   constexpr int QB = C::kQTileBytes;
@@ -222,7 +240,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (lane == 0 && mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) wi = atomicAdd(queue, 1);
           wi = __shfl_sync(0xffffffffu, wi, 0);
           if (wi < 0) break;  // the wait ran out
-          const Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads);
+          const Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups);
           if (lane == 0) {
             item_ring[slot] = it;
             __threadfence_block();
@@ -719,8 +737,17 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   const int grid = (int)(items < sms ? items : sms);
+  // Under a causal mask the items differ in length: interleave enough of the last
+  // groups that their work is several times (SMs x longest item).
+  int tail_groups = 0;
+  if (a.causal) {
+    const int64_t groups = (int64_t)a.batch * a.kv_heads;
+    const int64_t per_kv = (int64_t)(a.heads / a.kv_heads) * p.n_qt;
+    const int64_t want = (6 * (int64_t)sms + per_kv - 1) / per_kv;
+    tail_groups = (int)(want < groups ? want : groups);
+  }
   if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
-  attention_tc_p_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, head);
+  attention_tc_p_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, tail_groups, head);
   if (cfg != nullptr)
     snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1,persistent:%d}", 2 * kBQ, kBKV, D, C::kStages, grid);
   return 0;
