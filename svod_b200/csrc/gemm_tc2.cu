@@ -261,6 +261,14 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
       const int n0 = nt * p.out_bn;
       const int cols = p.out_bn / C::kGroups;
       const int c_lo = chalf * cols;
+      if (bias != nullptr) {
+        // This group's bias columns, brought into L1 while the tile is still being
+        // accumulated: the reads in the epilogue proper then hit.
+        const int line = (ew & 3) * 32 + lane;  // 128-byte lines: [gate | up] halves, 64 values each
+        const int up = line >= 64 ? 1 : 0;
+        const int col = n0 + c_lo + (line - 64 * up) * 64;
+        if ((line - 64 * up) * 64 < cols && col < p.n && (up == 0 || p.gated)) prefetch_l1(bias + (up ? p.n : 0) + col);
+      }
       if (!mbar_wait(&acc_full[as], aph, p.status)) {
         ok = false;
         break;
