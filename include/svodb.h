@@ -87,7 +87,9 @@ const char* svodb_last_chosen(void);
  * reached the tensor-core kernel, "gemm|<dtype>|<m>|<n>|<k>|<epilogue>" ("" when
  * none did). `svodb_config_set(key, bn)`: later calls with that key use tile
  * width bn (64, 128 or 256 on one CTA, 512 = the CTA-pair kernel; a choice the
- * shape or epilogue cannot take is ignored); bn = 0 forgets the key. `svodb_config_get` returns 0 when the key is unset. */
+ * shape or epilogue cannot take is ignored); bn = 0 forgets the key. The key
+ * "attention|one_item" (value 1) keeps attention on the one-item-per-CTA kernel.
+ * `svodb_config_get` returns 0 when the key is unset. */
 const char* svodb_last_config_key(void);
 int svodb_config_set(const char* key, int32_t value);
 int32_t svodb_config_get(const char* key);
@@ -168,7 +170,15 @@ typedef struct svodb_attn_opts {
 size_t svodb_attention_workspace_bytes(int64_t batch, int64_t t, int64_t heads, int64_t d, int32_t splits);
 
 /* `ops::attention(q,k,v,opts)` (tk/src/ops/attention.rs:100-102):
- * q [B,T,H,D], k,v [B,Tk,Hkv,D] sequence-major -> o [B,T,H,D]. */
+ * q [B,T,H,D], k,v [B,Tk,Hkv,D] sequence-major -> o [B,T,H,D].
+ * Calls with more work items (256 query rows x head x batch lane) than the
+ * device has SMs run a persistent kernel that hands the items out through a
+ * counter inside the library, one counter per (device, stream) pair, zeroed on
+ * the stream before each launch (a memset node under capture). Launches on one
+ * stream follow one another, so they may share it; a captured graph keeps the
+ * counter of the stream it was captured on, so two graphs captured on the SAME
+ * stream must not be replayed at the same time on different streams. Config key
+ * "attention|one_item" = 1 (`svodb_config_set`) turns the persistent kernel off. */
 int svodb_attention(const svodb_tensor* q, const svodb_tensor* k, const svodb_tensor* v, const svodb_attn_opts* opts,
                     svodb_tensor* o, void* stream);
 

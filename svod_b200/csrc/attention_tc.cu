@@ -644,7 +644,11 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
     if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, kvbox)) return -1;
   }
-  static bool attr_set = false;
+  // the attribute belongs to the device's copy of the kernel: once per device
+  static bool attr_seen[64] = {};
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(attention_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)

@@ -26,7 +26,9 @@
 #include <math.h>
 #include <stdio.h>
 
-#include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "attention_parts.cuh"
 #include "common.cuh"
@@ -40,10 +42,8 @@ namespace {
 
 using namespace fa_parts;
 
-// Queue heads: items handed out so far by a running launch. Every launch takes
-// the next slot (zeroed on its stream just before it), so launches in flight at
-// the same time on different streams do not share a head as long as fewer than
-// kQueueSlots of them are alive at once.
+// Queue heads: items handed out so far by a running launch, one per (device,
+// stream) pair, zeroed on the stream just before each launch.
 constexpr int kQueueSlots = 256;
 __device__ int g_next_item[kQueueSlots];
 
@@ -671,18 +671,33 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   }
 }
 
-int* queue_head() {
-  static int* addr[64] = {};
-  static std::atomic<unsigned> next{0};
+// The queue head of a launch on `stream`: launches on one stream run one after
+// the other and share a head; every other (device, stream) pair gets a head of
+// its own, so launches that overlap on different streams never share one. A
+// graph replays with the head of the stream it was captured on. Returns nullptr
+// once kQueueSlots pairs have been seen: the caller then takes the one-item kernel.
+int* queue_head(cudaStream_t stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, int> slots;
+  static int* base[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return nullptr;
-  if (addr[dev] == nullptr) {
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[dev] == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_next_item) != cudaSuccess) return nullptr;
-    addr[dev] = (int*)p;
+    base[dev] = (int*)p;
   }
-  return addr[dev] + (next.fetch_add(1) % kQueueSlots);
+  const auto key = std::make_pair(dev, stream);
+  auto it = slots.find(key);
+  if (it == slots.end()) {
+    int used = 0;
+    for (const auto& kv : slots) used += kv.first.first == dev ? 1 : 0;
+    if (used >= kQueueSlots) return nullptr;
+    it = slots.emplace(key, used).first;
+  }
+  return base[dev] + it->second;
 }
 
 template <typename T, int D>
@@ -703,15 +718,19 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
     if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, kvbox)) return -1;
   }
-  static bool attr_set = false;
+  // the attribute belongs to the device's copy of the kernel: once per device
+  static bool attr_seen[64] = {};
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(attention_tc_p_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)
       return -1;
     attr_set = true;
   }
-  int* head = queue_head();
-  if (head == nullptr) return -1;
+  int* head = queue_head(s);
+  if (head == nullptr) return 1;  // no queue head left for this stream: the one-item kernel takes the call
   FaParams p{};
   p.o = a.o;
   p.o_sb = a.o_sb, p.o_st = a.o_st, p.o_sh = a.o_sh;

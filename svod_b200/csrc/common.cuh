@@ -291,8 +291,13 @@ __device__ __forceinline__ uint32_t cluster_map(const void* p, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
   return out;
 }
+// Arrival on a barrier of a CTA of this cluster. Default semantics (release at
+// CTA scope): the arrival orders this thread's own earlier accesses, which is all
+// a "these tensor-memory reads are done" signal needs; a cluster-scope release
+// would first wait for every outstanding store of the thread to be visible
+// cluster-wide.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),

@@ -684,7 +684,11 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
         !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
       return -1;
   }
-  static bool attr_set = false;
+  // the attribute belongs to the device's copy of the kernel: once per device
+  static bool attr_seen[64] = {};
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)

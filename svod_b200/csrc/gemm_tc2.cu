@@ -503,7 +503,11 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
       if (!make_tmap_2d(&tsin, a.rope_sin, dt, 64, (uint64_t)p.rope_seq, 64, 64, BM)) return -1;
     }
   }
-  static bool attr_set = false;
+  // the attribute belongs to the device's copy of the kernel: once per device
+  static bool attr_seen[64] = {};
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_tc2_kernel<T, HEADS, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)

@@ -421,3 +421,30 @@ def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D
     assert np.array_equal(got, one)
     again = host(ops.attention(Q, K, V, a))  # a second launch takes another queue slot
     assert np.array_equal(got, again)
+
+
+def test_persistent_attention_launches_overlapping_on_two_streams_keep_their_own_queues():
+    """Each (device, stream) pair has its own work-queue head, so launches in
+    flight at once on two streams hand out every item exactly once: the outputs
+    equal those of the same calls made one after the other."""
+    dt, B, T, H, Hkv, D = O.BF16, 4, 1300, 8, 4, 128
+    rng = np.random.default_rng(77)
+    sets = []
+    for _ in range(2):
+        q, k, v = normal(rng, (B, T, H, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt)
+        sets.append((dev(q, dt), dev(k, dt), dev(v, dt)))
+    a = ops.Attn(causal=True)
+    want = [host(ops.attention(*s_, a)) for s_ in sets]
+    assert "persistent" in ops.chosen()
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = [[], []]
+    for _ in range(6):
+        for i in range(2):
+            with torch.cuda.stream(streams[i]):
+                got[i].append(ops.attention(*sets[i], a))
+    torch.cuda.synchronize()
+    ops.device_status()
+    for i in range(2):
+        for g in got[i]:
+            assert np.array_equal(host(g), want[i])
