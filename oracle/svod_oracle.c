@@ -284,6 +284,25 @@ void so_heads(const float* qkv, const float* q_w, const float* k_w, const float*
     }
 }
 
+/* e^x for x <= 0 in plain arithmetic the compiler can vectorise: 2^(x log2 e) with the
+ * fraction by a degree-6 polynomial (relative error below 3e-7, far inside the 16-bit
+ * rounding the weights get); inputs below -87 give 0. */
+static inline float exp_neg(float x) {
+  float y = x * 1.4426950408889634f;
+  if (y < -126.0f) y = -126.0f;
+  const float n = __builtin_rintf(y);
+  const float f = y - n; /* [-0.5, 0.5] */
+  float p = 1.530151e-4f;
+  p = p * f + 1.339887e-3f;
+  p = p * f + 9.618437e-3f;
+  p = p * f + 5.550357e-2f;
+  p = p * f + 2.402265e-1f;
+  p = p * f + 6.931472e-1f;
+  p = p * f + 1.0f;
+  const int32_t e = (int32_t)n;
+  return x < -87.0f ? 0.0f : bits_f32(f32_bits(p) + ((uint32_t)e << 23));
+}
+
 /* ---- attention (tensor/src/transformer.rs:358-531): f32 scores and softmax, weights cast to the
  * tensor dtype before @V (:526-530), hidden keys excluded, a row with no visible key -> 0 ---- */
 /* q [b,t,h,d], k,v [b,tk,hkv,d], o [b,t,h,d]; key_lens [b] or NULL; window (left,right) when has_window */
@@ -291,50 +310,92 @@ void so_attention(const float* q, const float* k, const float* v, float* o, int6
                   int hkv, int d, int causal, const int32_t* key_lens, int has_window, int win_left, int win_right,
                   float scale, int dtype) {
   const int group = h / hkv;
+  const int64_t row_blocks = (t + 3) / 4;
+  const int64_t ldq = (int64_t)h * d, ldk = (int64_t)hkv * d;
 #pragma omp parallel
   {
-    float* s = (float*)malloc((size_t)tk * sizeof(float));
-    float* acc = (float*)malloc((size_t)d * sizeof(float));
-#pragma omp for collapse(3) schedule(dynamic, 8)
+    /* four query rows at a time: their scores, then their weights, over the union of their key ranges */
+    float* s = (float*)malloc((size_t)(4 * tk) * sizeof(float));
+#pragma omp for collapse(3) schedule(dynamic, 4)
     for (int64_t bi = 0; bi < b; ++bi)
       for (int hh = 0; hh < h; ++hh)
-        for (int64_t i = 0; i < t; ++i) {
+        for (int64_t ib = 0; ib < row_blocks; ++ib) {
           const int kh = hh / group;
-          const float* qr = q + ((bi * t + i) * h + hh) * (int64_t)d;
-          int64_t lo = 0, hi = tk;
-          if (key_lens && key_lens[bi] < hi) hi = key_lens[bi] < 0 ? 0 : key_lens[bi];
-          if (causal && i + 1 < hi) hi = i + 1;
-          if (has_window) {
-            if (i - win_left > lo) lo = i - win_left;
-            if (i + win_right + 1 < hi) hi = i + win_right + 1;
+          const int64_t i0 = ib * 4;
+          const int nr = (int)(t - i0 < 4 ? t - i0 : 4);
+          int64_t lo[4], hi[4], blo = tk, bhi = 0;
+          for (int r = 0; r < nr; ++r) {
+            const int64_t i = i0 + r;
+            lo[r] = 0, hi[r] = tk;
+            if (key_lens && key_lens[bi] < hi[r]) hi[r] = key_lens[bi] < 0 ? 0 : key_lens[bi];
+            if (causal && i + 1 < hi[r]) hi[r] = i + 1;
+            if (has_window) {
+              if (i - win_left > lo[r]) lo[r] = i - win_left;
+              if (i + win_right + 1 < hi[r]) hi[r] = i + win_right + 1;
+            }
+            if (hi[r] > lo[r]) {
+              if (lo[r] < blo) blo = lo[r];
+              if (hi[r] > bhi) bhi = hi[r];
+            }
           }
-          float* orow = o + ((bi * t + i) * h + hh) * (int64_t)d;
-          if (hi <= lo) {
-            for (int c = 0; c < d; ++c) orow[c] = 0.0f;
-            continue;
+          const float* q0 = q + ((bi * t + i0) * h + hh) * (int64_t)d;
+          const float* k0 = k + (bi * tk * hkv + kh) * (int64_t)d;
+          const float* v0 = v + (bi * tk * hkv + kh) * (int64_t)d;
+          /* scores */
+          int64_t j = blo;
+          if (nr == 4)
+            for (; j + 4 <= bhi; j += 4) {
+              float blk[4][4];
+              dot_4x4(q0, ldq, k0 + j * ldk, ldk, d, blk);
+              for (int r = 0; r < 4; ++r)
+                for (int c = 0; c < 4; ++c) s[r * tk + j + c] = blk[r][c] * scale;
+            }
+          for (; j < bhi; ++j)
+            for (int r = 0; r < nr; ++r) s[r * tk + j] = dot_1(q0 + r * ldq, k0 + j * ldk, d) * scale;
+          /* weights: softmax over each row's own range, rounded to the tensor type, zero outside it */
+          for (int r = 0; r < nr; ++r) {
+            float* sr = s + r * tk;
+            float mx = -INFINITY, sum = 0.0f;
+            for (int64_t jj = lo[r]; jj < hi[r]; ++jj) mx = sr[jj] > mx ? sr[jj] : mx;
+            for (int64_t jj = lo[r]; jj < hi[r]; ++jj) {
+              sr[jj] = exp_neg(sr[jj] - mx);
+              sum += sr[jj];
+            }
+            const float inv = hi[r] > lo[r] ? 1.0f / sum : 0.0f;
+            for (int64_t jj = blo; jj < bhi; ++jj)
+              sr[jj] = (jj >= lo[r] && jj < hi[r]) ? round_to(dtype, sr[jj] * inv) : 0.0f;
           }
-          float mx = -INFINITY;
-          for (int64_t j = lo; j < hi; ++j) {
-            const float sc = dot_1(qr, k + ((bi * tk + j) * hkv + kh) * (int64_t)d, d) * scale;
-            s[j] = sc;
-            if (sc > mx) mx = sc;
+          /* o = weights . v, 16 output columns of the four rows at a time held in registers */
+          for (int c0 = 0; c0 < d; c0 += 16) {
+            if (d - c0 >= 16) {
+              v8 acc[4][2];
+              for (int r = 0; r < 4; ++r) acc[r][0] = acc[r][1] = (v8){0, 0, 0, 0, 0, 0, 0, 0};
+              for (int64_t jj = blo; jj < bhi; ++jj) {
+                v8 va, vb;
+                memcpy(&va, v0 + jj * ldk + c0, 32);
+                memcpy(&vb, v0 + jj * ldk + c0 + 8, 32);
+                for (int r = 0; r < nr; ++r) {
+                  const float pw = s[r * tk + jj];
+                  acc[r][0] += pw * va;
+                  acc[r][1] += pw * vb;
+                }
+              }
+              for (int r = 0; r < nr; ++r) {
+                float* orow = o + ((bi * t + i0 + r) * h + hh) * (int64_t)d + c0;
+                for (int c = 0; c < 8; ++c) orow[c] = round_to(dtype, acc[r][0][c]);
+                for (int c = 0; c < 8; ++c) orow[8 + c] = round_to(dtype, acc[r][1][c]);
+              }
+            } else {
+              for (int r = 0; r < nr; ++r)
+                for (int c = 0; c < d - c0; ++c) {
+                  float a = 0.0f;
+                  for (int64_t jj = blo; jj < bhi; ++jj) a += s[r * tk + jj] * v0[jj * ldk + c0 + c];
+                  o[((bi * t + i0 + r) * h + hh) * (int64_t)d + c0 + c] = round_to(dtype, a);
+                }
+            }
           }
-          float sum = 0.0f;
-          for (int64_t j = lo; j < hi; ++j) {
-            s[j] = expf(s[j] - mx);
-            sum += s[j];
-          }
-          const float inv = 1.0f / sum;
-          for (int c = 0; c < d; ++c) acc[c] = 0.0f;
-          for (int64_t j = lo; j < hi; ++j) {
-            const float p = round_to(dtype, s[j] * inv);
-            const float* vr = v + ((bi * tk + j) * hkv + kh) * (int64_t)d;
-            for (int c = 0; c < d; ++c) acc[c] += p * vr[c];
-          }
-          for (int c = 0; c < d; ++c) orow[c] = round_to(dtype, acc[c]);
         }
     free(s);
-    free(acc);
   }
 }
 
