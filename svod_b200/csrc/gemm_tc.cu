@@ -309,7 +309,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           sn4[v] = ldg128((const T*)p.rope_sin + rope_pos * 64 + v * 8);
         }
       }
+      // Staged epilogue with a residual: the first sub-tile's residual is fetched
+      // into the staging buffer while the tile is still being accumulated (the
+      // buffer is free once the previous tile's store has read it).
+      const bool res_ahead = p.tma_epilogue && p.residual != nullptr && n0 + c_lo < p.n;
+      if (res_ahead && (ew & 3) == 0 && lane == 0) {
+        tma_store_wait_read();
+        mbar_expect_tx(&res_full[chalf], 128 * 128);
+        tma_load_2d(staging + chalf * (128 * 128), &tmap_r, &res_full[chalf], n0 + c_lo, mt * BM);
+      }
       if (!mbar_wait(&acc_full[as], aph, p.status)) {
+        if (res_ahead) mbar_wait(&res_full[chalf], res_phase, p.status);  // the copy in flight lands or times out
         ok = false;
         break;
       }
@@ -331,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           // the previous store out of this buffer must have read it
           if (chief) tma_store_wait_read();
           named_barrier(1 + chalf, 128);
-          if (p.residual != nullptr && chief && n_at < p.n) {
+          if (sub > 0 && p.residual != nullptr && chief && n_at < p.n) {  // the first was fetched ahead
             mbar_expect_tx(&res_full[chalf], 128 * 128);
             tma_load_2d(stg, &tmap_r, &res_full[chalf], n_at, m0);
           }

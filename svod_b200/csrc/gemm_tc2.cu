@@ -261,25 +261,33 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
       const int n0 = nt * p.out_bn;
       const int cols = p.out_bn / C::kGroups;
       const int c_lo = chalf * cols;
-      if (bias != nullptr) {
-        // This group's bias columns, brought into L1 while the tile is still being
-        // accumulated: the reads in the epilogue proper then hit.
-        const int line = (ew & 3) * 32 + lane;  // 128-byte lines: [gate | up] halves, 64 values each
-        const int up = line >= 64 ? 1 : 0;
-        const int col = n0 + c_lo + (line - 64 * up) * 64;
-        if ((line - 64 * up) * 64 < cols && col < p.n && (up == 0 || p.gated)) prefetch_l1(bias + (up ? p.n : 0) + col);
+      uint8_t* stg = staging + chalf * kGroupStaging;
+      const bool chief = (ew & 3) == 0 && lane == 0;
+      const int m0 = mt * 2 * BM + (int)rank * BM;
+      const bool rows_live = m0 < p.m;  // a ragged last tile may leave the odd CTA no row
+      if constexpr (!HEADS) {
+        // The residual of the group's first sub-tile is fetched into the staging
+        // buffer while the tile is still being accumulated (the buffer is free as
+        // soon as the previous tile's store has read it), so that its latency
+        // does not sit between the accumulator and the store.
+        const int n_first = rows_live ? n0 + c_lo : p.n;
+        if (p.residual != nullptr && chief && n_first < p.n) {
+          tma_store_wait_read();
+          mbar_expect_tx(&res_full[chalf], 128 * 128);
+          tma_load_2d(stg, &tmap_r, &res_full[chalf], n_first, m0);
+        }
       }
       if (!mbar_wait(&acc_full[as], aph, p.status)) {
+        // leave only after the residual copy in flight (if any) has landed or timed out
+        if constexpr (!HEADS) {
+          if (p.residual != nullptr && rows_live && n0 + c_lo < p.n) mbar_wait(&res_full[chalf], res_phase, p.status);
+        }
         ok = false;
         break;
       }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
-      uint8_t* stg = staging + chalf * kGroupStaging;
-      const bool chief = (ew & 3) == 0 && lane == 0;
       const int r_tile = quarter * 32 + lane;
-      const int m0 = mt * 2 * BM + (int)rank * BM;
-      const bool rows_live = m0 < p.m;  // a ragged last tile may leave the odd CTA no row
       if constexpr (HEADS) {
         // One 128-column head per column half: sum of squares over the head, then
         // both halves of the head at once (a rotated column needs its partner 64
@@ -391,7 +399,7 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
         const int n_at = rows_live ? n0 + c0 : p.n;  // past N: nothing is loaded or stored
         if (chief) tma_store_wait_read();
         named_barrier(1 + chalf, 128);
-        if (p.residual != nullptr && chief && n_at < p.n) {
+        if (sub > 0 && p.residual != nullptr && chief && n_at < p.n) {  // the first was fetched ahead
           mbar_expect_tx(&res_full[chalf], 128 * 128);
           tma_load_2d(stg, &tmap_r, &res_full[chalf], n_at, m0);
         }
@@ -565,14 +573,12 @@ bool gemm_tc2_covers(const GemmArgs& a) {
   return tiles >= sm_count2() / 2;
 }
 
-// Where the pair kernel is the default: long enough k loops to pay for the
-// pair's extra hand-shakes per tile (measured: ahead from K = 1024 on, behind
-// at K = 768); a config store may still choose either kernel per shape.
+// Where the pair kernel is the default: from K = 512 on (measured at K = 512 /
+// 768: plain 980 vs 740 and 1446 vs 1167 TFLOP/s, gated 1425 vs 1240); a config
+// store may still choose either kernel per shape.
 bool gemm_tc2_preferred(const GemmArgs& a) {
   if (!gemm_tc2_covers(a)) return false;
-  // an activation on a plain projection runs the sixteen-warp epilogue, which pays from shorter k loops on
-  const bool wide = !a.gated && a.act != kActNone && a.rope_cos == nullptr && a.norm_q == nullptr && a.norm_k == nullptr;
-  return a.k >= 1024 || (wide && a.k >= 512);
+  return a.k >= 512;
 }
 
 int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
@@ -580,7 +586,8 @@ int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len
   const int sms = sm_count2();
   const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
   // sixteen epilogue warps where each output value costs an activation
-  // (long k loops hide the epilogue anyway and prefer the deeper ring of the eight-warp variant)
+  // (long k loops hide the epilogue anyway and prefer the deeper ring of the eight-warp variant;
+  // measured: a residual alone does not pay for them)
   const bool wide = !heads && !a.gated && a.act != kActNone && a.k <= 2048;
   if (a.dtype == SVODB_BF16)
     return heads  ? run2<__nv_bfloat16, true, 8>(a, sms, s, cfg, cfg_len)

@@ -448,3 +448,35 @@ def test_persistent_attention_launches_overlapping_on_two_streams_keep_their_own
     for i in range(2):
         for g in got[i]:
             assert np.array_equal(host(g), want[i])
+
+
+def test_persistent_attention_reads_cache_slices_through_a_row_map():
+    """More items than SMs with a cache (head slice + row map): the persistent
+    kernel's loader looks the cache row up per item; same numbers as the oracle
+    and as the one-item kernel."""
+    from svod_b200 import _lib as L
+    dt, B, rows, H, Hkv, D, T, Tk = O.BF16, 6, 8, 8, 4, 64, 1000, 1100
+    rng = np.random.default_rng(31)
+    q = normal(rng, (B, T, H, D), 1.0, dt)
+    k = normal(rng, (rows, Tk, 2 * Hkv, D), 1.0, dt)
+    v = normal(rng, (rows, Tk, 2 * Hkv, D), 1.0, dt)
+    rm = np.array([7, 0, 3, 3, 5, 1])
+    lens = np.array([Tk, 77, Tk - 1, 640, 0, 1024])
+    cache = dict(head_start=Hkv, kv_heads=Hkv, row_map=rm)
+    want = O.attention(q, k, v, key_lens=lens, cache=cache, dtype=dt)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    a = ops.Attn(keys=ops.KeyMask.Lens(i32(lens)), cache=ops.Cache(Hkv, Hkv, i32(rm)))
+    Q, K, V = dev(q, dt), dev(k, dt), dev(v, dt)
+    got = host(ops.attention(Q, K, V, a))
+    assert "persistent" in ops.chosen(), ops.chosen()
+    ops.device_status()
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+    assert not got[4].any()  # a lane without keys
+    lib = L.load()
+    lib.svodb_config_set(b"attention|one_item", 1)
+    try:
+        one = host(ops.attention(Q, K, V, a))
+        assert "persistent" not in ops.chosen()
+    finally:
+        lib.svodb_config_set(b"attention|one_item", 0)
+    assert np.array_equal(got, one)
