@@ -72,6 +72,7 @@ struct Params2 {
   int norm_q_cols, norm_cols;
   float norm_eps;
   int rope_width;
+  int head_dim;      // 128 (norm and/or rotation), or 64 (rotation only)
   int64_t rope_seq;  // table rows; a tile's 128 rows never wrap around it
 };
 
@@ -183,9 +184,10 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
           }
           tab_ph ^= 1;
           const int row0 = (int)((int64_t)m0 % p.rope_seq);
-          mbar_expect_tx(tab_full, (uint32_t)kTableBytes);
-          tma_load_2d(tables, &tmap_cos, tab_full, 0, row0);
-          tma_load_2d(tables + kTableBytes / 2, &tmap_sin, tab_full, 0, row0);
+          mbar_expect_tx(tab_full, (uint32_t)(p.head_dim == 64 ? kTableBytes / 2 : kTableBytes));
+          const int tab_row = p.head_dim == 64 ? row0 / 2 : row0;  // 64-wide heads: two positions per map row
+          tma_load_2d(tables, &tmap_cos, tab_full, 0, tab_row);
+          tma_load_2d(tables + kTableBytes / 2, &tmap_sin, tab_full, 0, tab_row);
         }
       }
       // Error path: a bounded pause lets copies already in flight land before
@@ -289,6 +291,73 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
       const uint32_t t_acc = tmem_base + (uint32_t)(as * BN) + ((uint32_t)(quarter * 32) << 16);
       const int r_tile = quarter * 32 + lane;
       if constexpr (HEADS) {
+       if (p.head_dim == 64) {
+        // 64-wide heads, rotation only: a head is one 64-column sub-tile, its two
+        // 32-column halves are partners. Table rows are 64 bytes here, two to a
+        // 128-byte line of the slab (128-byte swizzle over those lines).
+        const bool tile_tables = n0 < p.rope_width;
+        if (tile_tables) {
+          if (!mbar_wait(tab_full, res_phase, p.status)) ok = false;
+          res_phase ^= 1;
+        }
+        const uint8_t* cline = tables + (r_tile >> 1) * 128;
+        const uint8_t* nline = cline + kTableBytes / 2;
+        const int half_sel = (r_tile & 1) << 2, line_x = (r_tile >> 1) & 7;
+        uint8_t* srow = stg + r_tile * 128;
+        for (int sub = 0; sub < 2; ++sub) {
+          const int h_col = n0 + c_lo + sub * 64;
+          const bool turned = h_col < p.rope_width;
+          const uint32_t t_head = t_acc + (uint32_t)(c_lo + sub * 64);
+          if (chief) tma_store_wait_read();
+          named_barrier(1 + chalf, 128);
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t_head, ra);
+          tmem_ld32(t_head + 32u, rb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              a[i] = __uint_as_float(ra[v * 8 + i]);
+              b[i] = __uint_as_float(rb[v * 8 + i]);
+            }
+            if (turned) {
+              const int at = ((half_sel | v) ^ line_x) << 4;
+              const uint4 c4 = *reinterpret_cast<const uint4*>(cline + at);
+              const uint4 s4 = *reinterpret_cast<const uint4*>(nline + at);
+              const uint32_t cu[4] = {c4.x, c4.y, c4.z, c4.w};
+              const uint32_t su[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 c2 = Elem<T>::unpack(cu[i]), s2 = Elem<T>::unpack(su[i]);
+                const float a0 = a[2 * i], a1 = a[2 * i + 1], b0 = b[2 * i], b1 = b[2 * i + 1];
+                a[2 * i] = a0 * c2.x - b0 * s2.x;
+                b[2 * i] = a0 * s2.x + b0 * c2.x;
+                a[2 * i + 1] = a1 * c2.y - b1 * s2.y;
+                b[2 * i + 1] = a1 * s2.y + b1 * c2.y;
+              }
+            }
+            *reinterpret_cast<uint4*>(srow + ((v ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(a[0], a[1]), Elem<T>::pack(a[2], a[3]), Elem<T>::pack(a[4], a[5]),
+                           Elem<T>::pack(a[6], a[7]));
+            *reinterpret_cast<uint4*>(srow + (((4 + v) ^ (r_tile & 7)) << 4)) =
+                make_uint4(Elem<T>::pack(b[0], b[1]), Elem<T>::pack(b[2], b[3]), Elem<T>::pack(b[4], b[5]),
+                           Elem<T>::pack(b[6], b[7]));
+          }
+          fence_proxy_async_smem();
+          named_barrier(1 + chalf, 128);
+          if (chief && rows_live && h_col < p.n) {
+            tma_store_2d(&tmap_c, stg, h_col, m0);
+            tma_store_commit();
+          }
+        }
+        if (tile_tables) {
+          // this warp has read its table rows
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tab_empty);
+        }
+       } else {
         // One 128-column head per column half: sum of squares over the head, then
         // both halves of the head at once (a rotated column needs its partner 64
         // columns away); the first half goes to the staging buffer, the second
@@ -393,6 +462,7 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
           tma_store_2d(&tmap_c, stg, h_col + 64, m0);
           tma_store_commit();
         }
+       }
       } else
       for (int sub = 0; sub < cols / 64; ++sub) {
         const int c0 = c_lo + sub * 64;
@@ -503,12 +573,16 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
     p.norm_q_cols = a.norm_q != nullptr ? a.norm_q_heads * 128 : 0;
     p.norm_cols = a.norm_k != nullptr ? (a.norm_q_heads + a.norm_k_heads) * 128 : p.norm_q_cols;
     p.norm_eps = a.norm_eps;
-    p.rope_width = a.rope_cos != nullptr ? a.rope_heads * 128 : 0;
+    p.head_dim = a.rope_cos != nullptr && a.rope_head_dim == 64 ? 64 : 128;
+    p.rope_width = a.rope_cos != nullptr ? a.rope_heads * p.head_dim : 0;
     p.rope_seq = a.rope_seq > 0 ? a.rope_seq : 1;
     if (a.rope_cos != nullptr) {
-      // [rope_seq rows, 64 columns] tables, one 128-row slab per CTA and tile
-      if (!make_tmap_2d(&tcos, a.rope_cos, dt, 64, (uint64_t)p.rope_seq, 64, 64, BM)) return -1;
-      if (!make_tmap_2d(&tsin, a.rope_sin, dt, 64, (uint64_t)p.rope_seq, 64, 64, BM)) return -1;
+      // [rope_seq rows, head_dim/2 columns] tables, one 128-position slab per CTA and
+      // tile. 64-wide heads have 64-byte table rows: the map views two positions as
+      // one 128-byte row, so the slab keeps the 128-byte-row swizzle.
+      const uint64_t per_row = p.head_dim == 64 ? 2 : 1;
+      if (!make_tmap_2d(&tcos, a.rope_cos, dt, 64, (uint64_t)p.rope_seq / per_row, 64, 64, BM / (uint32_t)per_row)) return -1;
+      if (!make_tmap_2d(&tsin, a.rope_sin, dt, 64, (uint64_t)p.rope_seq / per_row, 64, 64, BM / (uint32_t)per_row)) return -1;
     }
   }
   // the attribute belongs to the device's copy of the kernel: once per device
@@ -564,7 +638,9 @@ bool gemm_tc2_covers(const GemmArgs& a) {
   if (!gemm_tc_covers(a)) return false;
   const bool heads = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
   if (heads) {
-    if (a.rope_head_dim != 128 || a.bias != nullptr) return false;
+    // 128-wide heads (norm and/or rotation), or 64-wide heads with a rotation only
+    const bool wide64 = a.rope_head_dim == 64 && a.rope_cos != nullptr && a.norm_q == nullptr && a.norm_k == nullptr;
+    if ((a.rope_head_dim != 128 && !wide64) || a.bias != nullptr) return false;
     if (a.rope_cos != nullptr && (a.rope_seq <= 0 || a.rope_seq % BM != 0)) return false;
   }
   const int out_bn = a.gated ? BN / 2 : BN;

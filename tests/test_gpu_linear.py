@@ -297,3 +297,36 @@ def test_qkv_prologue_on_the_cta_pair_kernel(dt, B, T, k, H, Hkv, qn, kn, rope):
     finally:
         lib.svodb_config_set(key, 0)
     assert max_abs(got, one) == 0.0
+
+
+@pytest.mark.parametrize("dt,B,T,k,heads,extra", [
+    (O.BF16, 4, 1664, 768, 8, 256),    # ModernBERT's layout in small: q,k heads turned, v columns stored as they are
+    (O.F16, 5, 1408, 512, 12, 0),      # every column turned, ragged last row tile (27.5 pair tiles of rows)
+])
+def test_rope_of_64_wide_heads_on_the_cta_pair_kernel(dt, B, T, k, heads, extra):
+    """`Rotary` with 64-wide heads in the CTA-pair kernel's store (table slabs of
+    64-byte rows by TMA) against the oracle and, bit for bit, against the
+    one-CTA kernel's direct-store rotation."""
+    hd = 64
+    rng = np.random.default_rng(T + k)
+    n = heads * hd + extra
+    x = O.round_to(dt, rng.standard_normal((B, T, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    cos, sin = O.rope_table(160000.0, np.arange(T), hd, dt)
+    want = O.linear(x, w, None, rope=(cos, sin, heads, hd), dtype=dt)
+    o = ops.Linear(rope=ops.Rotary(dev(cos, dt).view(1, T, 1, hd // 2), dev(sin, dt).view(1, T, 1, hd // 2), heads, hd))
+    X, W = dev(x, dt), dev(w, dt)
+    got = host(ops.linear(X, W, o))
+    assert "cta_pair:1" in ops.chosen(), ops.chosen()
+    ops.device_status()
+    assert rel_close(got, want, 2e-2) and mean_rel(got, want) < 5e-3
+    from svod_b200 import _lib as L
+    lib = L.load()
+    key = lib.svodb_last_config_key()
+    lib.svodb_config_set(key, 256)
+    try:
+        one = host(ops.linear(X, W, o))
+        assert "cta_pair" not in ops.chosen() and "kernel gemm" in ops.chosen()
+    finally:
+        lib.svodb_config_set(key, 0)
+    assert max_abs(got, one) == 0.0
