@@ -801,7 +801,20 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len)
   int bn = 256;
   const bool per_head = a.rope_cos != nullptr || a.norm_q != nullptr || a.norm_k != nullptr;
   const int min_bn = a.gated ? 128 : (per_head ? 2 * a.rope_head_dim : 64);
-  while (bn > min_bn && tiles(bn) < sms) bn /= 2;
+  // Tile width by a small cost model (cycles): waves x (the longer of the tile's MMAs and the time
+  // its operands take to arrive from L2 at ~52 bytes per clock and SM, plus a fixed per-tile cost of
+  // prologue, first-load latency and epilogue). Narrow tiles fill more SMs but move more bytes per
+  // flop; the widest of equally cheap widths wins.
+  {
+    double best = 0;
+    for (int cand = 256; cand >= min_bn; cand /= 2) {
+      const double waves = (double)((tiles(cand) + sms - 1) / sms);
+      const double mma = 2.0 * cand * (a.k / BK);
+      const double feed = (double)(BM + cand) * a.k * 2.0 / 52.0;
+      const double cost = waves * ((mma > feed ? mma : feed) + 6000.0);
+      if (cand == 256 || cost < best * 0.97) best = cost, bn = cand;
+    }
+  }
   if (bn < min_bn) bn = min_bn;
   if ((a.force_bn == 64 || a.force_bn == 128 || a.force_bn == 256) && a.force_bn >= min_bn) bn = a.force_bn;
   if (bn > 256) return 1;
