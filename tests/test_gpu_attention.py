@@ -480,3 +480,44 @@ def test_persistent_attention_reads_cache_slices_through_a_row_map():
     finally:
         lib.svodb_config_set(b"attention|one_item", 0)
     assert np.array_equal(got, one)
+
+
+@pytest.mark.parametrize("window", [None, (64, 64)], ids=["global", "local +-64"])
+def test_full_size_masked_attention_properties_at_seq_8192_d64(window):
+    """Size-independent checks at the ModernBERT layer shape (12 heads of 64, seq
+    8192, bool prefix mask of ragged lengths, global or +-64 window), batch 4:
+    (1) v = ones gives ones on every row that sees a key and zeros on a lane
+    without keys; (2) keys past a lane's length do not matter (they are replaced
+    by garbage); (3) sampled rows match an f32 softmax; (4) a replay is
+    bit-identical."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    B, T, H, D = 4, 8192, 12, 64
+    lens = [8192, 5000, 0, 2049]
+    qkv = torch.randn(B, T, 3 * H * D, generator=g, device="cuda").to(torch.bfloat16)
+    mask = (torch.arange(T, device="cuda")[None, :] < torch.tensor(lens, device="cuda")[:, None])
+    a = ops.Attn(keys=ops.KeyMask.Bool(mask), window=window)
+    o = ops.attention_packed(qkv, H, H, a)
+    assert "persistent" in ops.chosen(), ops.chosen()
+    ops.device_status()
+    assert torch.equal(ops.attention_packed(qkv, H, H, a), o)
+    q, k, v = (t_.reshape(B, T, H, D) for t_ in qkv.split(H * D, dim=-1))
+    ones = ops.attention(q.contiguous(), k.contiguous(), torch.ones_like(v).contiguous(), a)
+    left = window[0] if window else T
+    for b, n in enumerate(lens):
+        seen = torch.arange(T, device="cuda") - left < n if n > 0 else torch.zeros(T, dtype=torch.bool, device="cuda")
+        assert float((ones[b][seen].float() - 1).abs().max() if seen.any() else 0.0) < 1e-2
+        assert float(ones[b][~seen].float().abs().max() if (~seen).any() else 0.0) == 0.0
+    noisy = qkv.clone().reshape(B, T, 3, H, D)
+    for b, n in enumerate(lens):
+        noisy[b, n:, 1:] = 77.0  # keys and values past the length
+    o2 = ops.attention_packed(noisy.reshape(B, T, 3 * H * D), H, H, a)
+    assert torch.equal(o2, o)
+    for (b, h, i) in [(0, 0, 0), (1, 5, 4999), (1, 11, 6000), (3, 7, 2048), (0, 3, 8191)]:
+        lo = max(0, i - window[0]) if window else 0
+        hi = min(lens[b], i + window[1] + 1) if window else lens[b]
+        if hi <= lo:
+            assert float(o[b, i, h].float().abs().max()) == 0.0
+            continue
+        s = (k[b, lo:hi, h].float() @ q[b, i, h].float()) / math.sqrt(D)
+        ref = torch.softmax(s, 0) @ v[b, lo:hi, h].float()
+        assert float((o[b, i, h].float() - ref).abs().max()) < 2e-2
