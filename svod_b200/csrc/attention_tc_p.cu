@@ -99,10 +99,27 @@ __device__ __forceinline__ void scan_mask_row(const FaParams& p, int64_t b, int 
   if (row.b == b) return;
   int first_zero = 0x7fffffff, last_set = 0;
   const int64_t base = b * p.tk;
-  for (int64_t j = lane; j < p.tk; j += 32) {
-    const int m = p.key_mask_i32 ? ((const int32_t*)p.key_mask)[base + j] : (int)((const uint8_t*)p.key_mask)[base + j];
-    if (m != 0) last_set = (int)j + 1;
-    else if ((int)j < first_zero) first_zero = (int)j;
+  if (!p.key_mask_i32 && (p.tk & 15) == 0 && (reinterpret_cast<uintptr_t>(p.key_mask) & 15) == 0) {
+    // byte masks in 16-byte pieces: per 4-byte word, 0xff for every nonzero byte
+    const uint4* row = reinterpret_cast<const uint4*>((const uint8_t*)p.key_mask + base);
+    const int pieces = (int)(p.tk >> 4);
+    for (int c = lane; c < pieces; c += 32) {
+      const uint4 u = __ldg(row + c);
+      const uint32_t wd[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t set = __vcmpne4(wd[q], 0u);
+        const int at = c * 16 + q * 4;
+        if (set != 0u) last_set = max(last_set, at + ((31 - __clz((int)set)) >> 3) + 1);
+        if (set != 0xffffffffu) first_zero = min(first_zero, at + ((__ffs((int)~set) - 1) >> 3));
+      }
+    }
+  } else {
+    for (int64_t j = lane; j < p.tk; j += 32) {
+      const int m = p.key_mask_i32 ? ((const int32_t*)p.key_mask)[base + j] : (int)((const uint8_t*)p.key_mask)[base + j];
+      if (m != 0) last_set = (int)j + 1;
+      else if ((int)j < first_zero) first_zero = (int)j;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -521,3 +521,32 @@ def test_full_size_masked_attention_properties_at_seq_8192_d64(window):
         s = (k[b, lo:hi, h].float() @ q[b, i, h].float()) / math.sqrt(D)
         ref = torch.softmax(s, 0) @ v[b, lo:hi, h].float()
         assert float((o[b, i, h].float() - ref).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("kind", ["holes", "padding"])
+def test_persistent_attention_scans_aligned_byte_masks_in_16_byte_pieces(kind):
+    """A key count that is a multiple of 16 takes the vector scan of the mask row
+    (T = 1300 above takes the byte loop): same numbers as the oracle and as the
+    one-item kernel, with holes (the softmax reads the bits) and as padding."""
+    from svod_b200 import _lib as L
+    dt, B, T, H, Hkv, D = O.BF16, 4, 1280, 8, 4, 64
+    rng = np.random.default_rng(5)
+    q, k, v = normal(rng, (B, T, H, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt)
+    mask = key_mask(B, T) if kind == "holes" else padding_mask(B, T, [1280, 17, 0, 1279])
+    if kind == "holes":
+        mask[1, 900:] = False   # holes and a tail
+        mask[2, :] = False      # a lane without keys
+    want = O.attention(q, k, v, key_mask=mask, dtype=dt)
+    a = ops.Attn(keys=ops.KeyMask.Bool(torch.from_numpy(np.asarray(mask)).cuda()))
+    Q, K, V = dev(q, dt), dev(k, dt), dev(v, dt)
+    got = host(ops.attention(Q, K, V, a))
+    assert "persistent" in ops.chosen(), ops.chosen()
+    ops.device_status()
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+    lib = L.load()
+    lib.svodb_config_set(b"attention|one_item", 1)
+    try:
+        one = host(ops.attention(Q, K, V, a))
+    finally:
+        lib.svodb_config_set(b"attention|one_item", 0)
+    assert np.array_equal(got, one)
