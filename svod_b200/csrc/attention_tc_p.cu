@@ -19,9 +19,9 @@
 //     loader) and `o_empty` (the softmax warps have read O out, the next item's
 //     first P.V may overwrite it): the loader and the issuers run into the next
 //     item while the softmax warps still finish the last one.
-// A bool key mask needs no CTA-wide scan here: every warp scans the mask row of
-// its item's batch lane for itself (once per change of lane) and the softmax
-// gathers the bits of a block's keys with a ballot.
+// A bool key mask needs no CTA-wide scan here: the loader warp scans the mask row
+// of its item's batch lane (once per change of lane) and passes the result on
+// with the item; the softmax gathers the bits of a block's keys with a ballot.
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
@@ -49,6 +49,7 @@ __device__ int g_next_item[kQueueSlots];
 
 struct Item {
   int qt, h, b, valid;
+  int mask_len, mask_general;  // what the loader's scan of a bool key mask row found (see MaskRow)
 };
 
 // Work item w in queue order: batch, KV head, query head of the group, then
@@ -59,7 +60,7 @@ struct Item {
 // ends on the lightest items of many groups rather than starting the heaviest
 // items of the last group when everything else is done.
 __device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads, int tail_groups) {
-  Item it{0, 0, 0, 0};
+  Item it{0, 0, 0, 0, 0, 0};
   if (w >= n_items) return it;
   const int group = heads / kv_heads;
   const int per_kv = group * n_qt;
@@ -87,8 +88,8 @@ __device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int he
 
 // What a bool key mask row says about a batch lane: the keys past `len` are all
 // hidden; `general` when hidden keys also lie before it (then the softmax reads
-// the row's bits block by block). Every warp scans the row for itself, all lanes
-// taking part, when its item's batch lane changes.
+// the row's bits block by block). The loader warp scans the row, all lanes taking
+// part, when its item's batch lane changes.
 struct MaskRow {
   int64_t b;
   int len;
@@ -257,14 +258,21 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (lane == 0 && mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) wi = atomicAdd(queue, 1);
           wi = __shfl_sync(0xffffffffu, wi, 0);
           if (wi < 0) break;  // the wait ran out
-          const Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups);
+          Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups);
+          // The loader alone scans a bool key mask row (all its lanes, once per change
+          // of batch lane, while it runs ahead of the other warps) and hands what it
+          // found to them with the item.
+          if (it.valid && p.key_mask != nullptr) {
+            scan_mask_row(p, it.b, lane, mrow);
+            it.mask_len = mrow.len;
+            it.mask_general = mrow.general;
+          }
           if (lane == 0) {
             item_ring[slot] = it;
             __threadfence_block();
             mbar_arrive(&item_full[slot]);
           }
           if (!it.valid) break;
-          if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
           const Work w = plan(it, mrow);
           if (w.u_hi <= w.u_lo) continue;
           if (lane == 0) {
@@ -332,7 +340,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&item_empty[slot]);
         if (!it.valid) break;
-        if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+        mrow.len = it.mask_len, mrow.general = it.mask_general;
         const Work w = plan(it, mrow);
         if (w.u_hi <= w.u_lo) continue;
         const Range r = i == 0 ? w.r0 : w.r1;
@@ -436,7 +444,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&item_empty[slot]);
       if (!it.valid) break;
-      if (p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+      mrow.len = it.mask_len, mrow.general = it.mask_general;
       const Work w = plan(it, mrow);
       if (!ok) {
         const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
