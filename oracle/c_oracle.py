@@ -76,10 +76,19 @@ def load():
     lib.so_norm_rows.argtypes = [i32, fp, fp, fp, fp, fp, fp, i64, i64, f32, i32]
     lib.so_rope_table.argtypes = [f32, ip, i64, i32, fp, fp, i32]
     lib.so_heads.argtypes = [fp, fp, fp, fp, fp, fp, fp, fp, i64, i64, i32, i32, i32, f32, i32]
-    lib.so_attention.argtypes = [fp, fp, fp, fp, i64, i64, i64, i32, i32, i32, i32, ip, i32, i32, i32, f32, i32]
+    bp = ctypes.POINTER(ctypes.c_uint8)
+    lib.so_set_threads.argtypes = [i32]
+    lib.so_attention.argtypes = [fp, fp, fp, fp, i64, i64, i64, i32, i32, i32, i32, ip, bp, i32, i32, i32, f32, i32]
+    lib.so_linear_rope.argtypes = [fp, fp, fp, fp, i64, i64, i64, i64, fp, fp, i32, i32, i32]
     lib.so_qwen3_layers.argtypes = [fp, ctypes.POINTER(fp), i32, i64, i64, i32, i32, i32, i32, i32, f32, f32, i32]
     lib.so_qwen3_layers.restype = i32
-    for fn in (lib.so_round, lib.so_linear, lib.so_norm_rows, lib.so_rope_table, lib.so_heads, lib.so_attention):
+    lib.so_xlmr_layers.argtypes = [fp, ctypes.POINTER(fp), i32, i64, i64, i32, i32, i32, bp, f32, i32]
+    lib.so_xlmr_layers.restype = i32
+    lib.so_modernbert_layers.argtypes = [fp, ctypes.POINTER(fp), i32, i32, i64, i64, i32, i32, i32, bp, i32, f32, f32,
+                                         i32, i32, f32, i32]
+    lib.so_modernbert_layers.restype = i32
+    for fn in (lib.so_round, lib.so_linear, lib.so_norm_rows, lib.so_rope_table, lib.so_heads, lib.so_attention,
+               lib.so_linear_rope, lib.so_set_threads):
         fn.restype = None
     _LIB = lib
     return lib
@@ -87,6 +96,17 @@ def load():
 
 def threads() -> int:
     return int(load().so_threads())
+
+
+def use_all_cores() -> int:
+    """Sizes the OpenMP team to every core this process may run on, whatever
+    `OMP_NUM_THREADS` said (launchers such as torchrun export 1); returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    load().so_set_threads(n)
+    return threads()
 
 
 def _f(a):
@@ -141,17 +161,39 @@ def heads(qkv, heads_n, kv_heads, d, q_w=None, k_w=None, eps=1e-6, cos=None, sin
     return q, k, v
 
 
-def attention(q, k, v, *, causal=False, key_lens=None, window=None, scale=None, dtype=BF16):
+def _bp(a):
+    return None if a is None else a.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8))
+
+
+def _mask(m):
+    return None if m is None else np.ascontiguousarray(np.asarray(m) != 0, dtype=np.uint8)
+
+
+def attention(q, k, v, *, causal=False, key_lens=None, key_mask=None, window=None, scale=None, dtype=BF16):
     q, k, v = _f(q), _f(k), _f(v)
     b, t, h, d = q.shape
     tk, hkv = k.shape[1], k.shape[2]
     lens = None if key_lens is None else np.ascontiguousarray(key_lens, dtype=np.int32)
+    km = _mask(key_mask)
     o = np.empty_like(q)
     sc = float(np.float32(1.0 / np.sqrt(d))) if scale is None else float(scale)
     wl, wr = window if window is not None else (0, 0)
-    load().so_attention(_p(q), _p(k), _p(v), _p(o), b, t, tk, h, hkv, d, int(causal), _ip(lens), int(window is not None),
-                        int(wl), int(wr), sc, dtype)
+    load().so_attention(_p(q), _p(k), _p(v), _p(o), b, t, tk, h, hkv, d, int(causal), _ip(lens), _bp(km),
+                        int(window is not None), int(wl), int(wr), sc, dtype)
     return o
+
+
+def linear_rope(x, w, cos, sin, heads_n, head_dim, bias=None, dtype=BF16):
+    """`x [B,T,K] . w^T (+ bias)` with the first `heads_n*head_dim` output columns
+    turned in the store; tables `[T, head_dim/2]`."""
+    x, w, bias, cos, sin = _f(x), _f(w), _f(bias), _f(cos), _f(sin)
+    k = x.shape[-1]
+    t = x.shape[-2]
+    n = w.shape[0]
+    out = np.empty(x.shape[:-1] + (n,), dtype=np.float32)
+    load().so_linear_rope(_p(x), _p(w), _p(bias), _p(out), x.size // k, n, k, t, _p(cos), _p(sin), heads_n, head_dim,
+                          dtype)
+    return out
 
 
 QWEN3_LAYER_KEYS = ("in_w", "qkv_w", "qn_w", "kn_w", "o_w", "post_w", "gu_w", "down_w")
@@ -168,6 +210,47 @@ def qwen3_layers(hidden, layers, *, heads_n, kv_heads, head_dim, theta=1e6, eps=
     f = keep[0][7].shape[1]
     rc = load().so_qwen3_layers(_p(hid), flat, len(layers), b, t, dm, heads_n, kv_heads, head_dim, f, float(theta),
                                 float(eps), dtype)
+    if rc != 0:
+        raise MemoryError("the C oracle could not allocate its scratch")
+    return hid
+
+
+XLMR_LAYER_KEYS = ("q_w", "q_b", "k_w", "k_b", "v_w", "v_b", "o_w", "o_b", "ln1_w", "ln1_b", "fi_w", "fi_b", "fo_w",
+                   "fo_b", "ln2_w", "ln2_b")
+
+
+def _flat(layers, keys):
+    keep = [[_f(lp.get(k)) for k in keys] for lp in layers]
+    fp = ctypes.POINTER(ctypes.c_float)
+    return keep, (fp * (len(keys) * len(layers)))(*[_p(a) for lw in keep for a in lw])
+
+
+def xlmr_layers(hidden, layers, mask, *, heads_n, eps=1e-5, dtype=F16):
+    """Runs XLM-R encoder layers over `hidden [B,T,D]` (a copy); `mask [B,T]` nonzero = real token."""
+    hid = np.array(hidden, dtype=np.float32, order="C")
+    b, t, dm = hid.shape
+    keep, flat = _flat(layers, XLMR_LAYER_KEYS)
+    km = _mask(mask)
+    rc = load().so_xlmr_layers(_p(hid), flat, len(layers), b, t, dm, heads_n, keep[0][10].shape[0], _bp(km), float(eps),
+                               dtype)
+    if rc != 0:
+        raise MemoryError("the C oracle could not allocate its scratch")
+    return hid
+
+
+MODERNBERT_LAYER_KEYS = ("attn_ln_w", "qkv_w", "o_w", "mlp_ln_w", "wi_w", "wo_w")
+
+
+def modernbert_layers(hidden, layers, mask, *, heads_n, first_layer=0, global_every=3, global_theta=160000.0,
+                      local_theta=10000.0, local_window=(64, 64), eps=1e-5, dtype=BF16):
+    """Runs ModernBERT layers `first_layer ...` over `hidden [B,T,D]` (a copy)."""
+    hid = np.array(hidden, dtype=np.float32, order="C")
+    b, t, dm = hid.shape
+    keep, flat = _flat(layers, MODERNBERT_LAYER_KEYS)
+    km = _mask(mask)
+    rc = load().so_modernbert_layers(_p(hid), flat, len(layers), first_layer, b, t, dm, heads_n, keep[0][5].shape[1],
+                                     _bp(km), global_every, float(global_theta), float(local_theta),
+                                     int(local_window[0]), int(local_window[1]), float(eps), dtype)
     if rc != 0:
         raise MemoryError("the C oracle could not allocate its scratch")
     return hid

@@ -15,8 +15,10 @@
  *   norms       tensor/src/nn/norm.rs:333-358, fused sum tk/src/kernels/rows.rs:76-114
  *   rope table  tensor/src/transformer.rs:130-164
  *   rounding    tk/src/interp.rs:37-71 (nearest even)
- * and the Qwen3 layer wiring of model/src/qwen3/{attention.rs:69-113, feed_forward.rs:38-42,
- * decoder_layer.rs:55-65}.
+ * and the layer wiring of the three callers:
+ *   Qwen3       model/src/qwen3/{attention.rs:69-113, feed_forward.rs:38-42, decoder_layer.rs:55-65}
+ *   XLM-R       model/src/xlm_roberta/{attention.rs:63-77, feed_forward.rs:40-45, encoder_layer.rs:45-49}
+ *   ModernBERT  model/src/modernbert/{attention.rs:52-68, mlp.rs:41-46, encoder_layer.rs:52-60, encoder.rs:33-54}
  *
  * Tensors are f32 arrays that hold values already rounded to the 16-bit type
  * (`dtype`: 0 = bf16, 1 = f16, 2 = f32 keeps every bit). The numpy float64
@@ -78,6 +80,15 @@ int so_threads(void) {
   return omp_get_max_threads();
 #else
   return 1;
+#endif
+}
+
+/* Sets the team size of the loops below, whatever OMP_NUM_THREADS said at start-up. */
+void so_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
 #endif
 }
 
@@ -305,10 +316,11 @@ static inline float exp_neg(float x) {
 
 /* ---- attention (tensor/src/transformer.rs:358-531): f32 scores and softmax, weights cast to the
  * tensor dtype before @V (:526-530), hidden keys excluded, a row with no visible key -> 0 ---- */
-/* q [b,t,h,d], k,v [b,tk,hkv,d], o [b,t,h,d]; key_lens [b] or NULL; window (left,right) when has_window */
+/* q [b,t,h,d], k,v [b,tk,hkv,d], o [b,t,h,d]; key_lens [b] or NULL; key_mask [b,tk] bytes (nonzero = visible,
+ * `KeyMask::Bool`) or NULL; window (left,right) when has_window */
 void so_attention(const float* q, const float* k, const float* v, float* o, int64_t b, int64_t t, int64_t tk, int h,
-                  int hkv, int d, int causal, const int32_t* key_lens, int has_window, int win_left, int win_right,
-                  float scale, int dtype) {
+                  int hkv, int d, int causal, const int32_t* key_lens, const uint8_t* key_mask, int has_window,
+                  int win_left, int win_right, float scale, int dtype) {
   const int group = h / hkv;
   const int64_t row_blocks = (t + 3) / 4;
   const int64_t ldq = (int64_t)h * d, ldk = (int64_t)hkv * d;
@@ -356,12 +368,16 @@ void so_attention(const float* q, const float* k, const float* v, float* o, int6
           for (int r = 0; r < nr; ++r) {
             float* sr = s + r * tk;
             float mx = -INFINITY, sum = 0.0f;
+            if (key_mask)
+              for (int64_t jj = lo[r]; jj < hi[r]; ++jj)
+                if (!key_mask[bi * tk + jj]) sr[jj] = -INFINITY;
             for (int64_t jj = lo[r]; jj < hi[r]; ++jj) mx = sr[jj] > mx ? sr[jj] : mx;
+            const int empty = !(mx > -INFINITY); /* no visible key (also the empty range) */
             for (int64_t jj = lo[r]; jj < hi[r]; ++jj) {
-              sr[jj] = exp_neg(sr[jj] - mx);
+              sr[jj] = empty ? 0.0f : exp_neg(sr[jj] - mx);
               sum += sr[jj];
             }
-            const float inv = hi[r] > lo[r] ? 1.0f / sum : 0.0f;
+            const float inv = empty ? 0.0f : 1.0f / sum;
             for (int64_t jj = blo; jj < bhi; ++jj)
               sr[jj] = (jj >= lo[r] && jj < hi[r]) ? round_to(dtype, sr[jj] * inv) : 0.0f;
           }
@@ -426,7 +442,7 @@ int so_qwen3_layers(float* hid, const float* const* weights, int n_layers, int64
       so_norm_rows(1, hid, w[0], NULL, NULL, xn, NULL, rows, dm, eps, dtype);
       so_linear(xn, w[1], NULL, NULL, qkv, rows, total, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
       so_heads(qkv, w[2], w[3], cs, sn, q, k, v, b, t, h, hkv, d, eps, dtype);
-      so_attention(q, k, v, a, b, t, t, h, hkv, d, 1, NULL, 0, 0, 0, scale, dtype);
+      so_attention(q, k, v, a, b, t, t, h, hkv, d, 1, NULL, NULL, 0, 0, 0, scale, dtype);
       so_linear(a, w[4], NULL, hid, h2, rows, dm, (int64_t)h * d, SO_ACT_NONE, 0, 0, 1.0f, dtype);
       so_norm_rows(1, h2, w[5], NULL, NULL, xn, NULL, rows, dm, eps, dtype);
       so_linear(xn, w[6], NULL, NULL, g, rows, f, dm, SO_ACT_SILU, 1, 0, 1.0f, dtype);
@@ -435,5 +451,116 @@ int so_qwen3_layers(float* hid, const float* const* weights, int n_layers, int64
     rc = 0;
   }
   free(xn), free(qkv), free(q), free(k), free(v), free(a), free(g), free(h2), free(cs), free(sn), free(pos);
+  return rc;
+}
+
+/* ---- RoPE in the projection's store (tk/src/kernels/gemm.rs:670-718): x.w^T + bias, then the first
+ * heads*hd output columns turned by split halves, row r at position r % t, then the one rounding ---- */
+void so_linear_rope(const float* x, const float* w, const float* bias, float* out, int64_t m, int64_t n, int64_t k,
+                    int64_t t, const float* cos_t, const float* sin_t, int heads, int hd, int dtype) {
+  so_linear(x, w, bias, NULL, out, m, n, k, SO_ACT_NONE, 0, 0, 1.0f, SO_F32);
+  const int half = hd / 2;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < m; ++r) {
+    float* y = out + r * n;
+    const int64_t pos = r % t;
+    for (int hh = 0; hh < heads; ++hh)
+      for (int c = 0; c < half; ++c) {
+        const float cs = cos_t[pos * half + c], sn = sin_t[pos * half + c];
+        const float y1 = y[hh * hd + c], y2 = y[hh * hd + c + half];
+        y[hh * hd + c] = y1 * cs - y2 * sn;
+        y[hh * hd + c + half] = y1 * sn + y2 * cs;
+      }
+    for (int64_t c = 0; c < n; ++c) y[c] = round_to(dtype, y[c]);
+  }
+}
+
+/* ---- XLM-R layers (model/src/xlm_roberta/encoder_layer.rs:45-49): post-LN, h [b,t,dm] in place ---- */
+/* weights per layer, in this order (16): q_w [dm,dm], q_b, k_w, k_b, v_w, v_b, o_w, o_b, ln1_w, ln1_b,
+ * fi_w [f,dm], fi_b, fo_w [dm,f], fo_b, ln2_w, ln2_b. key_mask [b,t] bytes (nonzero = visible). */
+int so_xlmr_layers(float* hid, const float* const* weights, int n_layers, int64_t b, int64_t t, int dm, int h, int f,
+                   const uint8_t* key_mask, float eps, int dtype) {
+  const int64_t rows = b * t;
+  const int d = dm / h;
+  float* q = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* k = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* v = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* a = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* x = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* y = (float*)malloc((size_t)(rows * f) * sizeof(float));
+  int rc = -1;
+  if (q && k && v && a && x && y) {
+    const float scale = 1.0f / sqrtf((float)d);
+    for (int l = 0; l < n_layers; ++l) {
+      const float* const* w = weights + (int64_t)l * 16;
+      so_linear(hid, w[0], w[1], NULL, q, rows, dm, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_linear(hid, w[2], w[3], NULL, k, rows, dm, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_linear(hid, w[4], w[5], NULL, v, rows, dm, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_attention(q, k, v, a, b, t, t, h, h, d, 0, NULL, key_mask, 0, 0, 0, scale, dtype);
+      so_linear(a, w[6], w[7], hid, x, rows, dm, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_norm_rows(0, x, w[8], w[9], NULL, hid, NULL, rows, dm, eps, dtype);
+      so_linear(hid, w[10], w[11], NULL, y, rows, f, dm, SO_ACT_GELU, 0, 0, 1.0f, dtype);
+      so_linear(y, w[12], w[13], hid, x, rows, dm, f, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_norm_rows(0, x, w[14], w[15], NULL, hid, NULL, rows, dm, eps, dtype);
+    }
+    rc = 0;
+  }
+  free(q), free(k), free(v), free(a), free(x), free(y);
+  return rc;
+}
+
+/* ---- ModernBERT layers (model/src/modernbert/encoder_layer.rs:52-60): pre-LN without bias, h in place ---- */
+/* weights per layer, in this order (6): attn_ln_w [dm] or NULL (layer 0 has none), qkv_w [3dm,dm], o_w [dm,dm],
+ * mlp_ln_w [dm], wi_w [2f,dm] (gate rows first), wo_w [dm,f]. Layer `first_layer + l` is global (no window,
+ * global_theta) when its index is a multiple of `global_every`, else local (window, local_theta)
+ * (model/src/modernbert/encoder.rs:33-54, config.rs:78-92). */
+int so_modernbert_layers(float* hid, const float* const* weights, int n_layers, int first_layer, int64_t b, int64_t t,
+                         int dm, int h, int f, const uint8_t* key_mask, int global_every, float global_theta,
+                         float local_theta, int win_left, int win_right, float eps, int dtype) {
+  const int64_t rows = b * t;
+  const int d = dm / h, half = d / 2;
+  float* xn = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* qkv = (float*)malloc((size_t)(rows * 3 * dm) * sizeof(float));
+  float* q = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* k = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* v = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* a = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* h2 = (float*)malloc((size_t)(rows * dm) * sizeof(float));
+  float* g = (float*)malloc((size_t)(rows * f) * sizeof(float));
+  float* tab = (float*)malloc((size_t)(4 * t * half) * sizeof(float)); /* cos, sin global; cos, sin local */
+  int32_t* pos = (int32_t*)malloc((size_t)t * sizeof(int32_t));
+  int rc = -1;
+  if (xn && qkv && q && k && v && a && h2 && g && tab && pos) {
+    for (int64_t i = 0; i < t; ++i) pos[i] = (int32_t)i;
+    so_rope_table(global_theta, pos, t, d, tab, tab + t * half, dtype);
+    so_rope_table(local_theta, pos, t, d, tab + 2 * t * half, tab + 3 * t * half, dtype);
+    const float scale = 1.0f / sqrtf((float)d);
+    for (int l = 0; l < n_layers; ++l) {
+      const float* const* w = weights + (int64_t)l * 6;
+      const int is_global = (first_layer + l) % global_every == 0;
+      const float* cs = is_global ? tab : tab + 2 * t * half;
+      const float* sn = cs + t * half;
+      const float* src = hid;
+      if (w[0]) {
+        so_norm_rows(0, hid, w[0], NULL, NULL, xn, NULL, rows, dm, eps, dtype);
+        src = xn;
+      }
+      so_linear_rope(src, w[1], NULL, qkv, rows, 3 * (int64_t)dm, dm, t, cs, sn, 2 * h, d, dtype);
+      /* the packed projection read in place = three column windows (tk/src/ops/attention.rs:107-122) */
+#pragma omp parallel for schedule(static)
+      for (int64_t r = 0; r < rows; ++r) {
+        memcpy(q + r * dm, qkv + r * 3 * dm, (size_t)dm * sizeof(float));
+        memcpy(k + r * dm, qkv + r * 3 * dm + dm, (size_t)dm * sizeof(float));
+        memcpy(v + r * dm, qkv + r * 3 * dm + 2 * dm, (size_t)dm * sizeof(float));
+      }
+      so_attention(q, k, v, a, b, t, t, h, h, d, 0, NULL, key_mask, !is_global, win_left, win_right, scale, dtype);
+      so_linear(a, w[2], NULL, hid, h2, rows, dm, dm, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+      so_norm_rows(0, h2, w[3], NULL, NULL, xn, NULL, rows, dm, eps, dtype);
+      so_linear(xn, w[4], NULL, NULL, g, rows, f, dm, SO_ACT_GELU, 1, 0, 1.0f, dtype);
+      so_linear(g, w[5], NULL, h2, hid, rows, dm, f, SO_ACT_NONE, 0, 0, 1.0f, dtype);
+    }
+    rc = 0;
+  }
+  free(xn), free(qkv), free(q), free(k), free(v), free(a), free(h2), free(g), free(tab), free(pos);
   return rc;
 }

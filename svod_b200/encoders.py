@@ -109,9 +109,15 @@ class XlmRobertaEncoder:
         H = c.num_attention_heads
         x = ops.embed(ids, p["word"], p["pos"], p["type"], c.pad_token_id)
         x = ops.layer_norm(x, p["emb_ln_w"], p["emb_ln_b"], c.layer_norm_eps)
+        return self.run_layers(x, mask)
+
+    def run_layers(self, x: torch.Tensor, mask: torch.Tensor, start: int = 0, stop: Optional[int] = None):
+        """Layers `start .. stop` over the hidden states `x [B,L,D]`."""
+        c, p = self.cfg, self.p
+        H = c.num_attention_heads
         B, L, D = x.shape
         keys = KeyMask.Bool(mask)
-        for lp in p["layers"]:
+        for lp in p["layers"][start:stop]:
             qkv = ops.linear(x, lp["qkv_w"], Linear(bias=lp["qkv_b"]))
             a = ops.attention_packed(qkv, H, H, Attn(keys=keys)).view(B, L, D)
             y = ops.linear(a, lp["o_w"], Linear(bias=lp["o_b"], residual=x))
@@ -158,10 +164,17 @@ class Qwen3Embedder:
                rope=None) -> torch.Tensor:
         c, p = self.cfg, self.p
         H, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
-        x = ops.embed(ids, p["embed"])
+        x = self.run_layers(ops.embed(ids, p["embed"]), seg_start, rope)
+        return ops.rms_norm(x, p["norm_w"], c.rms_norm_eps)
+
+    def run_layers(self, x: torch.Tensor, seg_start: Optional[torch.Tensor] = None, rope=None, start: int = 0,
+                   stop: Optional[int] = None) -> torch.Tensor:
+        """Layers `start .. stop` over the hidden states `x [B,L,D]` (no final norm)."""
+        c, p = self.cfg, self.p
+        H, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         B, L, D = x.shape
         rope = rope or self.rope(L, x.device)
-        for lp in p["layers"]:
+        for lp in p["layers"][start:stop]:
             xn = ops.rms_norm(x, lp["in_w"], c.rms_norm_eps)
             prologue = Qkv(H, Hkv, hd, lp["qn_w"], lp["kn_w"], c.rms_norm_eps, rope)
             if self.fused_prologue:
@@ -177,7 +190,7 @@ class Qwen3Embedder:
             hn = ops.rms_norm(h, lp["post_w"], c.rms_norm_eps)
             g = ops.linear(hn, lp["gu_w"], Linear(act=Act.SILU, gated=True))
             x = ops.linear(g, lp["down_w"], Linear(residual=h))
-        return ops.rms_norm(x, p["norm_w"], c.rms_norm_eps)
+        return x
 
     def forward(self, ids, lengths, out=None):
         return ops.pool(self.hidden(ids), lengths, ops.POOL_LAST, True, out)
@@ -217,11 +230,18 @@ class ModernBertEncoder:
         H = c.num_attention_heads
         hd = c.hidden_size // H
         x = ops.layer_norm(ops.embed(ids, p["embed"]), p["emb_ln_w"], None, c.norm_eps)
+        return ops.layer_norm(self.run_layers(x, mask), p["final_ln_w"], None, c.norm_eps)
+
+    def run_layers(self, x: torch.Tensor, mask: torch.Tensor, start: int = 0, stop: Optional[int] = None):
+        """Layers `start .. stop` over the hidden states `x [B,L,D]` (no final norm)."""
+        c, p = self.cfg, self.p
+        H = c.num_attention_heads
+        hd = c.hidden_size // H
         B, L, D = x.shape
         tables = self.rope(L, x.device)
         keys = KeyMask.Bool(mask)
         half = c.local_attention // 2
-        for li, lp in enumerate(p["layers"]):
+        for li, lp in list(enumerate(p["layers"]))[start:stop]:
             is_global = li % c.global_attn_every_n_layers == 0
             cos, sin = tables[is_global]
             xn = x if lp["attn_ln_w"] is None else ops.layer_norm(x, lp["attn_ln_w"], None, c.norm_eps)
@@ -231,7 +251,7 @@ class ModernBertEncoder:
             hn = ops.layer_norm(h, lp["mlp_ln_w"], None, c.norm_eps)
             g = ops.linear(hn, lp["wi_w"], Linear(act=Act.GELU, gated=True))
             x = ops.linear(g, lp["wo_w"], Linear(residual=h))
-        return ops.layer_norm(x, p["final_ln_w"], None, c.norm_eps)
+        return x
 
     def forward(self, ids, mask, out=None):
         h = self.hidden(ids, mask)

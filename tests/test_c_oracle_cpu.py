@@ -123,3 +123,91 @@ def test_qwen3_layers_match_the_numpy_stack():
         hn, _ = O.norm_rows("rms", x, lp["post_w"], eps=1e-6, dtype=dt)
         x = O.linear(O.linear(hn, lp["gu_w"], act=O.ACT_SILU, gated=True, dtype=dt), lp["down_w"], residual=x, dtype=dt)
     assert np.abs(got - x).max() < 4e-2 and np.abs(got - x).mean() / np.abs(x).mean() < 5e-3
+
+
+def test_attention_with_a_bool_key_mask_matches():
+    """`KeyMask::Bool` with holes (the `(b+j)%5 != 2` mask of tk/src/test/unit/attention.rs:69-99)
+    and a batch lane with no visible key."""
+    rng = np.random.default_rng(7)
+    for odt, cdt in DT:
+        q, k, v = r(rng, (3, 40, 4, 64), odt), r(rng, (3, 40, 2, 64), odt), r(rng, (3, 40, 2, 64), odt)
+        mask = np.array([[(b + j) % 5 != 2 for j in range(40)] for b in range(3)])
+        mask[2] = False
+        for kw in (dict(), dict(window=(6, 2))):
+            got = C.attention(q, k, v, key_mask=mask, dtype=cdt, **kw)
+            want = O.attention(q, k, v, key_mask=mask, dtype=odt, **kw)
+            assert np.abs(got - want).max() < 2e-2
+            assert np.abs(got - want).mean() / np.abs(want).mean() < 5e-3
+            assert not got[2].any()
+
+
+def test_rope_in_the_projection_store_matches():
+    rng = np.random.default_rng(8)
+    for odt, cdt in DT:
+        B, T, K, H, hd = 2, 30, 48, 3, 16
+        x, w, b = r(rng, (B, T, K), odt), r(rng, (H * hd + 20, K), odt, 0.2), r(rng, (H * hd + 20,), odt, 0.2)
+        cos, sin = C.rope_table(1e4, np.arange(T), hd, cdt)
+        got = C.linear_rope(x, w, cos, sin, H, hd, bias=b, dtype=cdt)
+        want = O.linear(x, w, b, rope=(cos, sin, H, hd), dtype=odt)
+        assert np.abs(got - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
+        assert np.mean(got == want) > 0.97
+
+
+def test_xlmr_layers_match_the_numpy_stack():
+    rng = np.random.default_rng(9)
+    dt, D, H, F, L, B = O.F16, 128, 4, 256, 48, 2
+    w = lambda *s: r(rng, s, dt, 0.05)
+    lps = []
+    for _ in range(2):
+        lp = {k: w(*s) for k, s in dict(q_w=(D, D), q_b=(D,), k_w=(D, D), k_b=(D,), v_w=(D, D), v_b=(D,), o_w=(D, D),
+                                        o_b=(D,), fi_w=(F, D), fi_b=(F,), fo_w=(D, F), fo_b=(D,), ln1_b=(D,),
+                                        ln2_b=(D,)).items()}
+        lp["ln1_w"], lp["ln2_w"] = O.round_to(dt, 1 + w(D)).astype(np.float32), O.round_to(dt, 1 + w(D)).astype(np.float32)
+        lps.append(lp)
+    hidden = r(rng, (B, L, D), dt)
+    mask = np.arange(L)[None, :] < np.array([L, 19])[:, None]
+    got = C.xlmr_layers(hidden, lps, mask, heads_n=H, dtype=C.F16)
+    h = hidden.astype(np.float64)
+    hd = D // H
+    for lp in lps:
+        q = O.linear(h, lp["q_w"], lp["q_b"], dtype=dt).reshape(B, L, H, hd)
+        k = O.linear(h, lp["k_w"], lp["k_b"], dtype=dt).reshape(B, L, H, hd)
+        v = O.linear(h, lp["v_w"], lp["v_b"], dtype=dt).reshape(B, L, H, hd)
+        a = O.attention(q, k, v, key_mask=mask, dtype=dt).reshape(B, L, D)
+        x = O.linear(a, lp["o_w"], lp["o_b"], residual=h, dtype=dt)
+        h, _ = O.norm_rows("layer", x, lp["ln1_w"], lp["ln1_b"], eps=1e-5, dtype=dt)
+        y = O.linear(h, lp["fi_w"], lp["fi_b"], act=O.ACT_GELU, dtype=dt)
+        x = O.linear(y, lp["fo_w"], lp["fo_b"], residual=h, dtype=dt)
+        h, _ = O.norm_rows("layer", x, lp["ln2_w"], lp["ln2_b"], eps=1e-5, dtype=dt)
+    live = mask[..., None] & np.ones((1, 1, D), dtype=bool)
+    assert np.abs(got - h)[live].max() < 2e-2 and np.abs(got - h)[live].mean() / np.abs(h[live]).mean() < 5e-3
+
+
+def test_modernbert_layers_match_the_numpy_stack():
+    rng = np.random.default_rng(10)
+    dt, D, H, F, L, B = O.BF16, 128, 4, 192, 200, 2
+    w = lambda *s: r(rng, s, dt, 0.05)
+    one = lambda n: O.round_to(dt, 1 + w(n)).astype(np.float32)
+    lps = [dict(attn_ln_w=None if i == 0 else one(D), qkv_w=w(3 * D, D), o_w=w(D, D), mlp_ln_w=one(D),
+                wi_w=w(2 * F, D), wo_w=w(D, F)) for i in range(4)]
+    hidden = r(rng, (B, L, D), dt)
+    mask = np.arange(L)[None, :] < np.array([L, 77])[:, None]
+    got = C.modernbert_layers(hidden, lps, mask, heads_n=H, dtype=C.BF16)
+    h = hidden.astype(np.float64)
+    hd = D // H
+    tabs = {True: O.rope_table(160000.0, np.arange(L), hd, dt), False: O.rope_table(10000.0, np.arange(L), hd, dt)}
+    for li, lp in enumerate(lps):
+        glob = li % 3 == 0
+        cos, sin = tabs[glob]
+        xn = h if lp["attn_ln_w"] is None else O.norm_rows("layer", h, lp["attn_ln_w"], eps=1e-5, dtype=dt)[0]
+        qkv = O.linear(xn, lp["qkv_w"], rope=(cos, sin, 2 * H, hd), dtype=dt)
+        a = O.attention_packed(qkv, H, H, key_mask=mask, window=None if glob else (64, 64), dtype=dt).reshape(B, L, D)
+        h = O.linear(a, lp["o_w"], residual=h, dtype=dt)
+        hn, _ = O.norm_rows("layer", h, lp["mlp_ln_w"], eps=1e-5, dtype=dt)
+        h = O.linear(O.linear(hn, lp["wi_w"], act=O.ACT_GELU, gated=True, dtype=dt), lp["wo_w"], residual=h, dtype=dt)
+    live = mask[..., None] & np.ones((1, 1, D), dtype=bool)
+    assert np.abs(got - h)[live].max() < 4e-2 and np.abs(got - h)[live].mean() / np.abs(h[live]).mean() < 5e-3
+    # the layer index decides global / local: starting at layer 1 the first layer is windowed
+    one_layer = C.modernbert_layers(hidden, lps[1:2], mask, heads_n=H, first_layer=1, dtype=C.BF16)
+    as_global = C.modernbert_layers(hidden, lps[1:2], mask, heads_n=H, first_layer=0, dtype=C.BF16)
+    assert not np.array_equal(one_layer, as_global)

@@ -26,9 +26,14 @@ def to_dev(p, dt):
 
 
 def check_pooled(got, want, hidden_got, hidden_want):
-    # pooled, L2-normalised f32 embeddings: max-abs 2e-2 / mean-rel 5e-3 at 16-bit
-    assert max_abs(got, want) < 2e-2, max_abs(got, want)
-    assert mean_rel(hidden_got, hidden_want) < 2e-2
+    # 16-bit bounds on both the hidden states and the pooled, L2-normalised f32
+    # embeddings: max-abs 2e-2 / mean-rel 5e-3
+    report = (f"hidden max-abs {max_abs(hidden_got, hidden_want):.3e} mean-rel {mean_rel(hidden_got, hidden_want):.3e}; "
+              f"pooled max-abs {max_abs(got, want):.3e} mean-rel {mean_rel(got, want):.3e}")
+    print(report)
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3, report
+    assert mean_rel(hidden_got, hidden_want) < 5e-3, report
+    assert max_abs(hidden_got, hidden_want) < 2e-2 * max(1.0, float(np.abs(hidden_want).max())), report
 
 
 def test_xlm_roberta_stack_matches_the_oracle():

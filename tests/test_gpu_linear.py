@@ -111,22 +111,31 @@ def test_into_stores_a_channel_window():
     assert np.all(got[:, :32] == 3.0) and np.all(got[:, 64:] == 3.0)
 
 
-@pytest.mark.parametrize("m", [512, 4096])
-@pytest.mark.parametrize("nk", [768, 1024])
-@pytest.mark.parametrize("epi", ["gelu_tanh", "swiglu"])
+@pytest.mark.parametrize("m", [512, 4096, 32768])
+@pytest.mark.parametrize("nk", [768, 1024, 4096])
+@pytest.mark.parametrize("epi", ["gelu", "gelu_tanh", "swiglu"])
 def test_sweep_shapes_of_the_gemm_benchmark(m, nk, epi):
-    """The benchmark sweep's smaller shapes: bf16 N(0,0.02) inputs, bias, GELU
-    (tanh) and SwiGLU epilogues; max-abs 2e-2 / mean-rel 5e-3."""
+    """Every shape of the benchmark sweep (M in {512, 4096, 32768}, N = K in
+    {768, 1024, 4096}): bf16 N(0,0.02) inputs and bias, erf-GELU, GELU (tanh) and
+    SwiGLU (gate rows over up rows) epilogues. The whole product runs on the
+    GPU; 64 seeded output rows (the first and last among them) are compared
+    with the oracle on the same rows: max-abs 2e-2 / mean-rel 5e-3."""
     dt = O.BF16
-    rng = np.random.default_rng(2000 + m + nk)
+    g = torch.Generator(device="cuda").manual_seed(2000 + m + nk)
     gated = epi == "swiglu"
-    x = O.round_to(dt, rng.standard_normal((m, nk)) * 0.02)
-    w = O.round_to(dt, rng.standard_normal(((2 if gated else 1) * nk, nk)) * 0.02)
-    b = O.round_to(dt, rng.standard_normal((2 if gated else 1) * nk) * 0.02)
-    act = O.ACT_SILU if gated else O.ACT_GELU_TANH
-    want = O.linear(x, w, b, act, gated, dtype=dt)
-    got = run_linear(x, w, dt, b, act, gated)
-    assert max_abs(got, want) <= 2e-2 and mean_rel(got, want) <= 5e-3
+    halves = 2 if gated else 1
+    x = (torch.randn(m, nk, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    w = (torch.randn(halves * nk, nk, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b = (torch.randn(halves * nk, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    act = dict(gelu=O.ACT_GELU, gelu_tanh=O.ACT_GELU_TANH, swiglu=O.ACT_SILU)[epi]
+    y = ops.linear(x, w, ops.Linear(bias=b, act=ops.Act(act), gated=gated))
+    assert "kernel gemm" in ops.chosen()
+    rows = np.unique(np.concatenate([[0, m - 1], np.random.default_rng(m + nk).integers(0, m, 62)]))
+    idx = torch.from_numpy(rows).cuda()
+    want = O.linear(host(x[idx]), host(w), host(b), act, gated, dtype=dt)
+    got = host(y[idx])
+    assert got.shape == want.shape == (len(rows), nk)
+    assert max_abs(got, want) <= 2e-2 and mean_rel(got, want) <= 5e-3, (max_abs(got, want), mean_rel(got, want))
 
 
 def test_full_size_gemm_is_linear_in_its_input():
