@@ -100,6 +100,20 @@ void svodb_config_clear(void);
  * out since the last call. */
 int svodb_device_status(void* stream);
 
+/* Self-tests of the failure paths; none of them hangs or faults the device.
+ * `svodb_selftest_wait_timeout`: launches a one-warp kernel whose bounded wait
+ * (on a barrier nothing arrives on) gives up after `polls` tries (1..2^20) and
+ * returns normally; `svodb_device_status` then reports SVODB_ERR_TIMEOUT once,
+ * as it would for a production kernel (device/src/cuda/sys.rs has no
+ * counterpart: the reference has no device-side waits).
+ * `svodb_selftest_latch_error`: feeds a `cudaError_t` value through the
+ * classification a failed launch gets; a sticky code (device/src/cuda/sys.rs:78-96)
+ * latches the library into SVODB_ERR_POISONED for every later call until
+ * `svodb_selftest_clear_latch`. */
+int svodb_selftest_wait_timeout(uint32_t polls, void* stream);
+int svodb_selftest_latch_error(int32_t code);
+void svodb_selftest_clear_latch(void);
+
 /* ---- op layer: `svod_tk::ops` --------------------------------------------- */
 
 struct svodb_qkv_opts;

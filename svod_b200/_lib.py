@@ -126,6 +126,9 @@ SYMBOLS = [
     ("svodb_config_get", C.c_int32, [C.c_char_p]),
     ("svodb_config_clear", None, []),
     ("svodb_device_status", C.c_int, [C.c_void_p]),
+    ("svodb_selftest_wait_timeout", C.c_int, [C.c_uint32, C.c_void_p]),
+    ("svodb_selftest_latch_error", C.c_int, [C.c_int32]),
+    ("svodb_selftest_clear_latch", None, []),
     ("svodb_qwen3_create", C.c_int, [C.POINTER(Qwen3Config), C.POINTER(Qwen3Weights), C.POINTER(C.c_void_p)]),
     ("svodb_qwen3_free", None, [C.c_void_p]),
     ("svodb_qwen3_plan", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),

@@ -15,6 +15,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "common.cuh"
 #include "kernels.h"
 #include "svodb.h"
 
@@ -270,10 +271,27 @@ int svodb_device_status(void* stream) {
   if (host != 0) {
     cudaMemsetAsync(w, 0, sizeof host, (cudaStream_t)stream);
     cudaStreamSynchronize((cudaStream_t)stream);
+    if (host == kStatusBadIndex)
+      return fail(SVODB_ERR_SHAPE, "a device-side index was out of range (a cache row map entry)");
     return fail(SVODB_ERR_TIMEOUT, "a bounded device wait ran out (code %u)", host);
   }
   return SVODB_OK;
 }
+
+// The error latch, exercised without a device fault: `code` (a cudaError_t value)
+// goes through the same classification as the result of a failed launch; a
+// sticky code poisons the library exactly as a real one would.
+int svodb_selftest_latch_error(int32_t code) {
+  GUARD("selftest_latch_error");
+  const cudaError_t e = (cudaError_t)code;
+  if (e == cudaSuccess) return SVODB_OK;
+  if (sticky(e)) g_poisoned = true;
+  return fail(SVODB_ERR_LAUNCH, "selftest_latch_error: %s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+// Clears the latch a self-test set. A latch set by a real sticky error must not
+// be cleared: that context is gone and the process has to restart.
+void svodb_selftest_clear_latch(void) { g_poisoned = false; }
 
 // ---------------------------------------------------------------------------
 // linear

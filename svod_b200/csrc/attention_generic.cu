@@ -67,19 +67,27 @@ __global__ void __launch_bounds__(256) attention_generic_kernel(const AttnArgs a
   const T* q = (const T*)a.q + b * a.q_sb + h * a.q_sh;
   // `ops::Cache`: lane b reads cache row row_map[b]; keys tk .. tk+n_app-1 are
   // the appended rows, hidden only past app_lens[b].
-  const int64_t kv_row = a.row_map != nullptr ? (int64_t)a.row_map[b] : b;
+  int64_t kv_row = a.row_map != nullptr ? (int64_t)a.row_map[b] : b;
+  // A map entry outside the cache: nothing is read through it; the lane sees no
+  // key at all (zeros) and the status word reports it.
+  const bool bad_row = kv_row < 0 || kv_row >= a.kv_rows;
+  if (bad_row) {
+    kv_row = 0;
+    if (tid == 0 && a.status != nullptr) atomicExch(a.status, (uint32_t)kStatusBadIndex);
+  }
   const T* k = (const T*)a.k + kv_row * a.k_sb + hk * a.k_sh;
   const T* v = (const T*)a.v + kv_row * a.v_sb + hk * a.v_sh;
   const int64_t keys = a.tk + a.n_app;
   const T* k_app = a.n_app > 0 ? (const T*)a.k_app + (b * a.n_app * a.kv_heads + hk) * (int64_t)a.d : nullptr;
   const T* v_app = a.n_app > 0 ? (const T*)a.v_app + (b * a.n_app * a.kv_heads + hk) * (int64_t)a.d : nullptr;
-  const int64_t app_seen = a.app_lens != nullptr ? (int64_t)a.app_lens[b] : a.n_app;
+  const int64_t app_seen = bad_row ? 0 : (a.app_lens != nullptr ? (int64_t)a.app_lens[b] : a.n_app);
   const float sc = a.scale * kLog2e;
   int64_t len = a.tk;
   if (a.key_lens != nullptr) {
     int64_t kl = a.key_lens[b];
     len = kl < 0 ? 0 : (kl < len ? kl : len);
   }
+  if (bad_row) len = 0;
 
   for (int e = tid; e < BQ * D; e += 256) {
     const int r = e / D, c = e % D;

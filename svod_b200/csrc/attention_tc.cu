@@ -58,18 +58,6 @@ namespace {
 
 using namespace fa_parts;
 
-#ifdef SVODB_TRACE
-// Timeline probe (debug builds only): clock() stamps of CTA (0,0,0).
-__device__ unsigned int g_trace[9 * 64 * 8];
-#define TRACE(role, iter, ev)                                                    \
-  do {                                                                           \
-    if (trace_on && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = (unsigned int)clock(); \
-  } while (0)
-#else
-#define TRACE(role, iter, ev) \
-  do {                        \
-  } while (0)
-#endif
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsFa, 1)
@@ -100,10 +88,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef SVODB_TRACE
-  const bool trace_on = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
-                        (warp == 1 || warp == 3 || warp >= 4);
-#endif
   // Heavier (later, under a causal mask) query tiles are scheduled first.
   const int qt = p.n_qt - 1 - (int)blockIdx.x;
   const int h = blockIdx.y;
@@ -274,7 +258,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           const int vs_slot = have_v ? (jp - u_lo) % S : 0;
           const bool do_pv = have_v && jp >= r.lo && jp < r.hi;
           const bool do_qk = have_k && jq >= r.lo && jq < r.hi;
-          TRACE(0, t - u_lo + 1, 3 * i);
           // Every slot is waited for and released by both issuers, used or not:
           // an issuer can then never arrive twice on one phase of a ring barrier.
           if ((have_k && !mbar_wait(&k_full[ks_slot], (uint32_t)(((jq - u_lo) / S) & 1), p.status)) ||
@@ -289,7 +272,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
               break;
             }
             tc_fence_after();
-            TRACE(0, t - u_lo + 1, 1 + 3 * i);
             const uint32_t d_tmem = tmem_base + 256 + i * D;
             const uint32_t a_tmem = tmem_base + (uint32_t)((i * 2 + (n & 1)) * kBKV);
             const uint64_t vb = v_desc0 + (uint64_t)((vs_slot * KB) >> 4);
@@ -325,7 +307,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
             }
             // In-order completion: S(t+1) complete implies P.V(t-1) complete.
             if (leader) tc_commit(&s_full[i * 2 + (n & 1)]);
-            TRACE(0, t - u_lo + 1, 2 + 3 * i);
           }
           if (leader && have_v) tc_commit(&v_empty[vs_slot]);
           if (leader && have_k) tc_commit(&k_empty[ks_slot]);
@@ -417,7 +398,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_ld32(s_tmem, sr[0]);
         tmem_ld32(s_tmem + 32, sr[1]);
       }
-      TRACE(warp - 3, n, 0);
       const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
       bool need_mask = j1 >= ctx.len || ctx.general_mask || p.has_chunk;
       if (p.causal && j1 > i_first) need_mask = true;
@@ -426,7 +406,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
 
       tmem_ld_wait_for(sr[0]);
       tmem_ld_wait_for(sr[1]);
-      TRACE(warp - 3, n, 1);
       if (need_mask) {
         // Hidden scores become -inf: they drop out of the maximum and their
         // probability is 2^(-inf) = 0 (the scale is positive on this path).
@@ -492,7 +471,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_st_wait();
       }
       m_run = m_new;
-      TRACE(warp - 3, n, 2);
       float m_use = m_run == -INFINITY ? 0.f : m_run;
       if (n < n_paired && (i == 1 || n > 0)) {
         // tile 1 follows tile 0's block n; tile 0 follows tile 1's block n-1
@@ -536,7 +514,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         named_barrier_arrive(other_turn, 64);
       turns_done = n + 1;
       l_run += (la.x + la.y) + (lb.x + lb.y);
-      TRACE(warp - 3, n, 3);
       requested = false;
       if (n + 1 < nblk &&
           mbar_test_wait(&s_full[i * 2 + (buf ^ 1)], (uint32_t)(((n + 1) >> 1) & 1))) {
@@ -546,14 +523,9 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tmem_ld32(next_tmem + 32, sr[1]);
         requested = true;
       }
-      TRACE(warp - 3, n, 5);
-#ifdef SVODB_TRACE
-      if (trace_on && n < 64) g_trace[((warp - 3) * 64 + n) * 8 + 6] = requested ? 1u : 0u;
-#endif
       // Every lane's P stores have completed (wait::st is warp-wide); one lane
       // per warp then publishes the tile to the MMA issuer.
       tmem_st_wait();
-      TRACE(warp - 3, n, 7);
       // The tail barrier sees two commits (P.V of blocks N-2 and N-1); a parity
       // wait tells only adjacent phases apart, so the first is observed before
       // the last P — which lets the second happen — is published.
@@ -564,7 +536,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
-      TRACE(warp - 3, n, 4);
     }
     if (!ok) {
       for (int m = turns_done; m < n_paired; ++m) {
@@ -614,15 +585,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   }
 }
 
-#ifdef SVODB_TRACE
-}  // namespace
-}  // namespace svodb
-extern "C" int svodb_debug_read_trace(unsigned int* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, svodb::g_trace, sizeof(unsigned int) * n);
-}
-namespace svodb {
-namespace {
-#endif
 
 bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

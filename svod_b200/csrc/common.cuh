@@ -18,6 +18,7 @@ namespace svodb {
 enum : uint32_t {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,
+  kStatusBadIndex = 2,  // a device-side index (a cache row map entry) was out of range
 };
 
 // ---- dtype traits ----------------------------------------------------------
@@ -184,13 +185,16 @@ constexpr uint32_t kWaitLimit = 4u << 20;
 
 // Waits for `parity` on `bar`. On timeout sets *status and returns false; the
 // caller must then leave its loop without issuing further dependent work.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *reinterpret_cast<volatile uint32_t*>(status) != kStatusOk) return false;
   }
   atomicExch(status, (uint32_t)kStatusWaitTimeout);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status) {
+  return mbar_wait_for(bar, parity, status, kWaitLimit);
 }
 
 // ---- TMA (non-multicast only) ----------------------------------------------
@@ -464,6 +468,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- 128-bit global access ---------------------------------------------------
+// The vector kernels read and write 16 bytes per access: every base pointer they
+// take must sit on a 16-byte boundary (null = operand absent).
+__host__ __device__ __forceinline__ bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
 __device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void stg128(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 

@@ -108,18 +108,6 @@ __device__ __forceinline__ void store32(const Params& p, int64_t row, bool row_o
   }
 }
 
-#ifdef SVODB_TRACE
-// Timeline probe (debug builds only): clock() stamps of CTA 0's MMA warp.
-__device__ unsigned int g_gemm_trace[8 * 64 * 4];
-#define GTRACE(kb, ev)                                                                            \
-  do {                                                                                            \
-    if (blockIdx.x == 0 && lane == 0 && gtile < 8 && (kb) < 64) g_gemm_trace[(gtile * 64 + (kb)) * 4 + (ev)] = (unsigned int)clock(); \
-  } while (0)
-#else
-#define GTRACE(kb, ev) \
-  do {                 \
-  } while (0)
-#endif
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -145,9 +133,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.k + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
-#ifdef SVODB_TRACE
-  int gtile = 0;
-#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -248,20 +233,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          GTRACE(kb, 0);
           if (!mbar_wait(&full[s], ph, p.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          GTRACE(kb, 1);
           const uint64_t a_desc = desc0 + (uint64_t)((s * C::kStageBytes) >> 4);
           const uint64_t b_desc = a_desc + (uint64_t)((BM * BK * 2) >> 4);
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4)  // 16 columns = 32 bytes inside the 128-byte swizzle row
             if (leader) umma_ss(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
           if (leader) tc_commit(&empty[s]);
-          GTRACE(kb, 2);
           if (++s == S) {
             s = 0;
             ph ^= 1;
@@ -273,9 +255,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           as = 0;
           aph ^= 1;
         }
-#ifdef SVODB_TRACE
-        gtile++;
-#endif
       }
     }
   } else {
@@ -713,15 +692,6 @@ int run(const GemmArgs& a, const Params& p0, int sms, cudaStream_t s, char* cfg,
   return 0;
 }
 
-#ifdef SVODB_TRACE
-}  // namespace
-}  // namespace svodb
-extern "C" int svodb_debug_read_gemm_trace(unsigned int* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, svodb::g_gemm_trace, sizeof(unsigned int) * n);
-}
-namespace svodb {
-namespace {
-#endif
 
 int sm_count() {
   static int sms = 0;
@@ -733,8 +703,6 @@ int sm_count() {
   }
   return sms;
 }
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
 

@@ -20,7 +20,7 @@ template <typename T, typename I>
 __global__ void __launch_bounds__(256)
     embed_kernel(const I* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ pos_table,
                  const T* __restrict__ type_row, int64_t pad_id, T* __restrict__ out, int64_t t_len, int d,
-                 int64_t vocab, int64_t max_pos) {
+                 int64_t vocab, int64_t max_pos, int vec16) {
   __shared__ int red[8];
   __shared__ int64_t tok_id[kTok];
   __shared__ int64_t tok_pos[kTok];
@@ -59,6 +59,16 @@ __global__ void __launch_bounds__(256)
     p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
     const T* psrc = pos_table != nullptr ? pos_table + p * d : nullptr;
     T* dst = out + (b * t_len + t) * d;
+    if (!vec16) {
+      // an operand off the 16-byte boundary: element by element, same roundings
+      for (int c = tid; c < d; c += 256) {
+        float v = Elem<T>::to_f(src[c]);
+        if (psrc != nullptr) v = Elem<T>::to_f(Elem<T>::from_f(v + Elem<T>::to_f(psrc[c])));
+        if (type_row != nullptr) v = Elem<T>::to_f(Elem<T>::from_f(v + Elem<T>::to_f(type_row[c])));
+        dst[c] = Elem<T>::from_f(v);
+      }
+      continue;
+    }
     for (int c = tid; c < vec; c += 256) {
       uint4 u = ldg128(src + c * 8);
       if (psrc != nullptr || type_row != nullptr) {
@@ -167,9 +177,11 @@ __global__ void rope_table_kernel(float theta, const int32_t* __restrict__ posit
 void launch_embed(const EmbedArgs& a, cudaStream_t s) {
   if (a.batch * a.t == 0) return;
   dim3 grid((unsigned)((a.t + kTok - 1) / kTok), (unsigned)a.batch);
+  const int vec16 = aligned16(a.table) && aligned16(a.pos_table) && aligned16(a.type_row) && aligned16(a.out) ? 1 : 0;
 #define SVODB_EMBED(T, I)                                                                                         \
   embed_kernel<T, I><<<grid, 256, 0, s>>>((const I*)a.ids, (const T*)a.table, (const T*)a.pos_table,              \
-                                          (const T*)a.type_row, a.pad_id, (T*)a.out, a.t, a.d, a.vocab, a.max_pos)
+                                          (const T*)a.type_row, a.pad_id, (T*)a.out, a.t, a.d, a.vocab, a.max_pos, \
+                                          vec16)
   if (a.dtype == SVODB_BF16) {
     if (a.ids_i64) SVODB_EMBED(__nv_bfloat16, int64_t);
     else SVODB_EMBED(__nv_bfloat16, int32_t);

@@ -186,8 +186,12 @@ int launch_heads(const HeadsArgs& a, cudaStream_t s) {
   if (a.batch * a.t == 0) return 1;
   // Vector kernel: 16-bit, D a power of two in 16..256 (tk/src/ops/heads.rs; the
   // reference's kernel has the same bound).
-  if (a.dtype == SVODB_BF16 && dispatch<__nv_bfloat16>(a, s)) return 1;
-  if (a.dtype == SVODB_F16 && dispatch<__half>(a, s)) return 1;
+  // Its 128-bit accesses need every operand on a 16-byte boundary; a view that
+  // starts at an odd element takes the generic kernel.
+  const bool aligned = aligned16(a.qkv) && aligned16(a.q_w) && aligned16(a.k_w) && aligned16(a.cos) &&
+                       aligned16(a.sin) && aligned16(a.q) && aligned16(a.k) && aligned16(a.v);
+  if (aligned && a.dtype == SVODB_BF16 && dispatch<__nv_bfloat16>(a, s)) return 1;
+  if (aligned && a.dtype == SVODB_F16 && dispatch<__half>(a, s)) return 1;
   if (a.dtype == SVODB_BF16) run_generic<__nv_bfloat16>(a, s);
   else if (a.dtype == SVODB_F16) run_generic<__half>(a, s);
   else run_generic<float>(a, s);

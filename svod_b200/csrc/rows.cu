@@ -198,7 +198,10 @@ int launch_norm(const NormArgs& a, cudaStream_t s) {
   if (a.rows == 0) return 1;
   // The warp-per-row kernel covers what the reference's kernel covers: 16-bit
   // rows of 256..2048 elements in multiples of 256 (tk/src/ops/config/norm.rs:19-24).
-  const bool fits = a.d % 256 == 0 && a.d >= 256 && a.d <= 2048;
+  // Its 128-bit accesses need every operand on a 16-byte boundary (a view that
+  // starts at an odd element does not); such rows take the generic kernel.
+  const bool fits = a.d % 256 == 0 && a.d >= 256 && a.d <= 2048 && aligned16(a.x) && aligned16(a.residual) &&
+                    aligned16(a.w) && aligned16(a.b) && aligned16(a.out) && aligned16(a.sum);
   if (fits && a.dtype == SVODB_BF16 && run_rows_dispatch<__nv_bfloat16>(a, s)) return 1;
   if (fits && a.dtype == SVODB_F16 && run_rows_dispatch<__half>(a, s)) return 1;
   if (a.dtype == SVODB_BF16) run_generic<__nv_bfloat16>(a, s);

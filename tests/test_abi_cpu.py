@@ -46,3 +46,20 @@ def test_struct_layouts_match_the_header():
 def test_no_product_module_imports_the_oracle():
     for path in (ROOT / "svod_b200").rglob("*.py"):
         assert "oracle" not in path.read_text(), path
+
+
+def test_the_error_latch_without_a_device():
+    """A sticky CUDA error code (faked: no device is touched) makes every later
+    call fail fast with SVODB_ERR_POISONED until the self-test clears it."""
+    lib = _lib.load()
+    assert lib.svodb_selftest_latch_error(0) == _lib.OK
+    assert lib.svodb_selftest_latch_error(1) == _lib.ERR_LAUNCH            # cudaErrorInvalidValue: not sticky
+    assert lib.svodb_selftest_latch_error(0) == _lib.OK
+    assert lib.svodb_selftest_latch_error(700) == _lib.ERR_LAUNCH          # cudaErrorIllegalAddress: sticky
+    try:
+        assert lib.svodb_selftest_latch_error(0) == _lib.ERR_POISONED
+        assert lib.svodb_graph_begin(None) == _lib.ERR_POISONED
+        assert b"poisoned" in lib.svodb_last_error()
+    finally:
+        lib.svodb_selftest_clear_latch()
+    assert lib.svodb_selftest_latch_error(0) == _lib.OK

@@ -129,3 +129,50 @@ def test_embed_and_pool_are_exact():
     buf = torch.full((B, 2 * D), 7.0, device="cuda")
     out = ops.pool(H, torch.from_numpy(mask).cuda(), ops.POOL_MEAN, True, buf[:, :D])
     assert np.all(host(out)[2] == 0) and np.all(host(buf[:, D:]) == 7.0)
+
+
+def off_boundary(x, dt, shift=3):
+    """The same values as a contiguous device view that starts `shift` elements
+    (6 bytes for a 16-bit type) past an allocation boundary."""
+    flat = dev(np.asarray(x).reshape(-1), dt)
+    buf = torch.zeros(flat.numel() + 16, dtype=flat.dtype, device="cuda")
+    buf[shift:shift + flat.numel()] = flat
+    view = buf[shift:shift + flat.numel()].view(np.asarray(x).shape)
+    assert view.data_ptr() % 16 != 0 and view.is_contiguous()
+    return view
+
+
+def test_views_off_the_16_byte_boundary_take_the_generic_kernels():
+    """The vector kernels move 16 bytes per access; a dense view that starts at
+    an odd element is valid input and must run (on the element-wise kernels),
+    not fault."""
+    dt = O.BF16
+    rng = np.random.default_rng(11)
+    # norms: x, then the weight, off the boundary
+    d = 512
+    x = O.round_to(dt, rng.standard_normal((5, d)) * 2 + 1.5)
+    w = O.round_to(dt, 1 + 0.5 * rng.standard_normal(d))
+    r = O.round_to(dt, rng.standard_normal((5, d)))
+    want, wsum = O.norm_rows("rms", x, w, None, r, 1e-6, dt)
+    for X, W in ((off_boundary(x, dt), dev(w, dt)), (dev(x, dt), off_boundary(w, dt))):
+        s, got = ops.add_rms_norm(X, dev(r, dt), W, 1e-6)
+        assert "graph" in ops.chosen()
+        assert rel_close(host(got), want, 1e-2) and np.array_equal(host(s), wsum)
+    # heads: the packed projection off the boundary
+    B, T, H, Hkv, hd = 1, 9, 4, 2, 64
+    qkv, qw, kw, cos, sin = heads_recipe(B, T, H, Hkv, hd, True, True, False, 7)
+    want = O.heads(qkv, H, Hkv, hd, qw, kw, 1e-6, cos, sin, dt)
+    tabs = (dev(cos, dt).view(-1, T, 1, hd // 2), dev(sin, dt).view(-1, T, 1, hd // 2))
+    got = ops.heads(off_boundary(qkv, dt), ops.Qkv(H, Hkv, hd, dev(qw, dt), dev(kw, dt), 1e-6, tabs))
+    assert "graph" in ops.chosen()
+    assert max_abs(host(got[0]), want[0]) < 2e-2 and max_abs(host(got[1]), want[1]) < 2e-2
+    assert np.array_equal(host(got[2]), want[2])
+    # embedding: the table off the boundary, same bits as the aligned lookup
+    V, D = 50, 64
+    table = O.round_to(dt, rng.standard_normal((V, D)))
+    pos = O.round_to(dt, rng.standard_normal((12, D)))
+    ids = rng.integers(2, V, (2, 7))
+    pid = O.xlmr_position_ids(ids, 1)
+    got = ops.embed(torch.from_numpy(ids).cuda(), off_boundary(table, dt), off_boundary(pos, dt, 5), None, 1)
+    assert np.array_equal(host(got), O.round_to(dt, table[ids] + pos[pid]))
+    ops.device_status()
