@@ -14,12 +14,16 @@ pooled `[32, 1024]` f32 rows, which each rank writes straight into its slot of
 the gather buffer.
 
 Prints ONE JSON line on rank 0. `value` is device-timed with inputs resident in
-HBM (CUDA-graph replay + all-gather, CUDA events on the launching stream, max
-over ranks); `e2e` adds the pinned-host -> device copy of every step's inputs
-and the device -> host read of the pooled result inside the timed region.
-`roofline` is measured live for the dominant kernel; `cpu_baseline` times the
-compiled C + OpenMP restatement on a bounded sample of the same workload on this
-box's host cores.
+HBM (one CUDA-graph replay per step, the all-gather captured inside the graph,
+CUDA events on the launching stream, max over ranks); `e2e` adds the pinned-host
+-> device copy of every step's inputs and the device -> host read of the pooled
+result inside the timed region. `roofline` is measured live for the dominant
+kernel (timed alone against the burst peak, and inside a step against the
+sustained one); `cpu_baseline` times the compiled C + OpenMP restatement on a
+bounded sample of the same workload on this box's host cores. `strong` deals ONE
+batch of 32 ragged rows over the ranks (`shard_rows`) and times that; at N = 1
+`workloads` adds the two other encoder configurations (XLM-RoBERTa-large
+B64 x 512 fp16, ModernBERT-base B16 x 8192 bf16).
 """
 from __future__ import annotations
 
@@ -124,34 +128,75 @@ def visible_index(local_rank: int) -> int:
 
 
 # --------------------------------------------------------------------------- CPU legs
-def oracle_sample(kind: str, seq: int, layers: int, seed: int = 7):
+CPU_SAMPLES = {
+    # kind: (rows, seq, layers timed, layers of the full stack)
+    "qwen3": (1, 4096, 4, 28),
+    "xlmr": (4, 512, 4, 24),
+    "modernbert": (1, 8192, 3, 22),
+}
+
+
+def oracle_sample(kind: str, seed: int = 7):
     """A bounded sample of the workload for the compiled CPU restatement
-    (`oracle/svod_oracle.c`: f32, OpenMP over all host threads): one sequence of
-    `seq` tokens through `layers` decoder layers of the same architecture.
-    Returns a closure that runs it and the number of tokens it processes."""
+    (`oracle/svod_oracle.c`: f32, OpenMP over all host threads): a few rows of the
+    workload's sequence length through a few layers of the same architecture.
+    Returns a closure that runs it (and returns the seconds the FULL depth would
+    take, by layer count) and the number of tokens it processes."""
     import numpy as np
+    import torch
     from oracle import c_oracle as C
-    from oracle import svod_oracle as O
     try:
         C.build()
     except Exception:
         pass  # a library built earlier still loads; `load()` reports a missing one
-    rng = np.random.default_rng(seed)
-    dt = O.BF16
-    w = lambda *s: O.round_to(dt, rng.standard_normal(s) * 0.02).astype(np.float32)
-    if kind != "qwen3":
-        raise SystemExit("the CPU leg samples the default (qwen3) workload")
-    D, H, Hkv, hd, F = 1024, 16, 8, 128, 3072
-    ones = lambda n: np.ones(n, dtype=np.float32)
-    lp = dict(in_w=ones(D), qkv_w=w((H + 2 * Hkv) * hd, D), qn_w=ones(hd), kn_w=ones(hd), o_w=w(D, H * hd),
-              post_w=ones(D), gu_w=w(2 * F, D), down_w=w(D, F))
-    hidden = w(1, seq, D)
     C.load()
+    C.use_all_cores()  # launchers export OMP_NUM_THREADS=1; the baseline uses every core it may run on
+    rows, seq, layers, full = CPU_SAMPLES[kind]
+    g = torch.Generator().manual_seed(seed)
+    dt16 = torch.float16 if kind == "xlmr" else torch.bfloat16
+    w = lambda *sh: (torch.randn(*sh, generator=g) * 0.02).to(dt16).float().numpy()
+    ones = lambda n: np.ones(n, dtype=np.float32)
+    zeros = lambda n: np.zeros(n, dtype=np.float32)
+    if kind == "qwen3":
+        D, H, Hkv, hd, F = 1024, 16, 8, 128, 3072
+        lp = dict(in_w=ones(D), qkv_w=w((H + 2 * Hkv) * hd, D), qn_w=ones(hd), kn_w=ones(hd), o_w=w(D, H * hd),
+                  post_w=ones(D), gu_w=w(2 * F, D), down_w=w(D, F))
+        hidden = w(rows, seq, D)
 
-    def run():
-        return C.qwen3_layers(hidden, [lp] * layers, heads_n=H, kv_heads=Hkv, head_dim=hd, dtype=C.BF16)
+        def run():
+            t0 = time.perf_counter()
+            C.qwen3_layers(hidden, [lp] * layers, heads_n=H, kv_heads=Hkv, head_dim=hd, dtype=C.BF16)
+            return (time.perf_counter() - t0) * full / layers
+    elif kind == "xlmr":
+        D, H, F = 1024, 16, 4096
+        lp = dict(q_w=w(D, D), q_b=w(D), k_w=w(D, D), k_b=w(D), v_w=w(D, D), v_b=w(D), o_w=w(D, D), o_b=w(D),
+                  ln1_w=ones(D), ln1_b=zeros(D), fi_w=w(F, D), fi_b=w(F), fo_w=w(D, F), fo_b=w(D), ln2_w=ones(D),
+                  ln2_b=zeros(D))
+        hidden = w(rows, seq, D)
+        lens = np.array([512, 64, 288, 400][:rows])
+        mask = np.arange(seq)[None, :] < lens[:, None]
 
-    return run, seq
+        def run():
+            t0 = time.perf_counter()
+            C.xlmr_layers(hidden, [lp] * layers, mask, heads_n=H, dtype=C.F16)
+            return (time.perf_counter() - t0) * full / layers
+    else:
+        D, H, F = 768, 12, 1152
+        lp = dict(attn_ln_w=ones(D), qkv_w=w(3 * D, D), o_w=w(D, D), mlp_ln_w=ones(D), wi_w=w(2 * F, D), wo_w=w(D, F))
+        hidden = w(rows, seq, D)
+        mask = np.ones((rows, seq), dtype=bool)
+
+        def run():
+            # one global layer and two windowed ones timed apart: the stack has 8 and 14 of them
+            t0 = time.perf_counter()
+            C.modernbert_layers(hidden, [lp], mask, heads_n=H, first_layer=0, dtype=C.BF16)
+            t1 = time.perf_counter()
+            C.modernbert_layers(hidden, [lp] * 2, mask, heads_n=H, first_layer=1, dtype=C.BF16)
+            t2 = time.perf_counter()
+            n_global = (full + 2) // 3
+            return (t1 - t0) * n_global + (t2 - t1) / 2 * (full - n_global)
+
+    return run, rows * seq
 
 
 def cpu_threads() -> int:
@@ -159,19 +204,16 @@ def cpu_threads() -> int:
     return C.threads()
 
 
-def time_cpu(kind: str, steps: int, warmup: int, seq: int = 4096, layers: int = 4, full_layers: int = 28):
-    """Times the compiled CPU restatement on `layers` of the `full_layers` layers
-    of one full-length sequence and scales to the full depth (every layer does
-    identical work; the embedding lookup and the pooling are negligible)."""
-    run, tokens = oracle_sample(kind, seq, layers)
+def time_cpu(kind: str, steps: int, warmup: int):
+    """Times the compiled CPU restatement on a few layers of a few rows and scales
+    to the full depth (every layer of a kind does identical work; the embedding
+    lookup and the pooling are negligible)."""
+    run, tokens = oracle_sample(kind)
+    rows, seq, layers, full_layers = CPU_SAMPLES[kind]
     for _ in range(warmup):
         run()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        run()
-    dt = (time.perf_counter() - t0) / steps
-    full = dt * full_layers / layers
-    sample = (f"C + OpenMP f32 restatement, 1 sequence x {seq} tokens, {layers} of {full_layers} layers timed "
+    full = sum(run() for _ in range(steps)) / steps
+    sample = (f"C + OpenMP f32 restatement, {rows} row(s) x {seq} tokens, {layers} of {full_layers} layers timed "
               f"and scaled to {full_layers}, {steps} step(s)")
     return tokens / full, full * 1e3, sample
 
@@ -183,6 +225,10 @@ def time_torch_cpu(seq: int = 4096, layers: int = 4, full_layers: int = 28, step
     with all the threads torch will use."""
     import torch
     import torch.nn.functional as F
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))  # launchers export OMP_NUM_THREADS=1
+    except (AttributeError, RuntimeError):
+        pass
     g = torch.Generator().manual_seed(7)
     D, H, Hkv, hd, Fn = 1024, 16, 8, 128, 3072
     r = lambda *sh: torch.randn(*sh, generator=g) * 0.02
@@ -233,7 +279,7 @@ def reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": "f16" if kind == "xlmr" else "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": batch, "seq_len": seq, "parallelism": "cpu"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -298,9 +344,10 @@ def kernel_rooflines(kind: str, batch: int, seq: int, peaks):
         H, Hkv, D, causal = 16, 16, 64, False
     else:
         H, Hkv, D, causal = 12, 12, 64, False
-    q = torch.randn(batch, seq, H, D, generator=g, device="cuda").to(torch.bfloat16)
-    k = torch.randn(batch, seq, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
-    v = torch.randn(batch, seq, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+    dt16 = torch.float16 if kind == "xlmr" else torch.bfloat16
+    q = torch.randn(batch, seq, H, D, generator=g, device="cuda").to(dt16)
+    k = torch.randn(batch, seq, Hkv, D, generator=g, device="cuda").to(dt16)
+    v = torch.randn(batch, seq, Hkv, D, generator=g, device="cuda").to(dt16)
     a = ops.Attn(causal=causal)
     ms = time_graphed(lambda: ops.attention(q, k, v, a), 20)
     fl = 4 * batch * H * seq * seq * D / (2 if causal else 1)
@@ -314,8 +361,8 @@ def kernel_rooflines(kind: str, batch: int, seq: int, peaks):
         N, K, opts, gated = 4096, 1024, ops.Linear(act=ops.Act.GELU), False
     else:
         N, K, opts, gated = 1152, 768, ops.Linear(act=ops.Act.GELU, gated=True), True
-    x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
-    w = (torch.randn((2 if gated else 1) * N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(dt16)
+    w = (torch.randn((2 if gated else 1) * N, K, generator=g, device="cuda") * 0.02).to(dt16)
     ms = time_graphed(lambda: ops.linear(x, w, opts), 20)
     fl = 2 * M * N * K * (2 if gated else 1)
     out["gemm"] = {"ms": ms, "tflops": fl / ms / 1e9, "flops_per_launch": fl,
@@ -325,6 +372,141 @@ def kernel_rooflines(kind: str, batch: int, seq: int, peaks):
         v_["frac_of_burst"] = v_["tflops"] / peaks["burst"]
         v_["frac_of_nominal_2250"] = v_["tflops"] / 2250.0
     return out
+
+
+def synthetic_batch(kind: str, rows: int, seq: int, vocab: int, seed: int, ragged: bool):
+    """Pinned host inputs of one batch: uniform ids (the pad id avoided) and the
+    padding mask `[rows, seq]` (XLM-R lengths in [seq/8, seq], ModernBERT in
+    [seq/4, seq], as the configurations state) or the lengths `[rows]` (Qwen3:
+    full rows, or ragged ones when asked). Returns ids, aux, lengths."""
+    import torch
+    gen = torch.Generator().manual_seed(seed)
+    ids = torch.randint(2, vocab, (rows, seq), generator=gen, dtype=torch.int32)
+    if kind == "qwen3":
+        lens = torch.randint(seq // 4, seq + 1, (rows,), generator=gen) if ragged else torch.full((rows,), seq)
+        return ids, lens.to(torch.int32), lens
+    lens = torch.randint(seq // 8 if kind == "xlmr" else seq // 4, seq + 1, (rows,), generator=gen)
+    return ids, torch.arange(seq)[None, :] < lens[:, None], lens
+
+
+class StackRun:
+    """One plan of one stack on this rank: rows x seq, pooled rows written into this
+    rank's slot of `gathered`, the all-gather captured inside the plan's graph."""
+
+    def __init__(self, model, aux_kind, rows, seq, world, rank, device):
+        import torch
+        from svod_b200 import encoders as E
+        from svod_b200 import ops
+        self.world, self.rows, self.seq = world, rows, seq
+        D = model.cfg.hidden_size
+        self.gathered = torch.zeros(world * rows, D, dtype=torch.float32, device=device)
+        self.mine = self.gathered[rank * rows:(rank + 1) * rows]
+        self.out_host = torch.empty(rows, D, dtype=torch.float32).pin_memory()
+        epilogue = (lambda: E.gather_pooled(self.mine, self.gathered)) if world > 1 else None
+        before = ops.launches
+        self.plan = E.Plan(model, rows, seq, aux_kind, out=self.mine, device=device, epilogue=epilogue)
+        self._capture = lambda: self.plan.capture()
+        self._before = before
+
+    def load(self, ids_host, aux_host):
+        import torch
+        from svod_b200 import ops
+        self.ids_host, self.aux_host = ids_host.pin_memory(), aux_host.pin_memory()
+        self.plan.ids.copy_(self.ids_host)
+        self.plan.aux.copy_(self.aux_host)
+        torch.cuda.synchronize()
+        self._capture()
+        self.launches_per_step = (ops.launches - self._before) // 2   # capture() runs the stack twice (eager + capture)
+        return self
+
+    def step_resident(self):
+        self.plan.replay()
+
+    def step_e2e(self):
+        import torch
+        self.plan.run(self.ids_host, self.aux_host, None)
+        with torch.cuda.stream(self.plan.stream):
+            self.out_host.copy_(self.mine, non_blocking=True)
+
+    def timed(self, fn, steps):
+        import torch
+        import torch.distributed as dist
+        stream = self.plan.stream
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        stream.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=self.gathered.device)
+        if self.world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def h2d_bytes(self):
+        return (self.ids_host.numel() * self.ids_host.element_size()
+                + self.aux_host.numel() * self.aux_host.element_size())
+
+
+def attention_in_step_ms(model, run):
+    """The attention launches of one eager step, each bracketed by a CUDA-event
+    pair on the step's stream, right after the timed steps (so under the same
+    clocks): the mean per launch and the launch count."""
+    import torch
+    from svod_b200 import ops
+    pairs = []
+    real = {"attention": ops.attention, "attention_packed": ops.attention_packed}
+
+    def wrap(fn):
+        def inner(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(torch.cuda.current_stream())
+            out = fn(*a, **kw)
+            e1.record(torch.cuda.current_stream())
+            pairs.append((e0, e1))
+            return out
+        return inner
+
+    plan = run.plan
+    try:
+        ops.attention, ops.attention_packed = wrap(real["attention"]), wrap(real["attention_packed"])
+        with torch.cuda.stream(plan.stream):
+            for it in range(2):
+                pairs.clear()
+                model.forward(plan.ids, plan.aux, plan.out)
+        plan.stream.synchronize()
+    finally:
+        ops.attention, ops.attention_packed = real["attention"], real["attention_packed"]
+    ms = [a.elapsed_time(b) for a, b in pairs]
+    return (sum(ms) / len(ms), len(ms), max(ms)) if ms else (None, 0, None)
+
+
+def measure_stack(kind, model, aux_kind, rows, seq, world, rank, device, args, ids_host, aux_host, sample_clocks):
+    """Warm-up, K timed resident steps, K timed end-to-end steps of one plan."""
+    import torch
+    from svod_b200 import ops
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    run = StackRun(model, aux_kind, rows, seq, world, rank, device).load(ids_host, aux_host)
+    for _ in range(max(3, args.warmup)):
+        run.step_resident()
+    run.plan.check()
+    sampler = ClockSampler(visible_index(local)) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    ms_step = run.timed(run.step_resident, args.steps) / args.steps
+    clocks = sampler.stop() if sampler else None
+    for _ in range(2):
+        run.step_e2e()
+    run.plan.stream.synchronize()
+    e2e_ms = run.timed(run.step_e2e, args.steps) / args.steps
+    run.plan.check()
+    return run, dict(ms_per_step=ms_step, e2e_ms=e2e_ms, clocks=clocks, finite=bool(torch.isfinite(run.mine).all()))
 
 
 def gpu_arm(args):
@@ -344,94 +526,67 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=device)
     kind, batch, seq = WORKLOADS[args.workload]
     peaks = measured_peaks()
+    dtype_name = "f16" if kind == "xlmr" else "bf16"
 
     model, aux_kind = build_model(kind, device, args.reference_ops)
     D = model.cfg.hidden_size
-    gathered = torch.zeros(world * batch, D, dtype=torch.float32, device=device)
-    mine = gathered[rank * batch:(rank + 1) * batch]
-    before = ops.launches
-    plan = E.Plan(model, batch, seq, aux_kind, out=mine, device=device)
-    # synthetic inputs: uniform ids (pad id avoided), full-length rows
-    gen = torch.Generator().manual_seed(1234 + rank)
     vocab = model.cfg.vocab_size
-    ids_host = torch.randint(2, vocab, (batch, seq), generator=gen, dtype=torch.int32).pin_memory()
-    if aux_kind == "mask":
-        lens = torch.randint(seq // 8 if kind == "xlmr" else seq // 4, seq + 1, (batch,), generator=gen)
-        aux_host = (torch.arange(seq)[None, :] < lens[:, None]).pin_memory()
-        real_tokens = int(lens.sum())
-    else:
-        aux_host = torch.full((batch,), seq, dtype=torch.int32).pin_memory()
-        real_tokens = batch * seq
-    out_host = torch.empty(batch, D, dtype=torch.float32).pin_memory()
-    plan.ids.copy_(ids_host)
-    plan.aux.copy_(aux_host)
-    torch.cuda.synchronize()
-    plan.capture()
-    launches_per_step = (ops.launches - before) // 2   # capture() runs the stack twice (eager + capture)
-    stream = plan.stream
 
-    def step_resident():
-        plan.replay()
-        if world > 1:
-            with torch.cuda.stream(stream):
-                E.gather_pooled(mine, gathered)
-
-    def step_e2e():
-        plan.run(ids_host, aux_host, None)
-        with torch.cuda.stream(stream):
-            if world > 1:
-                E.gather_pooled(mine, gathered)
-            out_host.copy_(mine, non_blocking=True)
-
-    def timed(fn, steps):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    for _ in range(max(3, args.warmup)):
-        step_resident()
-    stream.synchronize()
-    ops.device_status()
-    sampler = ClockSampler(visible_index(local))
-    sampler.start()
-    total_ms = timed(step_resident, args.steps)
-    clocks = sampler.stop()
-    ms_step = total_ms / args.steps
+    # ---- weak pass: every rank its own full batch (the headline `value`) ----
+    ids_host, aux_host, lens = synthetic_batch(kind, batch, seq, vocab, 1234 + rank, ragged=False)
+    run, m = measure_stack(kind, model, aux_kind, batch, seq, world, rank, device, args, ids_host, aux_host, True)
+    ms_step, e2e_ms, clocks = m["ms_per_step"], m["e2e_ms"], m["clocks"]
     tokens_step = batch * seq * world
     value = tokens_step / (ms_step * 1e-3)
-
-    for _ in range(2):
-        step_e2e()
-    stream.synchronize()
-    e2e_ms = timed(step_e2e, args.steps) / args.steps
     e2e_value = tokens_step / (e2e_ms * 1e-3)
+    real_tokens = int(lens.sum())
+    launches_per_step = run.launches_per_step
+    h2d, d2h = run.h2d_bytes(), run.out_host.numel() * 4
+    attn_ms, attn_launches, attn_ms_max = attention_in_step_ms(model, run) if rank == 0 else (None, 0, None)
     ops.device_status()
-    finite = bool(torch.isfinite(mine).all())
+    ref_rows = run.mine.detach().cpu().numpy().copy() if rank == 0 else None
+
+    # ---- strong pass: ONE batch of `batch` ragged rows dealt over the ranks ----
+    strong = None
+    if world > 1 and batch % world == 0:
+        g_ids, g_aux, g_lens = synthetic_batch(kind, batch, seq, vocab, 4321, ragged=True)   # same on every rank
+        shards = E.shard_rows([int(x) for x in g_lens], world)
+        my_rows = torch.tensor(shards[rank])
+        per = batch // world
+        del run
+        torch.cuda.empty_cache()
+        # rank 0 also embeds the whole batch by itself (eagerly, no collective): the rows the shards must reproduce
+        full_rows = None
+        if rank == 0:
+            full_rows = model.forward(g_ids.to(device), g_aux.to(device)).clone()
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        srun, sm = measure_stack(kind, model, aux_kind, per, seq, world, rank, device, args, g_ids[my_rows],
+                                 g_aux[my_rows], False)
+        s_ms = sm["ms_per_step"]
+        strong = {"tokens_per_s": batch * seq / (s_ms * 1e-3), "ms_per_step": s_ms, "rows_per_gpu": per,
+                  "global_batch": batch, "e2e_tokens_per_s": batch * seq / (sm["e2e_ms"] * 1e-3),
+                  "n1_ms_per_step": ms_step, "speedup_vs_n1": ms_step / s_ms, "efficiency_vs_n1": ms_step / s_ms / world,
+                  "note": ("one batch of ragged rows dealt longest-first round-robin (shard_rows); n1 = this run's "
+                           "own full-batch step on one GPU (the weak pass); all-gather inside the captured graph")}
+        if rank == 0:
+            undone = E.unshard_rows(srun.gathered, shards)   # back to the batch's own row order
+            strong["matches_one_gpu_rows"] = bool(torch.equal(undone, full_rows))
+            strong["max_abs_diff_vs_one_gpu_rows"] = float((undone - full_rows).abs().max())
+        del srun
+        torch.cuda.empty_cache()
+    else:
+        del run
+        torch.cuda.empty_cache()
 
     # The same step through the library's native runner (C ABI, host buffers in,
     # host pooled rows out): no Python between the copies and the graph launch.
     native = None
     if kind == "qwen3" and rank == 0:
         from svod_b200.native import NativeQwen3
-        ref_rows = mine.detach().cpu().numpy().copy()
-        del plan
-        plan = None
-        torch.cuda.empty_cache()
         runner = NativeQwen3(model, reference_ops=args.reference_ops)
-        ids_np, len_np, out_np = ids_host.numpy(), aux_host.numpy(), out_host.numpy()
+        out_np = torch.empty(batch, D, dtype=torch.float32).pin_memory().numpy()
+        ids_np, len_np = ids_host.pin_memory().numpy(), aux_host.pin_memory().numpy()
         for _ in range(2):
             runner.run(ids_np, len_np, out_np)
         nstream = runner.stream(batch, seq)
@@ -454,23 +609,25 @@ def gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16" if kind != "xlmr" else "f16", "data": "synthetic",
+            "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": batch, "global_batch": batch * world,
                        "seq_len": seq, "parallelism": f"dp{world}",
                        "l2": "activations per step (GBs) exceed the 126 MB L2; no explicit flush",
-                       "real_tokens_per_step": real_tokens * world},
+                       "real_tokens_per_step": real_tokens * world,
+                       "collective": "all-gather of pooled rows, captured inside the step's CUDA graph" if world > 1
+                       else "none at one GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size() + aux_host.numel() * aux_host.element_size(),
-                    "d2h_bytes_per_step": out_host.numel() * 4},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step * args.steps,
             "gpu_launches_per_step": launches_per_step,
             "clocks": clocks,
             "step_tflops": (gemm_fl + attn_fl) / ms_step / 1e9,
-            "output_finite": finite,
+            "output_finite": m["finite"],
         }
         if native is not None:
             line["e2e_native"] = native
-    del plan
+        if strong is not None:
+            line["strong"] = strong
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -478,23 +635,64 @@ def gpu_arm(args):
         ks = kernel_rooflines(kind, batch, seq, peaks)
         top = max(ks, key=lambda n: ks[n]["ms"] * ks[n]["launches_per_step"])
         line["roofline"] = {
-            "kernel": top, "bound": "tensor", "achieved": ks[top]["tflops"], "peak": peaks["sustained"],
-            "unit": "TFLOP/s", "frac": ks[top]["tflops"] / peaks["sustained"],
+            "kernel": top, "bound": "tensor", "achieved": ks[top]["tflops"], "peak": peaks["burst"],
+            "unit": "TFLOP/s", "frac": ks[top]["tflops"] / peaks["burst"],
             "traffic": NCU_DRAM_BYTES_PER_ROW.get((kind, top), 0) * batch or None,
             "traffic_note": "dram read+write bytes of one ncu capture at batch 4, scaled by rows (profiles/)",
-            "peak_source": f"{peaks['source']} bf16 sustained (kernel timed back to back)",
+            "peak_source": f"{peaks['source']} bf16 burst: the kernel is timed alone (20 launches in one graph)",
         }
+        if attn_ms:
+            fl = ks["flash_attention"]["flops_per_launch"]
+            line["roofline"]["in_step"] = {
+                "kernel": "flash_attention", "ms": attn_ms, "ms_max": attn_ms_max, "launches": attn_launches,
+                "achieved": fl / attn_ms / 1e9, "peak": peaks["sustained"], "frac": fl / attn_ms / 1e9 / peaks["sustained"],
+                "peak_source": f"{peaks['source']} bf16 sustained: event pairs around the attention launches of one "
+                               "eager step under the step's clocks"}
+            if top == "flash_attention":
+                line["roofline"]["frac_in_step"] = line["roofline"]["in_step"]["frac"]
         line["kernels"] = ks
         line["attention_fwd_tflops"] = ks["flash_attention"]["tflops"]
+        if world == 1 and not args.no_workloads and kind == "qwen3":
+            del model
+            torch.cuda.empty_cache()
+            line["workloads"] = other_workloads(args, device, peaks)
         if world == 1 and not args.no_cpu:
-            v, ms, sample = time_cpu("qwen3", 2, 1) if kind == "qwen3" else (None, None, None)
-            if v is not None:
-                line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
-                                        "sample": sample, "second_point": time_torch_cpu()}
+            v, ms, sample = time_cpu(kind, 2, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample}
+            if kind == "qwen3":
+                line["cpu_baseline"]["second_point"] = time_torch_cpu()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def other_workloads(args, device, peaks):
+    """The two other encoder configurations on one GPU, a few steps each: padded
+    and real tokens/s (real = the tokens under the padding mask), step TFLOP/s and
+    the per-launch timing of their attention and largest GEMM."""
+    import torch
+    from svod_b200 import ops
+    out = {}
+    for name in ("xlm-roberta-large", "modernbert-base"):
+        kind, batch, seq = WORKLOADS[name]
+        model, aux_kind = build_model(kind, device)
+        ids_host, aux_host, lens = synthetic_batch(kind, batch, seq, model.cfg.vocab_size, 1234, ragged=False)
+        run, m = measure_stack(kind, model, aux_kind, batch, seq, 1, 0, device, args, ids_host, aux_host, True)
+        ms = m["ms_per_step"]
+        gemm_fl, attn_fl = step_flops(kind, batch, seq)
+        rec = {"batch": batch, "seq_len": seq, "dtype": "f16" if kind == "xlmr" else "bf16", "ms_per_step": ms,
+               "tokens_per_s": batch * seq / (ms * 1e-3), "real_tokens_per_s": int(lens.sum()) / (ms * 1e-3),
+               "real_tokens_per_step": int(lens.sum()),
+               "e2e_tokens_per_s": batch * seq / (m["e2e_ms"] * 1e-3), "step_tflops_padded": (gemm_fl + attn_fl) / ms / 1e9,
+               "gpu_launches_per_step": run.launches_per_step, "clocks": m["clocks"], "output_finite": m["finite"]}
+        del run, model
+        torch.cuda.empty_cache()
+        rec["kernels"] = kernel_rooflines(kind, batch, seq, peaks)
+        ops.device_status()
+        out[name] = rec
+        torch.cuda.empty_cache()
+    return out
 
 
 def kernel_case(args):
@@ -612,6 +810,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b-embed", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the short XLM-RoBERTa-large and ModernBERT-base runs of the default one-GPU line")
     ap.add_argument("--reference-ops", action="store_true",
                     help="Qwen3: the reference's op sequence (linear, heads, attention) instead of the "
                          "q/k prologue fused into the projection's store")

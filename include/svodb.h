@@ -157,7 +157,8 @@ typedef struct svodb_attn_opts {
   int32_t has_chunk;            /* `Chunk{size,left,right}` */
   int64_t chunk_size, chunk_left /* -1 = every earlier chunk */, chunk_right;
   const svodb_tensor* seg_start; /* [B,T] i32 or NULL */
-  int32_t splits;               /* 0 = library's choice; >1 needs `workspace` */
+  int32_t splits;               /* 0 or 1 = the keys in one pass; >1 = that many key splits (capped at
+                                   the number of 32-key tiles), which need `workspace` */
   int32_t has_scale;
   float scale;                  /* default 1/sqrt(D) */
   const svodb_tensor* bias;     /* [B|1,H,T,Tk] in the stream dtype, or NULL */
@@ -314,7 +315,10 @@ void svodb_qwen3_free(svodb_qwen3* model);
 int svodb_qwen3_plan(svodb_qwen3* model, int64_t rows, int64_t len, int32_t reference_ops, svodb_plan** out);
 /* One batch: ids [rows, len] i32 and lengths [rows] i32 from host memory (NULL =
  * keep what the plan holds), graph replay, pooled unit-norm rows [rows, hidden]
- * f32 to host memory (NULL = leave them on the device and do not wait). */
+ * f32 to host memory (NULL = leave them on the device and do not wait). With
+ * host_out the call waits for the replay and returns SVODB_ERR_TIMEOUT if a
+ * bounded device-side wait ran out during it; without, call
+ * `svodb_device_status(svodb_plan_stream(plan))` before trusting the rows. */
 int svodb_plan_run(svodb_plan* plan, const int32_t* host_ids, const int32_t* host_lengths, float* host_out);
 void* svodb_plan_stream(svodb_plan* plan);   /* the plan's CUstream */
 float* svodb_plan_output(svodb_plan* plan);  /* device [rows, hidden] f32 */

@@ -675,10 +675,7 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
     chose_graph(OP, "shape");
     return check_launch(OP);
   }
-  if (a.splits > 1) {
-    const int64_t tiles = (Tk + n_app + 31) / 32;
-    if (a.splits > tiles) a.splits = (int)tiles;  // capped at the key block count
-  }
+  a.splits = capped_splits(Tk + n_app, a.splits);  // capped at the key tile count
   if (a.splits > 1) {
     const size_t need = svodb_attention_workspace_bytes(B, T, H, D, a.splits);
     if (opts->workspace == nullptr || opts->workspace_bytes < need)

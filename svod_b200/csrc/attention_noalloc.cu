@@ -73,11 +73,16 @@ extern "C" int svodb_attention_splits_noalloc(const svodb_tensor* q, const svodb
   if (q == nullptr || opts == nullptr || q->rank != 4)
     return svodb_attention(q, k, v, opts, o, stream);  // let the regular entry point report it
   svodb_attn_opts with_scratch = *opts;
-  if (opts->splits > 1) {
-    const size_t need = svodb_attention_workspace_bytes(q->shape[0], q->shape[1], q->shape[2], q->shape[3], opts->splits);
+  // the split count the attention will really run with (a request above the key
+  // tile count is capped), so that what fits after capping is not refused
+  int64_t keys = k != nullptr && k->rank == 4 ? k->shape[1] : 0;
+  if (opts->has_cache && opts->cache_app_k != nullptr && opts->cache_app_k->rank == 4) keys += opts->cache_app_k->shape[1];
+  const int splits = svodb::capped_splits(keys, opts->splits);
+  if (splits > 1) {
+    const size_t need = svodb_attention_workspace_bytes(q->shape[0], q->shape[1], q->shape[2], q->shape[3], splits);
     if (need > SVODB_NOALLOC_SCRATCH_BYTES) {
       svodb::set_last_error("attention: %d key splits of this shape need %zu scratch bytes, the built-in scratch holds %zu",
-                           opts->splits, need, (size_t)SVODB_NOALLOC_SCRATCH_BYTES);
+                           splits, need, (size_t)SVODB_NOALLOC_SCRATCH_BYTES);
       return SVODB_ERR_WORKSPACE;
     }
     float* scratch = nullptr;

@@ -130,6 +130,15 @@ bool attention_tc_covers(const AttnArgs& a);
 int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 bool attention_tc_p_covers(const AttnArgs& a);
 
+// The split count an attention over `keys` keys (cached + appended) really runs
+// with: a request is capped at the number of 32-key tiles, so no split is empty
+// by construction.
+inline int capped_splits(int64_t keys, int requested) {
+  if (requested <= 1) return 1;
+  const int64_t tiles = (keys + 31) / 32;
+  return (int)(requested > tiles ? (tiles > 1 ? tiles : 1) : requested);
+}
+
 struct CombineArgs {
   const float* o_part;
   const float* m_part;

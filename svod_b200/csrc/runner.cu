@@ -267,7 +267,9 @@ int svodb_plan_run(svodb_plan* p, const int32_t* host_ids, const int32_t* host_l
   RUN(svodb_graph_replay(p->graph, p->stream));
   if (host_out != nullptr) {
     RUN(svodb_copy_d2h(host_out, p->pooled, (size_t)p->rows * D * 4, p->stream));
-    RUN(svodb_stream_sync(p->stream));
+    // waits for the stream and reads (and clears) the status word: a bounded wait
+    // that ran out during this replay is this call's error, never a later launch's
+    RUN(svodb_device_status(p->stream));
   }
   return SVODB_OK;
 }

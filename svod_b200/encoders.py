@@ -268,12 +268,15 @@ class Plan:
 
     `aux` is the padding mask `[rows, len]` (bool) or the lengths `[rows]` (i32),
     whichever the model's `forward` takes. `out` may be this rank's slice of a
-    gather buffer.
+    gather buffer; `epilogue` (no arguments) is issued on the plan's stream right
+    after the stack and becomes part of the captured graph: the all-gather of the
+    pooled rows on several GPUs, so that a replay is the whole step.
     """
 
     def __init__(self, model, rows: int, length: int, aux_kind: str, out: Optional[torch.Tensor] = None,
-                 ids_dtype=torch.int32, device="cuda"):
+                 ids_dtype=torch.int32, device="cuda", epilogue=None):
         self.model = model
+        self.epilogue = epilogue
         self.ids = torch.zeros(rows, length, dtype=ids_dtype, device=device)
         self.aux = (torch.ones(rows, length, dtype=torch.bool, device=device) if aux_kind == "mask"
                     else torch.full((rows,), length, dtype=torch.int32, device=device))
@@ -287,11 +290,17 @@ class Plan:
         # happens outside the capture.
         with torch.cuda.stream(self.stream):
             self.model.forward(self.ids, self.aux, self.out)
+            if self.epilogue is not None:
+                self.epilogue()
         self.stream.synchronize()
         ops.device_status()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=self.stream):
+        # thread-local capture mode: helper threads of the process (a collective
+        # library's watchdog) may query events while this thread captures
+        with torch.cuda.graph(g, stream=self.stream, capture_error_mode="thread_local"):
             self.model.forward(self.ids, self.aux, self.out)
+            if self.epilogue is not None:
+                self.epilogue()
         self.graph = g
         return self
 
@@ -309,6 +318,13 @@ class Plan:
         with torch.cuda.stream(self.stream):
             self.graph.replay()
 
+    def check(self):
+        """Waits for the plan's stream and raises if a bounded device-side wait ran
+        out during the replays since the last check (the status word is cleared, so
+        a stale value never reaches later launches)."""
+        with torch.cuda.stream(self.stream):
+            ops.device_status()
+
 
 # --------------------------------------------------------------------------- sharding
 def shard_rows(lengths: List[int], world: int) -> List[List[int]]:
@@ -317,6 +333,15 @@ def shard_rows(lengths: List[int], world: int) -> List[List[int]]:
     arch/src/pipelines/text.rs:968-985). Returns the row indices of each rank."""
     order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
     return [order[r::world] for r in range(world)]
+
+
+def unshard_rows(gathered: torch.Tensor, shards: List[List[int]]) -> torch.Tensor:
+    """Undoes `shard_rows` on the gathered `[rows, D]` output: gathered row
+    `r * per + i` is input row `shards[r][i]`; returns the rows in input order."""
+    order = torch.tensor([i for sh in shards for i in sh], device=gathered.device)
+    out = torch.empty_like(gathered)
+    out[order] = gathered
+    return out
 
 
 def gather_pooled(local: torch.Tensor, gathered: torch.Tensor, group=None):

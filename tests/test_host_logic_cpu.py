@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from svod_b200.encoders import gather_pooled, shard_rows
+from svod_b200.encoders import gather_pooled, shard_rows, unshard_rows
 
 
 def test_shard_rows_deals_longest_first_round_robin():
@@ -48,6 +48,40 @@ def test_all_gather_of_pooled_rows_world_size_2():
     want = np.concatenate([np.arange(rows * d, dtype=np.float32).reshape(rows, d) + 1000 * r for r in range(world)])
     for r in range(world):
         assert np.array_equal(ret[r], want)
+
+
+def _embed_stub(ids):
+    """Stands in for the stack: a row's output depends on that row alone."""
+    return torch.stack([ids.float().sum(1), ids.float().max(1).values, ids[:, 0].float()], 1)
+
+
+def _strong_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(5)                       # the same batch on every rank
+    ids = torch.randint(0, 1000, (8, 16), generator=g)
+    lens = [int(x) for x in torch.randint(1, 17, (8,), generator=g)]
+    shards = shard_rows(lens, world)
+    per = len(shards[rank])
+    gathered = torch.zeros(world * per, 3)
+    local = gathered[rank * per:(rank + 1) * per]
+    local.copy_(_embed_stub(ids[torch.tensor(shards[rank])]))
+    gather_pooled(local, gathered)
+    ret[rank] = (unshard_rows(gathered, shards).numpy(), _embed_stub(ids).numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_one_batch_dealt_over_two_ranks_comes_back_in_input_order():
+    """The strong-scaling path: one batch's rows dealt by length over the ranks,
+    each rank's rows gathered, the deal undone: every rank holds what one process
+    computes on the whole batch."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_strong_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        got, want = ret[r]
+        assert np.array_equal(got, want)
 
 
 # ---- plan-shape bucketing and packing (model/src/encoder_head.rs:366-533; qwen3/embed.rs:26-62) ----

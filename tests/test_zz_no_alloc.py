@@ -19,8 +19,10 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import svod_oracle as O
 from svod_b200 import _lib as L
 from svod_b200 import ops
+from tests.util import host, max_abs
 
 pytestmark = pytest.mark.gpu
 
@@ -60,6 +62,9 @@ def test_noalloc_split_attention_matches_the_workspace_entry_point_twice():
         # the tolerance the attention tests use; the two paths run the same kernels
         assert float((got.float() - want.float()).abs().max()) <= 2e-2
         assert torch.equal(got, want)
+        # and the oracle on the same inputs (16-bit bound)
+        ref = O.attention(host(q), host(k), host(v), key_lens=np.array(lens), dtype=O.BF16)
+        assert max_abs(host(got), ref) < 2e-2
         if trial == 1:
             assert float(got[0].abs().max()) == 0.0   # a lane with no keys attends to nothing
     ops.device_status()
@@ -75,6 +80,13 @@ def test_noalloc_refuses_partials_that_do_not_fit():
     rc, _ = call("svodb_attention_splits_noalloc", q, k, k, splits, lens)
     assert rc == L.ERR_WORKSPACE
     assert b"built-in scratch" in lib.svodb_last_error()
+    # a request above the key tile count is capped before the size check: 64 keys are two
+    # tiles, and two splits of this shape fit although the 64 requested would not
+    k64 = torch.zeros(B, 64, H, D, dtype=torch.bfloat16, device="cuda")
+    assert lib.svodb_attention_workspace_bytes(B, T, H, D, 64) > L.NOALLOC_SCRATCH_BYTES
+    assert lib.svodb_attention_workspace_bytes(B, T, H, D, 2) <= L.NOALLOC_SCRATCH_BYTES
+    rc, out = call("svodb_attention_splits_noalloc", q, k64, k64, 64, torch.full((B,), 64, dtype=torch.int32, device="cuda"))
+    assert rc == 0, lib.svodb_last_error()
     # without splits no scratch is needed and the call is the regular attention
     rc, out = call("svodb_attention_splits_noalloc", q, k, k, 1, lens)
     assert rc == 0 and float(out.abs().max()) == 0.0
