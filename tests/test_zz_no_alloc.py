@@ -82,10 +82,11 @@ def test_noalloc_refuses_partials_that_do_not_fit():
     assert b"built-in scratch" in lib.svodb_last_error()
     # a request above the key tile count is capped before the size check: 64 keys are two
     # tiles, and two splits of this shape fit although the 64 requested would not
-    k64 = torch.zeros(B, 64, H, D, dtype=torch.bfloat16, device="cuda")
-    assert lib.svodb_attention_workspace_bytes(B, T, H, D, 64) > L.NOALLOC_SCRATCH_BYTES
-    assert lib.svodb_attention_workspace_bytes(B, T, H, D, 2) <= L.NOALLOC_SCRATCH_BYTES
-    rc, out = call("svodb_attention_splits_noalloc", q, k64, k64, 64, torch.full((B,), 64, dtype=torch.int32, device="cuda"))
+    q4 = torch.zeros(4, T, H, D, dtype=torch.bfloat16, device="cuda")
+    k64 = torch.zeros(4, 64, H, D, dtype=torch.bfloat16, device="cuda")
+    assert lib.svodb_attention_workspace_bytes(4, T, H, D, 64) > L.NOALLOC_SCRATCH_BYTES
+    assert lib.svodb_attention_workspace_bytes(4, T, H, D, 2) <= L.NOALLOC_SCRATCH_BYTES
+    rc, out = call("svodb_attention_splits_noalloc", q4, k64, k64, 64, torch.full((4,), 64, dtype=torch.int32, device="cuda"))
     assert rc == 0, lib.svodb_last_error()
     # without splits no scratch is needed and the call is the regular attention
     rc, out = call("svodb_attention_splits_noalloc", q, k, k, 1, lens)
