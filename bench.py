@@ -663,8 +663,14 @@ def gpu_arm(args):
                 line["cpu_baseline"]["second_point"] = time_torch_cpu()
         print(json.dumps(line), flush=True)
     if world > 1:
+        # The line is out. Leave without tearing the process group down: destroying a
+        # communicator whose collectives live in captured graphs can wait forever, and
+        # nothing after this point is worth a hang (a timer covers the barrier too).
+        sys.stdout.flush()
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        os._exit(0)
 
 
 def other_workloads(args, device, peaks):

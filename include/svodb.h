@@ -261,6 +261,18 @@ int svodb_add_rms_norm(const svodb_tensor* x, const svodb_tensor* residual, cons
 int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
                 const svodb_tensor* type_row, int64_t pad_id, svodb_tensor* out, void* stream);
 
+/* The same lookup with the embedding norm applied before the store, one kernel
+ * instead of a gather pass and a norm pass over [B, T, D]
+ * (`Embeddings::forward`: word + position + type rows, then LayerNorm,
+ * model/src/xlm_roberta/embeddings.rs:53-63; ModernBERT: table row, then LayerNorm
+ * without bias). `norm_w` [D] is required, `norm_b` [D] may be NULL; `layer` != 0
+ * = LayerNorm, 0 = RMSNorm. Rows outside the fused kernel (D not a multiple of
+ * 256 in 256..2048, operands off the 16-byte boundary) run the lookup and then
+ * the norm in place; `svodb_last_chosen` says which. */
+int svodb_embed_norm(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+                     const svodb_tensor* type_row, int64_t pad_id, const svodb_tensor* norm_w,
+                     const svodb_tensor* norm_b, double eps, int32_t layer, svodb_tensor* out, void* stream);
+
 /* `encoder_head::pool` + `lp_normalize` (model/src/encoder_head.rs:280-286;
  * tensor/src/nn/norm.rs:205-213) and Qwen3's last-token gather
  * (model/src/qwen3/model.rs:77-99): hidden [B,L,D] -> out [B,D] f32 rows of an
@@ -270,6 +282,21 @@ int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_
  * (model/src/qwen3/embed.rs:119-136, embedder.rs:37-52). */
 int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
                svodb_tensor* out, void* stream);
+
+/* The stack's final norm, the pooling and the L2 normalisation as ONE kernel
+ * (model/src/encoder_head.rs:280-286 applied to the last norm's output;
+ * model/src/qwen3/model.rs:77-99): `hidden` [B,L,D] is the stack's output BEFORE
+ * its final norm. CLS, last-token and gather modes normalise only the tokens
+ * they pool; the masked mean normalises the row's real tokens as it sums them.
+ * `norm_w` NULL = no norm (a post-LN stack): pooling + L2 in one launch. Modes,
+ * mask / lengths / indices and `out` as in `svodb_pool`. Rows outside the fused
+ * kernel (D not a multiple of 256 in 256..2048, operands off the 16-byte
+ * boundary) take the unfused sequence, which writes the normalised hidden
+ * states into `scratch` (the shape and dtype of `hidden`; may be NULL when the
+ * fused kernel applies or there is no norm) - SVODB_ERR_WORKSPACE without it. */
+int svodb_norm_pool(const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b, double eps,
+                    int32_t layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
+                    int32_t normalize, svodb_tensor* out, void* stream);
 
 /* RoPE tables `Tensor::rope_table` (tensor/src/transformer.rs:130-164): angles
  * and cos/sin in f32, cast last; positions [P] i32 (NULL = 0..P-1);

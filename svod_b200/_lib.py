@@ -148,7 +148,11 @@ SYMBOLS = [
     ("svodb_rms_norm", C.c_int, [TensorP, TensorP, C.c_double, TensorP, C.c_void_p]),
     ("svodb_add_rms_norm", C.c_int, [TensorP, TensorP, TensorP, C.c_double, TensorP, TensorP, C.c_void_p]),
     ("svodb_embed", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_int64, TensorP, C.c_void_p]),
+    ("svodb_embed_norm", C.c_int, [TensorP, TensorP, TensorP, TensorP, C.c_int64, TensorP, TensorP, C.c_double, C.c_int32,
+                                   TensorP, C.c_void_p]),
     ("svodb_pool", C.c_int, [TensorP, TensorP, C.c_int32, C.c_int32, TensorP, C.c_void_p]),
+    ("svodb_norm_pool", C.c_int, [TensorP, TensorP, TensorP, C.c_double, C.c_int32, TensorP, TensorP, C.c_int32,
+                                  C.c_int32, TensorP, C.c_void_p]),
     ("svodb_rope_table", C.c_int, [C.c_double, TensorP, C.c_int32, TensorP, TensorP, C.c_void_p]),
     ("svodb_module_load", C.c_int,
      [C.c_void_p, C.c_size_t, C.c_char_p, C.POINTER(AbiParam), C.c_int32, C.POINTER(C.c_void_p)]),

@@ -945,9 +945,23 @@ int svodb_add_rms_norm(const svodb_tensor* x, const svodb_tensor* residual, cons
 // ---------------------------------------------------------------------------
 // glue
 // ---------------------------------------------------------------------------
-int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
-                const svodb_tensor* type_row, int64_t pad_id, svodb_tensor* out, void* stream) {
-  static const char* OP = "embed";
+namespace {
+// A fused norm's operands: weight [D] (required), bias [D] or null, both of the row dtype.
+int norm_operands(const char* op, const svodb_tensor* w, const svodb_tensor* b, int64_t d, int dtype) {
+  TRY(realized(op, "norm weight", w));
+  if (numel(w) != d || !contiguous(w)) return shape_err(op, "norm weight", w, "[D]");
+  if (w->dtype != dtype) return dtype_err(op, "norm weight", w->dtype, dtype);
+  if (b != nullptr) {
+    TRY(realized(op, "norm bias", b));
+    if (numel(b) != d || !contiguous(b)) return shape_err(op, "norm bias", b, "[D]");
+    if (b->dtype != dtype) return dtype_err(op, "norm bias", b->dtype, dtype);
+  }
+  return SVODB_OK;
+}
+
+int embed_impl(const char* OP, const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+               const svodb_tensor* type_row, int64_t pad_id, const svodb_tensor* norm_w, const svodb_tensor* norm_b,
+               double eps, int layer, svodb_tensor* out, void* stream) {
   GUARD(OP);
   TRY(realized(OP, "ids", ids));
   TRY(realized(OP, "table", table));
@@ -983,13 +997,44 @@ int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_
   a.vocab = table->shape[0];
   a.max_pos = pos_table ? pos_table->shape[0] : 1;
   a.dtype = table->dtype;
+  if (norm_w == nullptr) {
+    launch_embed(a, (cudaStream_t)stream);
+    return check_launch(OP);
+  }
+  TRY(norm_operands(OP, norm_w, norm_b, d, table->dtype));
+  EmbedNormArgs n{norm_w->data, norm_b ? norm_b->data : nullptr, (float)eps, layer};
+  if (launch_embed_norm(a, n, (cudaStream_t)stream)) {
+    chose_kernel(OP, "embed_norm", "{tokens_per_block:8}");
+    return check_launch(OP);
+  }
+  // outside the fused kernel's rows: the lookup, then the norm over it in place
   launch_embed(a, (cudaStream_t)stream);
+  NormArgs r{};
+  r.x = out->data, r.w = norm_w->data, r.b = n.b, r.out = out->data;
+  r.rows = a.batch * a.t, r.d = a.d, r.eps = n.eps, r.layer = layer, r.dtype = a.dtype;
+  launch_norm(r, (cudaStream_t)stream);
+  chose_graph(OP, "shape");
   return check_launch(OP);
 }
+}  // namespace
 
-int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
-               svodb_tensor* out, void* stream) {
-  static const char* OP = "pool";
+int svodb_embed(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+                const svodb_tensor* type_row, int64_t pad_id, svodb_tensor* out, void* stream) {
+  return embed_impl("embed", ids, table, pos_table, type_row, pad_id, nullptr, nullptr, 0.0, 1, out, stream);
+}
+
+int svodb_embed_norm(const svodb_tensor* ids, const svodb_tensor* table, const svodb_tensor* pos_table,
+                     const svodb_tensor* type_row, int64_t pad_id, const svodb_tensor* norm_w,
+                     const svodb_tensor* norm_b, double eps, int32_t layer, svodb_tensor* out, void* stream) {
+  if (norm_w == nullptr) return fail(SVODB_ERR_UNREALIZED, "embed_norm: norm weight is missing");
+  return embed_impl("embed_norm", ids, table, pos_table, type_row, pad_id, norm_w, norm_b, eps, layer ? 1 : 0, out,
+                    stream);
+}
+
+namespace {
+int pool_impl(const char* OP, const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b,
+              double eps, int layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
+              int32_t normalize, svodb_tensor* out, void* stream, bool fused) {
   GUARD(OP);
   TRY(realized(OP, "hidden", hidden));
   TRY(realized(OP, "out", out));
@@ -1029,8 +1074,45 @@ int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, 
   a.batch = B, a.l = L;
   a.d = (int)D;
   a.dtype = hidden->dtype;
+  if (!fused) {
+    launch_pool(a, (cudaStream_t)stream);
+    return check_launch(OP);
+  }
+  if (norm_w != nullptr) TRY(norm_operands(OP, norm_w, norm_b, D, hidden->dtype));
+  EmbedNormArgs n{norm_w ? norm_w->data : nullptr, norm_b ? norm_b->data : nullptr, (float)eps, layer};
+  if (launch_norm_pool(a, n, (cudaStream_t)stream)) {
+    chose_kernel(OP, "norm_pool", norm_w ? "{norm:fused}" : "{norm:none}");
+    return check_launch(OP);
+  }
+  // outside the fused kernel's rows: the norm into the caller's scratch, then the two pooling kernels
+  if (norm_w != nullptr) {
+    if (scratch == nullptr || scratch->data == nullptr || !same_shape(scratch, hidden) || !contiguous(scratch) ||
+        scratch->dtype != hidden->dtype)
+      return fail(SVODB_ERR_WORKSPACE, "%s: rows of %lld elements take the unfused path, which needs a scratch tensor "
+                  "of the hidden states' shape", OP, (long long)D);
+    NormArgs r{};
+    r.x = hidden->data, r.w = norm_w->data, r.b = n.b, r.out = scratch->data;
+    r.rows = B * L, r.d = (int)D, r.eps = n.eps, r.layer = layer, r.dtype = hidden->dtype;
+    launch_norm(r, (cudaStream_t)stream);
+    a.hidden = scratch->data;
+  }
   launch_pool(a, (cudaStream_t)stream);
+  chose_graph(OP, "shape");
   return check_launch(OP);
+}
+}  // namespace
+
+int svodb_pool(const svodb_tensor* hidden, const svodb_tensor* mask_or_lengths, int32_t mode, int32_t normalize,
+               svodb_tensor* out, void* stream) {
+  return pool_impl("pool", hidden, nullptr, nullptr, 0.0, 1, nullptr, mask_or_lengths, mode, normalize, out, stream,
+                   false);
+}
+
+int svodb_norm_pool(const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b, double eps,
+                    int32_t layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
+                    int32_t normalize, svodb_tensor* out, void* stream) {
+  return pool_impl("norm_pool", hidden, norm_w, norm_b, eps, layer ? 1 : 0, scratch, mask_or_lengths, mode, normalize,
+                   out, stream, true);
 }
 
 int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,

@@ -3,6 +3,7 @@
 // RoPE tables. All HBM-bound or negligible; written for coalesced access.
 #include "common.cuh"
 #include "kernels.h"
+#include "rows_parts.cuh"
 #include "svodb.h"
 
 namespace svodb {
@@ -98,6 +99,194 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same lookup with the embedding LayerNorm applied before the store
+// (model/src/xlm_roberta/embeddings.rs:53-63: word + position + type, then LN):
+// one kernel instead of a gather pass and a norm pass over [B, T, D]. A block
+// takes kTok tokens of one row; its warps each gather one token's row into
+// registers (every add rounded to the element type, as above), normalise the
+// rounded sum and store it. d = SPANS * 256.
+template <typename T, typename I, int SPANS>
+__global__ void __launch_bounds__(kTok * 32)
+    embed_norm_kernel(const I* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ pos_table,
+                      const T* __restrict__ type_row, int64_t pad_id, const T* __restrict__ w,
+                      const T* __restrict__ b, float eps, int layer, T* __restrict__ out, int64_t t_len,
+                      int64_t vocab, int64_t max_pos) {
+  constexpr int D = SPANS * 256;
+  __shared__ int red[kTok];
+  __shared__ int64_t tok_id[kTok];
+  __shared__ int64_t tok_pos[kTok];
+  const int64_t bi = blockIdx.y;
+  const int64_t t0 = (int64_t)blockIdx.x * kTok;
+  const I* row = ids + bi * t_len;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int before = 0;
+  if (pos_table != nullptr && pad_id >= 0) {
+    int cnt = 0;
+    for (int64_t i = tid; i < t0; i += kTok * 32) cnt += (int64_t)row[i] != pad_id;
+    cnt = (int)warp_sum((float)cnt);  // counts stay below 2^24: exact in f32
+    if (lane == 0) red[warp] = cnt;
+    __syncthreads();
+    for (int i = 0; i < kTok; ++i) before += red[i];
+  }
+  if (tid == 0) {
+    int run = before;
+    for (int j = 0; j < kTok; ++j) {
+      const int64_t t = t0 + j;
+      if (t >= t_len) break;
+      int64_t id = (int64_t)row[t];
+      const bool real = id != pad_id;
+      run += real ? 1 : 0;
+      tok_pos[j] = pad_id >= 0 ? (real ? run : 0) + pad_id : t;
+      tok_id[j] = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    }
+  }
+  __syncthreads();
+  const int64_t t = t0 + warp;
+  if (t >= t_len) return;
+  const T* src = table + tok_id[warp] * D;
+  int64_t pp = tok_pos[warp];
+  pp = pp < 0 ? 0 : (pp >= max_pos ? max_pos - 1 : pp);
+  const T* psrc = pos_table != nullptr ? pos_table + pp * D : nullptr;
+  float v[SPANS][8];
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    const int off = s * 256 + lane * 8;
+    rows_parts::unpack8<T>(ldg128(src + off), v[s]);
+    if (psrc != nullptr) {
+      float q[8];
+      rows_parts::unpack8<T>(ldg128(psrc + off), q);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[s][i] += q[i];
+      rows_parts::unpack8<T>(rows_parts::pack8<T>(v[s]), v[s]);
+    }
+    if (type_row != nullptr) {
+      float q[8];
+      rows_parts::unpack8<T>(ldg128(type_row + off), q);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[s][i] += q[i];
+      rows_parts::unpack8<T>(rows_parts::pack8<T>(v[s]), v[s]);
+    }
+  }
+  const float inv = rows_parts::centre_and_scale<SPANS>(v, eps, layer);
+  T* dst = out + (bi * t_len + t) * D;
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    const int off = s * 256 + lane * 8;
+    float y[8];
+    rows_parts::affine8<T>(v[s], inv, ldg128(w + off), b != nullptr ? ldg128(b + off) : make_uint4(0, 0, 0, 0),
+                           b != nullptr, y);
+    stg128(dst + off, rows_parts::pack8<T>(y));
+  }
+}
+
+// Final norm + pooling + L2 in one kernel (model/src/encoder_head.rs:280-286 after
+// the stack's last norm): one block per output row. CLS, last-token and gather
+// modes normalise the ONE token they pool (the other rows of the hidden states
+// never need their final norm); the masked mean walks the row's real tokens,
+// normalising each, and sums them in f32. The normalised values are rounded to
+// the element type before they are pooled, as the unfused sequence stores them.
+// w == nullptr: the hidden states are pooled as they are. d = SPANS * 256.
+template <typename T, int SPANS>
+__global__ void __launch_bounds__(256)
+    norm_pool_kernel(const T* __restrict__ hidden, const T* __restrict__ w, const T* __restrict__ b, float eps,
+                     int layer, const void* __restrict__ aux, int aux_i32, int mode, int slots, int normalize,
+                     float* __restrict__ out, int64_t out_row_stride, int64_t l_len) {
+  constexpr int D = SPANS * 256;
+  __shared__ float part[8192];  // [warps][D], warps * D <= 8192
+  __shared__ float cnts[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int64_t bi = mode == 3 ? blockIdx.x / slots : blockIdx.x;
+  const T* h = hidden + bi * l_len * D;
+  float acc[SPANS][8];
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[s][i] = 0.f;
+  float cnt = 0.f;
+  int64_t first = 0, last = 1;  // the token range this block walks
+  if (mode == 1) {
+    last = l_len;
+  } else if (mode == 2) {
+    first = (int64_t)((const int32_t*)aux)[bi] - 1;
+  } else if (mode == 3) {
+    first = (int64_t)((const int32_t*)aux)[blockIdx.x];
+  }
+  if (mode != 1) {
+    first = first < 0 ? 0 : (first > l_len - 1 ? l_len - 1 : first);
+    last = first + 1;
+  }
+  for (int64_t t = first + warp; t < last; t += warps) {
+    if (mode == 1) {
+      const int m = aux_i32 ? ((const int32_t*)aux)[bi * l_len + t] : (int)((const uint8_t*)aux)[bi * l_len + t];
+      if (m == 0) continue;
+      cnt += 1.f;
+    }
+    float v[SPANS][8];
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s) rows_parts::unpack8<T>(ldg128(h + t * D + s * 256 + lane * 8), v[s]);
+    if (w != nullptr) {
+      const float inv = rows_parts::centre_and_scale<SPANS>(v, eps, layer);
+#pragma unroll
+      for (int s = 0; s < SPANS; ++s) {
+        const int off = s * 256 + lane * 8;
+        float y[8];
+        rows_parts::affine8<T>(v[s], inv, ldg128(w + off), b != nullptr ? ldg128(b + off) : make_uint4(0, 0, 0, 0),
+                               b != nullptr, y);
+        rows_parts::unpack8<T>(rows_parts::pack8<T>(y), v[s]);  // the 16-bit value the norm would store
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[s][i] += v[s][i];
+  }
+  if (warps > 1) {
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[warp * D + s * 256 + lane * 8 + i] = acc[s][i];
+    if (lane == 0) cnts[warp] = cnt;
+    __syncthreads();
+    if (warp != 0) return;
+    cnt = 0.f;
+    for (int k = 0; k < warps; ++k) cnt += cnts[k];
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = 0.f;
+        for (int k = 0; k < warps; ++k) t += part[k * D + s * 256 + lane * 8 + i];  // fixed order: reproducible
+        acc[s][i] = t;
+      }
+  }
+  if (mode == 1) {
+    const float invc = 1.0f / fmaxf(cnt, 1e-9f);
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[s][i] *= invc;
+  }
+  if (normalize) {
+    float sq = 0.f;
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq = fmaf(acc[s][i], acc[s][i], sq);
+    const float inv = 1.0f / (sqrtf(warp_sum(sq)) + 1.17549435e-38f);
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[s][i] *= inv;
+  }
+  float* dst = out + (int64_t)blockIdx.x * out_row_stride;
+#pragma unroll
+  for (int s = 0; s < SPANS; ++s) {
+    float4* d4 = reinterpret_cast<float4*>(dst + s * 256 + lane * 8);
+    d4[0] = make_float4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]);
+    d4[1] = make_float4(acc[s][4], acc[s][5], acc[s][6], acc[s][7]);
+  }
+}
+
 // Pooling, pass 1: out[b, c] = pooled value in f32 (un-normalised).
 // grid (ceil(D/128), B), 256 threads: thread = (token lane 0..1, column 0..127).
 template <typename T>
@@ -190,6 +379,69 @@ void launch_embed(const EmbedArgs& a, cudaStream_t s) {
     else SVODB_EMBED(__half, int32_t);
   }
 #undef SVODB_EMBED
+}
+
+namespace {
+template <typename T, typename I>
+bool embed_norm_dispatch(const EmbedArgs& a, const EmbedNormArgs& n, cudaStream_t s) {
+  dim3 grid((unsigned)((a.t + kTok - 1) / kTok), (unsigned)a.batch);
+#define SVODB_EN(SP)                                                                                                \
+  case SP:                                                                                                          \
+    embed_norm_kernel<T, I, SP><<<grid, kTok * 32, 0, s>>>((const I*)a.ids, (const T*)a.table, (const T*)a.pos_table, \
+                                                           (const T*)a.type_row, a.pad_id, (const T*)n.w,             \
+                                                           (const T*)n.b, n.eps, n.layer, (T*)a.out, a.t, a.vocab,   \
+                                                           a.max_pos);                                               \
+    return true
+  switch (a.d / 256) {
+    SVODB_EN(1); SVODB_EN(2); SVODB_EN(3); SVODB_EN(4); SVODB_EN(5); SVODB_EN(6); SVODB_EN(7); SVODB_EN(8);
+    default: return false;
+  }
+#undef SVODB_EN
+}
+
+template <typename T>
+bool norm_pool_dispatch(const PoolArgs& a, const EmbedNormArgs& n, cudaStream_t s) {
+  const int64_t out_rows = a.mode == 3 ? a.batch * a.slots : a.batch;
+  // the masked mean walks a whole row with as many warps as the partial sums leave room for
+  const int spans = a.d / 256;
+  int warps = 1;
+  if (a.mode == 1) warps = spans <= 4 ? 8 : (spans <= 8 ? 4 : 1);
+#define SVODB_NP(SP)                                                                                               \
+  case SP:                                                                                                         \
+    norm_pool_kernel<T, SP><<<(unsigned)out_rows, warps * 32, 0, s>>>((const T*)a.hidden, (const T*)n.w,           \
+                                                                      (const T*)n.b, n.eps, n.layer, a.aux,         \
+                                                                      a.aux_i32, a.mode, a.slots, a.normalize,      \
+                                                                      a.out, a.out_row_stride, a.l);                \
+    return true
+  switch (spans) {
+    SVODB_NP(1); SVODB_NP(2); SVODB_NP(3); SVODB_NP(4); SVODB_NP(5); SVODB_NP(6); SVODB_NP(7); SVODB_NP(8);
+    default: return false;
+  }
+#undef SVODB_NP
+}
+}  // namespace
+
+int launch_embed_norm(const EmbedArgs& a, const EmbedNormArgs& n, cudaStream_t s) {
+  if (a.batch * a.t == 0) return 1;
+  const bool fits = a.d % 256 == 0 && a.d >= 256 && a.d <= 2048 && aligned16(a.table) && aligned16(a.pos_table) &&
+                    aligned16(a.type_row) && aligned16(a.out) && aligned16(n.w) && aligned16(n.b);
+  if (!fits) return 0;
+  if (a.dtype == SVODB_BF16)
+    return (a.ids_i64 ? embed_norm_dispatch<__nv_bfloat16, int64_t>(a, n, s)
+                      : embed_norm_dispatch<__nv_bfloat16, int32_t>(a, n, s)) ? 1 : 0;
+  if (a.dtype == SVODB_F16)
+    return (a.ids_i64 ? embed_norm_dispatch<__half, int64_t>(a, n, s) : embed_norm_dispatch<__half, int32_t>(a, n, s)) ? 1 : 0;
+  return 0;
+}
+
+int launch_norm_pool(const PoolArgs& a, const EmbedNormArgs& n, cudaStream_t s) {
+  if (a.batch == 0) return 1;
+  const bool fits = a.d % 256 == 0 && a.d >= 256 && a.d <= 2048 && aligned16(a.hidden) && aligned16(n.w) &&
+                    aligned16(n.b) && aligned16(a.out) && a.out_row_stride % 4 == 0;
+  if (!fits) return 0;
+  if (a.dtype == SVODB_BF16) return norm_pool_dispatch<__nv_bfloat16>(a, n, s) ? 1 : 0;
+  if (a.dtype == SVODB_F16) return norm_pool_dispatch<__half>(a, n, s) ? 1 : 0;
+  return 0;
 }
 
 void launch_pool(const PoolArgs& a, cudaStream_t s) {

@@ -75,6 +75,20 @@ struct PoolArgs {
 };
 void launch_pool(const PoolArgs& a, cudaStream_t s);
 
+// A norm fused with the lookup before it or the pooling after it: weight
+// (null = no norm, pooling only), bias (nullable), LayerNorm or RMSNorm.
+struct EmbedNormArgs {
+  const void* w;
+  const void* b;
+  float eps;
+  int layer;  // 1 = LayerNorm, 0 = RMSNorm
+};
+// Both return 1 when the fused kernel ran, 0 (nothing launched) when the shape,
+// dtype or alignment is outside it: 16-bit rows of 256..2048 elements in
+// multiples of 256 on 16-byte boundaries.
+int launch_embed_norm(const EmbedArgs& a, const EmbedNormArgs& n, cudaStream_t s);
+int launch_norm_pool(const PoolArgs& a, const EmbedNormArgs& n, cudaStream_t s);
+
 void launch_rope_table(double theta, const int32_t* positions, int64_t n_pos, int head_dim, void* cos, void* sin,
                        int dtype, cudaStream_t s);
 

@@ -10,6 +10,7 @@
 // registers so x (and the residual) are read exactly once.
 #include "common.cuh"
 #include "kernels.h"
+#include "rows_parts.cuh"
 #include "svodb.h"
 
 namespace svodb {
@@ -36,72 +37,29 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   }
   const int64_t stride = (int64_t)gridDim.x * kWarpsPerBlock;
   for (int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); row < rows; row += stride) {
-  const T* xr = x + row * D;
-  float v[SPANS][8];
+    const T* xr = x + row * D;
+    float v[SPANS][8];
 #pragma unroll
-  for (int s = 0; s < SPANS; ++s) {
-    const int off = s * 256 + lane * 8;
-    uint4 u = ldg128(xr + off);
-    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+    for (int s = 0; s < SPANS; ++s) {
+      const int off = s * 256 + lane * 8;
+      rows_parts::unpack8<T>(ldg128(xr + off), v[s]);
+      if (res != nullptr) {
+        float r[8];
+        rows_parts::unpack8<T>(ldg128(res + row * D + off), r);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = Elem<T>::unpack(uu[i]);
-      v[s][2 * i] = f.x;
-      v[s][2 * i + 1] = f.y;
-    }
-    if (res != nullptr) {
-      uint4 r = ldg128(res + row * D + off);
-      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-      uint32_t packed[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 f = Elem<T>::unpack(rr[i]);
-        packed[i] = Elem<T>::pack(v[s][2 * i] + f.x, v[s][2 * i + 1] + f.y);
-        float2 g = Elem<T>::unpack(packed[i]);
-        v[s][2 * i] = g.x;
-        v[s][2 * i + 1] = g.y;
+        for (int i = 0; i < 8; ++i) v[s][i] += r[i];
+        const uint4 packed = rows_parts::pack8<T>(v[s]);  // the rounded sum is what gets normalised
+        rows_parts::unpack8<T>(packed, v[s]);
+        stg128(sum + row * D + off, packed);
       }
-      stg128(sum + row * D + off, make_uint4(packed[0], packed[1], packed[2], packed[3]));
     }
-  }
-  float mean = 0.f;
-  if (layer) {
-    float acc = 0.f;
+    const float inv = rows_parts::centre_and_scale<SPANS>(v, eps, layer);
 #pragma unroll
-    for (int s = 0; s < SPANS; ++s)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc += v[s][i];
-    mean = warp_sum(acc) * (1.0f / D);
-  }
-  float sq = 0.f;
-#pragma unroll
-  for (int s = 0; s < SPANS; ++s)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[s][i] -= mean;
-      sq = fmaf(v[s][i], v[s][i], sq);
+    for (int s = 0; s < SPANS; ++s) {
+      float y[8];
+      rows_parts::affine8<T>(v[s], inv, wreg[s], breg[s], b != nullptr, y);
+      stg128(out + row * D + s * 256 + lane * 8, rows_parts::pack8<T>(y));
     }
-  const float inv = rsqrtf(warp_sum(sq) * (1.0f / D) + eps);
-#pragma unroll
-  for (int s = 0; s < SPANS; ++s) {
-    const int off = s * 256 + lane * 8;
-    const uint32_t ww[4] = {wreg[s].x, wreg[s].y, wreg[s].z, wreg[s].w};
-    const uint32_t bb[4] = {breg[s].x, breg[s].y, breg[s].z, breg[s].w};
-    uint32_t packed[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 wf = Elem<T>::unpack(ww[i]);
-      float2 bf = Elem<T>::unpack(bb[i]);
-      float y0 = v[s][2 * i] * inv * wf.x;
-      float y1 = v[s][2 * i + 1] * inv * wf.y;
-      if (b != nullptr) {
-        y0 += bf.x;
-        y1 += bf.y;
-      }
-      packed[i] = Elem<T>::pack(y0, y1);
-    }
-    stg128(out + row * D + off, make_uint4(packed[0], packed[1], packed[2], packed[3]));
-  }
   }
 }
 

@@ -107,8 +107,9 @@ class XlmRobertaEncoder:
     def hidden(self, ids: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         c, p = self.cfg, self.p
         H = c.num_attention_heads
-        x = ops.embed(ids, p["word"], p["pos"], p["type"], c.pad_token_id)
-        x = ops.layer_norm(x, p["emb_ln_w"], p["emb_ln_b"], c.layer_norm_eps)
+        # lookup (word + position + type) and the embedding LayerNorm: one kernel
+        x = ops.embed_norm(ids, p["word"], p["emb_ln_w"], p["emb_ln_b"], c.layer_norm_eps, p["pos"], p["type"],
+                           c.pad_token_id)
         return self.run_layers(x, mask)
 
     def run_layers(self, x: torch.Tensor, mask: torch.Tensor, start: int = 0, stop: Optional[int] = None):
@@ -130,7 +131,8 @@ class XlmRobertaEncoder:
     def forward(self, ids, mask, out=None):
         h = self.hidden(ids, mask)
         mode = ops.POOL_CLS if self.cfg.pooling == "cls" else ops.POOL_MEAN
-        return ops.pool(h, mask if mode == ops.POOL_MEAN else None, mode, True, out)
+        # post-LN stack: the last layer's norm is the final one; pooling + L2 in one kernel
+        return ops.norm_pool(h, aux=mask if mode == ops.POOL_MEAN else None, mode=mode, out=out)
 
 
 # --------------------------------------------------------------------------- Qwen3
@@ -193,7 +195,10 @@ class Qwen3Embedder:
         return x
 
     def forward(self, ids, lengths, out=None):
-        return ops.pool(self.hidden(ids), lengths, ops.POOL_LAST, True, out)
+        # final RMSNorm of the pooled (last real) tokens alone, pooling and L2: one kernel
+        x = self.run_layers(ops.embed(ids, self.p["embed"]))
+        return ops.norm_pool(x, self.p["norm_w"], None, self.cfg.rms_norm_eps, layer=False, aux=lengths,
+                             mode=ops.POOL_LAST, out=out)
 
 
 # --------------------------------------------------------------------------- ModernBERT
@@ -229,7 +234,7 @@ class ModernBertEncoder:
         c, p = self.cfg, self.p
         H = c.num_attention_heads
         hd = c.hidden_size // H
-        x = ops.layer_norm(ops.embed(ids, p["embed"]), p["emb_ln_w"], None, c.norm_eps)
+        x = ops.embed_norm(ids, p["embed"], p["emb_ln_w"], None, c.norm_eps)
         return ops.layer_norm(self.run_layers(x, mask), p["final_ln_w"], None, c.norm_eps)
 
     def run_layers(self, x: torch.Tensor, mask: torch.Tensor, start: int = 0, stop: Optional[int] = None):
@@ -254,9 +259,12 @@ class ModernBertEncoder:
         return x
 
     def forward(self, ids, mask, out=None):
-        h = self.hidden(ids, mask)
-        mode = ops.POOL_CLS if self.cfg.pooling == "cls" else ops.POOL_MEAN
-        return ops.pool(h, mask if mode == ops.POOL_MEAN else None, mode, True, out)
+        c, p = self.cfg, self.p
+        x = self.run_layers(ops.embed_norm(ids, p["embed"], p["emb_ln_w"], None, c.norm_eps), mask)
+        mode = ops.POOL_CLS if c.pooling == "cls" else ops.POOL_MEAN
+        # final LayerNorm (of the tokens that are pooled), pooling and L2: one kernel
+        return ops.norm_pool(x, p["final_ln_w"], None, c.norm_eps, aux=mask if mode == ops.POOL_MEAN else None,
+                             mode=mode, out=out)
 
 
 # --------------------------------------------------------------------------- plan replay

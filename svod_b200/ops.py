@@ -431,7 +431,47 @@ def embed(ids, table, pos_table=None, type_row=None, pad_id: int = -1):
     return out
 
 
+def embed_norm(ids, table, norm_w, norm_b=None, eps: float = 1e-5, pos_table=None, type_row=None, pad_id: int = -1,
+               layer: bool = True):
+    """The lookup of `embed` and the embedding norm in one kernel
+    (model/src/xlm_roberta/embeddings.rs:53-63: word + position + type, LayerNorm)."""
+    B, T = ids.shape
+    out = torch.empty(B, T, table.shape[1], dtype=table.dtype, device=table.device)
+    a, b, c, d, e = _desc(ids), _desc(table), _desc(pos_table), _desc(type_row), _desc(out)
+    w, bb = _desc(norm_w), _desc(norm_b)
+    _check(L.load().svodb_embed_norm(_p(a), _p(b), _p(c), _p(d), int(pad_id), _p(w), _p(bb), float(eps), int(layer),
+                                     _p(e), _stream()), 1)
+    return out
+
+
 POOL_CLS, POOL_MEAN, POOL_LAST, POOL_GATHER = 0, 1, 2, 3
+
+
+def norm_pool(hidden, norm_w=None, norm_b=None, eps: float = 1e-5, layer: bool = True, aux=None, mode: int = POOL_CLS,
+              normalize: bool = True, out=None):
+    """The stack's final norm (none when `norm_w` is None), the pooling and the
+    L2 normalisation in one kernel (model/src/encoder_head.rs:280-286;
+    model/src/qwen3/model.rs:77-99): `hidden [B,L,D]` before its final norm ->
+    f32 `[B,D]`. Only the pooled tokens are normalised (every real token for the
+    masked mean)."""
+    B, _, D = hidden.shape
+    if out is None:
+        rows = B * aux.shape[1] if mode == POOL_GATHER else B
+        out = torch.empty(rows, D, dtype=torch.float32, device=hidden.device)
+    if aux is not None and aux.dtype not in (torch.bool, torch.uint8, torch.int32):
+        aux = aux.to(torch.int32)
+    a, b, c, w, bb = _desc(hidden), _desc(aux), _desc(out), _desc(norm_w), _desc(norm_b)
+    lib = L.load()
+    rc = lib.svodb_norm_pool(_p(a), _p(w), _p(bb), float(eps), int(layer), None, _p(b), int(mode), int(normalize), _p(c),
+                             _stream())
+    if rc == L.ERR_WORKSPACE:
+        # rows outside the fused kernel: the unfused sequence wants room for the normalised hidden states
+        scratch = torch.empty_like(hidden)
+        sd = _desc(scratch)
+        rc = lib.svodb_norm_pool(_p(a), _p(w), _p(bb), float(eps), int(layer), _p(sd), _p(b), int(mode), int(normalize),
+                                 _p(c), _stream())
+    _check(rc, 1)
+    return out
 
 
 def pool(hidden, aux=None, mode: int = POOL_CLS, normalize: bool = True, out=None):

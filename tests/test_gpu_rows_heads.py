@@ -176,3 +176,68 @@ def test_views_off_the_16_byte_boundary_take_the_generic_kernels():
     got = ops.embed(torch.from_numpy(ids).cuda(), off_boundary(table, dt), off_boundary(pos, dt, 5), None, 1)
     assert np.array_equal(host(got), O.round_to(dt, table[ids] + pos[pid]))
     ops.device_status()
+
+
+@pytest.mark.parametrize("dt,D", [(O.F16, 1024), (O.BF16, 768), (O.BF16, 320)])
+def test_embedding_lookup_with_the_norm_in_one_kernel(dt, D):
+    """`embed_norm`: word + position + type rows (each add rounded) and the
+    LayerNorm of the rounded sum, against the oracle and bit for bit against the
+    two separate ops; D = 320 has no fused kernel and takes the two-pass path."""
+    rng = np.random.default_rng(D)
+    V, B, T = 500, 3, 70
+    table = O.round_to(dt, rng.standard_normal((V, D)) * 0.02)
+    pos = O.round_to(dt, rng.standard_normal((T + 2, D)) * 0.02)
+    typ = O.round_to(dt, rng.standard_normal((1, D)) * 0.02)
+    w = O.round_to(dt, 1 + 0.1 * rng.standard_normal(D))
+    b = O.round_to(dt, 0.1 * rng.standard_normal(D))
+    ids = rng.integers(2, V, (B, T))
+    for r, l in enumerate([70, 33, 1]):
+        ids[r, l:] = 1
+    I = torch.from_numpy(ids).cuda()
+    e = O.round_to(dt, O.round_to(dt, table[ids] + pos[O.xlmr_position_ids(ids, 1)]) + typ[0])
+    want, _ = O.norm_rows("layer", e, w, b, eps=1e-5, dtype=dt)
+    got = ops.embed_norm(I, dev(table, dt), dev(w, dt), dev(b, dt), 1e-5, dev(pos, dt), dev(typ, dt), 1)
+    assert ("kernel embed_norm" in ops.chosen()) == (D % 256 == 0)
+    assert rel_close(host(got), want, 1e-2)
+    two = ops.layer_norm(ops.embed(I, dev(table, dt), dev(pos, dt), dev(typ, dt), 1), dev(w, dt), dev(b, dt), 1e-5)
+    assert torch.equal(got, two)
+    # ModernBERT's form: the table row alone, LayerNorm without bias, i32 ids
+    want2, _ = O.norm_rows("layer", table[ids], w, None, eps=1e-5, dtype=dt)
+    got2 = ops.embed_norm(I.to(torch.int32), dev(table, dt), dev(w, dt), None, 1e-5)
+    assert rel_close(host(got2), want2, 1e-2)
+    ops.device_status()
+
+
+@pytest.mark.parametrize("dt,D,kind", [(O.BF16, 1024, "rms"), (O.BF16, 768, "layer"), (O.F16, 1024, None),
+                                       (O.BF16, 320, "layer")])
+def test_final_norm_pooling_and_l2_in_one_kernel(dt, D, kind):
+    """`norm_pool` against the oracle's norm -> pool -> L2 for every pooling mode;
+    D = 320 has no fused kernel and takes the unfused sequence through a scratch."""
+    rng = np.random.default_rng(D + 1)
+    B, T = 3, 90
+    h = O.round_to(dt, rng.standard_normal((B, T, D)) * 2 + 0.5)
+    w = O.round_to(dt, 1 + 0.1 * rng.standard_normal(D))
+    lens = [90, 41, 0]
+    mask = np.arange(T)[None, :] < np.array(lens)[:, None]
+    normed = h if kind is None else O.norm_rows(kind, h, w, None, eps=1e-6, dtype=dt)[0]
+    H, W = dev(h, dt), (None if kind is None else dev(w, dt))
+    kw = dict(norm_w=W, eps=1e-6, layer=kind != "rms")
+    M, Ln = torch.from_numpy(mask).cuda(), torch.tensor(lens, dtype=torch.int32).cuda()
+    got = ops.norm_pool(H, aux=None, mode=ops.POOL_CLS, **kw)
+    assert ("kernel norm_pool" in ops.chosen()) == (D % 256 == 0)
+    assert max_abs(host(got), O.pool(normed, mask, "cls")) < 2e-4
+    got = ops.norm_pool(H, aux=M, mode=ops.POOL_MEAN, **kw)
+    want = O.pool(normed, mask, "mean")
+    assert max_abs(host(got), want) < 2e-4 and np.all(host(got)[2] == 0)       # an all-pad row stays the zero vector
+    got = ops.norm_pool(H, aux=Ln, mode=ops.POOL_LAST, **kw)
+    assert max_abs(host(got), O.pool(normed, None, "last", lengths=np.array(lens))) < 2e-4
+    idx = np.array([[0, 5], [40, 40], [89, 3]])
+    got = ops.norm_pool(H, aux=torch.from_numpy(idx.astype(np.int32)).cuda(), mode=ops.POOL_GATHER, **kw)
+    want = O.l2_normalize(np.stack([normed[b, t] for b in range(B) for t in idx[b]]))
+    assert max_abs(host(got), want) < 2e-4
+    # the slot of a wider buffer is honoured, unnormalised pooling too
+    buf = torch.full((B, 2 * D), 7.0, device="cuda")
+    out = ops.norm_pool(H, aux=M, mode=ops.POOL_MEAN, normalize=False, out=buf[:, :D], **kw)
+    assert max_abs(host(out), O.pool(normed, mask, "mean", normalize=False)) < 2e-3
+    assert np.all(host(buf[:, D:]) == 7.0)
+    ops.device_status()
