@@ -304,23 +304,27 @@ int svodb_norm_pool(const svodb_tensor* hidden, const svodb_tensor* norm_w, cons
 int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,
                      svodb_tensor* sin, void* stream);
 
-/* ---- native model runner ------------------------------------------------------
- * The Qwen3 embedding stack driven from compiled code, for hosts without a
- * Python layer: what `Qwen3Model` + `HeadPlans` do in the reference
- * (model/src/qwen3/{model,decoder_layer,attention,feed_forward}.rs;
- * model/src/encoder_head.rs:384-500). A model borrows the caller's device
- * weights; a plan owns one arena of activations, the RoPE tables and one captured
+/* ---- native model runners ------------------------------------------------------
+ * The three encoder stacks driven from compiled code, for hosts without a Python
+ * layer: what the model structs + `HeadPlans` do in the reference
+ * (model/src/{qwen3,xlm_roberta,modernbert}/...; model/src/encoder_head.rs:384-500).
+ * A model borrows the caller's device weights (dense row-major, all of one 16-bit
+ * dtype); a plan owns one arena of activations, the RoPE tables and one captured
  * CUDA graph for a `(rows, len)` shape on its own stream. */
+typedef struct svodb_model svodb_model;
+typedef struct svodb_plan svodb_plan;
+
+/* Qwen3 embedding decoder (model/src/qwen3/config.rs:62-81). */
 typedef struct svodb_qwen3_config {
   int32_t vocab, hidden, layers, heads, kv_heads, head_dim, ffn;
-  int32_t dtype;    /* SVODB_BF16 / SVODB_F16 / SVODB_F32 of every weight */
+  int32_t dtype;    /* SVODB_BF16 / SVODB_F16 of every weight */
   double eps;       /* RMSNorm epsilon */
   double rope_theta;
 } svodb_qwen3_config;
 
-/* Device pointers, dense row-major: in_w [hidden], qkv_w [(heads+2*kv_heads)*head_dim, hidden],
- * qn_w, kn_w [head_dim], o_w [hidden, heads*head_dim], post_w [hidden],
- * gu_w [2*ffn, hidden] (gate rows first), down_w [hidden, ffn]. */
+/* in_w [hidden], qkv_w [(heads+2*kv_heads)*head_dim, hidden], qn_w, kn_w [head_dim],
+ * o_w [hidden, heads*head_dim], post_w [hidden], gu_w [2*ffn, hidden] (gate rows
+ * first), down_w [hidden, ffn]. */
 typedef struct svodb_qwen3_layer {
   const void *in_w, *qkv_w, *qn_w, *kn_w, *o_w, *post_w, *gu_w, *down_w;
 } svodb_qwen3_layer;
@@ -331,22 +335,69 @@ typedef struct svodb_qwen3_weights {
   const void* norm_w;              /* [hidden] */
 } svodb_qwen3_weights;
 
-typedef struct svodb_qwen3 svodb_qwen3;
-typedef struct svodb_plan svodb_plan;
+/* XLM-RoBERTa / BGE-M3 encoder (model/src/xlm_roberta/config.rs:119-136). */
+typedef struct svodb_xlmr_config {
+  int32_t vocab, hidden, layers, heads, ffn, max_positions;
+  int32_t pad_id;   /* position ids count the tokens that differ from it */
+  int32_t dtype;
+  int32_t pooling;  /* 0 = CLS, 1 = masked mean */
+  double eps;       /* LayerNorm epsilon */
+} svodb_xlmr_config;
 
-int svodb_qwen3_create(const svodb_qwen3_config* cfg, const svodb_qwen3_weights* weights, svodb_qwen3** out);
-void svodb_qwen3_free(svodb_qwen3* model);
+/* qkv_w [3*hidden, hidden] = the reference's q, k, v weights stacked (rows q, then
+ * k, then v), qkv_b [3*hidden] likewise; o_w [hidden, hidden]; fi_w [ffn, hidden];
+ * fo_w [hidden, ffn]; biases and LayerNorm weights [hidden] ([ffn] for fi_b). */
+typedef struct svodb_xlmr_layer {
+  const void *qkv_w, *qkv_b, *o_w, *o_b, *ln1_w, *ln1_b, *fi_w, *fi_b, *fo_w, *fo_b, *ln2_w, *ln2_b;
+} svodb_xlmr_layer;
+
+typedef struct svodb_xlmr_weights {
+  const void *word, *pos, *type;   /* [vocab, hidden], [max_positions, hidden], [hidden] (type row 0) */
+  const void *emb_ln_w, *emb_ln_b; /* [hidden] */
+  const svodb_xlmr_layer* layers;  /* [cfg.layers] */
+} svodb_xlmr_weights;
+
+/* ModernBERT encoder (model/src/modernbert/config.rs:72-92). */
+typedef struct svodb_modernbert_config {
+  int32_t vocab, hidden, layers, heads, ffn;
+  int32_t global_every;  /* layer l attends globally when l % global_every == 0 */
+  int32_t local_window;  /* total width of the local layers' window (half to each side) */
+  int32_t dtype;
+  int32_t pooling;       /* 0 = CLS, 1 = masked mean */
+  double eps, global_theta, local_theta;
+} svodb_modernbert_config;
+
+/* attn_ln_w [hidden] or NULL (layer 0 has none), qkv_w [3*hidden, hidden],
+ * o_w [hidden, hidden], mlp_ln_w [hidden], wi_w [2*ffn, hidden] (gate rows first),
+ * wo_w [hidden, ffn]. */
+typedef struct svodb_modernbert_layer {
+  const void *attn_ln_w, *qkv_w, *o_w, *mlp_ln_w, *wi_w, *wo_w;
+} svodb_modernbert_layer;
+
+typedef struct svodb_modernbert_weights {
+  const void *embed, *emb_ln_w;         /* [vocab, hidden], [hidden] */
+  const svodb_modernbert_layer* layers; /* [cfg.layers] */
+  const void* final_ln_w;               /* [hidden] */
+} svodb_modernbert_weights;
+
+int svodb_qwen3_create(const svodb_qwen3_config* cfg, const svodb_qwen3_weights* weights, svodb_model** out);
+int svodb_xlmr_create(const svodb_xlmr_config* cfg, const svodb_xlmr_weights* weights, svodb_model** out);
+int svodb_modernbert_create(const svodb_modernbert_config* cfg, const svodb_modernbert_weights* weights,
+                            svodb_model** out);
+void svodb_model_free(svodb_model* model);
 /* Prepares the plan of one shape: allocates, runs once eagerly, captures.
- * reference_ops != 0 keeps the reference's op sequence (projection, heads
- * kernel, attention) instead of the prologue fused into the projection's store. */
-int svodb_qwen3_plan(svodb_qwen3* model, int64_t rows, int64_t len, int32_t reference_ops, svodb_plan** out);
-/* One batch: ids [rows, len] i32 and lengths [rows] i32 from host memory (NULL =
- * keep what the plan holds), graph replay, pooled unit-norm rows [rows, hidden]
- * f32 to host memory (NULL = leave them on the device and do not wait). With
- * host_out the call waits for the replay and returns SVODB_ERR_TIMEOUT if a
- * bounded device-side wait ran out during it; without, call
- * `svodb_device_status(svodb_plan_stream(plan))` before trusting the rows. */
-int svodb_plan_run(svodb_plan* plan, const int32_t* host_ids, const int32_t* host_lengths, float* host_out);
+ * reference_ops != 0 (Qwen3 only) keeps the reference's op sequence (projection,
+ * heads kernel, attention) instead of the prologue fused into the projection's store. */
+int svodb_model_plan(svodb_model* model, int64_t rows, int64_t len, int32_t reference_ops, svodb_plan** out);
+/* One batch from host memory: ids [rows, len] i32 and `host_aux` = lengths [rows]
+ * i32 (Qwen3) or the padding mask [rows, len] bytes, nonzero = real token (XLM-R,
+ * ModernBERT); NULL keeps what the plan holds. Graph replay, then the pooled
+ * unit-norm rows [rows, hidden] f32 to host memory (NULL = leave them on the
+ * device and do not wait). With host_out the call waits for the replay and
+ * returns SVODB_ERR_TIMEOUT if a bounded device-side wait ran out during it;
+ * without, call `svodb_device_status(svodb_plan_stream(plan))` before trusting
+ * the rows. */
+int svodb_plan_run(svodb_plan* plan, const int32_t* host_ids, const void* host_aux, float* host_out);
 void* svodb_plan_stream(svodb_plan* plan);   /* the plan's CUstream */
 float* svodb_plan_output(svodb_plan* plan);  /* device [rows, hidden] f32 */
 void svodb_plan_free(svodb_plan* plan);

@@ -111,6 +111,37 @@ class Qwen3Weights(C.Structure):
     _fields_ = [("embed", C.c_void_p), ("layers", C.POINTER(Qwen3Layer)), ("norm_w", C.c_void_p)]
 
 
+class XlmrConfig(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("hidden", C.c_int32), ("layers", C.c_int32), ("heads", C.c_int32),
+                ("ffn", C.c_int32), ("max_positions", C.c_int32), ("pad_id", C.c_int32), ("dtype", C.c_int32),
+                ("pooling", C.c_int32), ("eps", C.c_double)]
+
+
+class XlmrLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("qkv_w", "qkv_b", "o_w", "o_b", "ln1_w", "ln1_b", "fi_w", "fi_b", "fo_w",
+                                          "fo_b", "ln2_w", "ln2_b")]
+
+
+class XlmrWeights(C.Structure):
+    _fields_ = [("word", C.c_void_p), ("pos", C.c_void_p), ("type", C.c_void_p), ("emb_ln_w", C.c_void_p),
+                ("emb_ln_b", C.c_void_p), ("layers", C.POINTER(XlmrLayer))]
+
+
+class ModernBertConfig(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("hidden", C.c_int32), ("layers", C.c_int32), ("heads", C.c_int32),
+                ("ffn", C.c_int32), ("global_every", C.c_int32), ("local_window", C.c_int32), ("dtype", C.c_int32),
+                ("pooling", C.c_int32), ("eps", C.c_double), ("global_theta", C.c_double), ("local_theta", C.c_double)]
+
+
+class ModernBertLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_ln_w", "qkv_w", "o_w", "mlp_ln_w", "wi_w", "wo_w")]
+
+
+class ModernBertWeights(C.Structure):
+    _fields_ = [("embed", C.c_void_p), ("emb_ln_w", C.c_void_p), ("layers", C.POINTER(ModernBertLayer)),
+                ("final_ln_w", C.c_void_p)]
+
+
 class AbiParam(C.Structure):
     _fields_ = [("slot", C.c_int32), ("kind", C.c_int32)]
 
@@ -130,8 +161,11 @@ SYMBOLS = [
     ("svodb_selftest_latch_error", C.c_int, [C.c_int32]),
     ("svodb_selftest_clear_latch", None, []),
     ("svodb_qwen3_create", C.c_int, [C.POINTER(Qwen3Config), C.POINTER(Qwen3Weights), C.POINTER(C.c_void_p)]),
-    ("svodb_qwen3_free", None, [C.c_void_p]),
-    ("svodb_qwen3_plan", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
+    ("svodb_xlmr_create", C.c_int, [C.POINTER(XlmrConfig), C.POINTER(XlmrWeights), C.POINTER(C.c_void_p)]),
+    ("svodb_modernbert_create", C.c_int,
+     [C.POINTER(ModernBertConfig), C.POINTER(ModernBertWeights), C.POINTER(C.c_void_p)]),
+    ("svodb_model_free", None, [C.c_void_p]),
+    ("svodb_model_plan", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
     ("svodb_plan_run", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     ("svodb_plan_stream", C.c_void_p, [C.c_void_p]),
     ("svodb_plan_output", C.c_void_p, [C.c_void_p]),

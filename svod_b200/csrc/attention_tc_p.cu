@@ -42,45 +42,6 @@ namespace {
 
 using namespace fa_parts;
 
-#ifndef FA_POLY
-#define FA_POLY 0
-#endif
-#ifndef FA_SPLIT_ST
-#define FA_SPLIT_ST 0
-#endif
-#ifdef FA_TRACE
-__device__ unsigned int g_fa_trace[2 * 64 * 8];
-#define FTRACE(ev)                                                                                       \
-  do {                                                                                                   \
-    if (trace_on && n < 64) g_fa_trace[((i * 64) + n) * 8 + (ev)] = (unsigned int)clock();               \
-  } while (0)
-#else
-#define FTRACE(ev) \
-  do {             \
-  } while (0)
-#endif
-
-// 2^x of a pair on the FMA pipe: round-to-nearest split by a magic-number add,
-// a degree-3 minimax polynomial of the fraction in [-0.5, 0.5] (relative error
-// 7.5e-5, far inside the rounding of the 16-bit probabilities), and the integer
-// part added into the exponent field. Inputs below -126 return 2^-126.
-__device__ __forceinline__ float2 ex2_fma2(float2 x) {
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 magic = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23
-  const float2 r = __fadd2_rn(x, magic);                       // low mantissa bits: round(x)
-  const float2 nn = __fadd2_rn(r, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(nn, make_float2(-1.0f, -1.0f), x);
-  float2 pl = __ffma2_rn(f, make_float2(0.05517016723752022f, 0.05517016723752022f),
-                         make_float2(0.24260878562927246f, 0.24260878562927246f));
-  pl = __ffma2_rn(pl, f, make_float2(0.6932610273361206f, 0.6932610273361206f));
-  pl = __ffma2_rn(pl, f, make_float2(0.9999282360076904f, 0.9999282360076904f));
-  float2 out;
-  out.x = __uint_as_float(__float_as_uint(pl.x) + (__float_as_uint(r.x) << 23));
-  out.y = __uint_as_float(__float_as_uint(pl.y) + (__float_as_uint(r.y) << 23));
-  return out;
-}
-
 // Queue heads: items handed out so far by a running launch, one per (device,
 // stream) pair, zeroed on the stream just before each launch.
 constexpr int kQueueSlots = 256;
@@ -471,9 +432,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     uint32_t my_blocks = 0;   // blocks of this tile in all earlier items
     uint32_t tail_count = 0;  // tail commits of this tile in all earlier items
     MaskRow mrow{-1, 0, 0};
-#ifdef FA_TRACE
-    bool trace_on = false;
-#endif
     // A warp whose bounded wait ran out stops computing but keeps walking the
     // queue and the hand-over sequence of every later item (`ok` stays false):
     // its partner on the named barriers, which sees the same items, is never
@@ -488,9 +446,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       if (!it.valid) break;
       mrow.len = it.mask_len, mrow.general = it.mask_general;
       const Work w = plan(it, mrow);
-#ifdef FA_TRACE
-      trace_on = blockIdx.x == 5 && n_it == 2 && quarter == 0 && lane == 0;
-#endif
       if (!ok) {
         const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
         for (int m = 0; m < pairs; ++m) {
@@ -557,7 +512,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           tmem_ld32(s_tmem, sr[0]);
           tmem_ld32(s_tmem + 32, sr[1]);
         }
-        FTRACE(0);
         const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
         bool need_mask = j1 >= w.ctx.len || p.has_chunk || w.ctx.general_mask;
         if (p.causal && j1 > i_first) need_mask = true;
@@ -565,7 +519,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
         tmem_ld_wait_for(sr[0]);
         tmem_ld_wait_for(sr[1]);
-        FTRACE(1);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
@@ -631,86 +584,37 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         }
         m_run = m_new;
         float m_use = m_run == -INFINITY ? 0.f : m_run;
-        FTRACE(2);
-        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-        uint32_t pk[32];
-        // Pairs kMufuPairs .. 31 of the block take their exponentials from the FMA
-        // pipe, before this warp's turn on the MUFU unit (whose throughput the
-        // partner warp is using meanwhile); blocks a mask edge crosses keep every
-        // exponential on the MUFU unit, where a hidden score gives an exact zero.
-        constexpr int kPolyPairs = FA_POLY / 2;
-        const bool use_poly = kPolyPairs > 0 && !need_mask;
-        const int mufu_pairs = use_poly ? 32 - kPolyPairs : 32;
-        if (use_poly) {
-          const float2 sl2_p = make_float2(sl2, sl2), nm_p = make_float2(-m_use, -m_use);
-#pragma unroll
-          for (int k = 32 - kPolyPairs; k < 32; ++k) {
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
-                                                    __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
-                                        sl2_p, nm_p);
-            const float2 e = ex2_fma2(x);
-            if (k & 1) lb = __fadd2_rn(lb, e);
-            else la = __fadd2_rn(la, e);
-            pk[k] = Elem<T>::pack(e.x, e.y);
-          }
-#pragma unroll
-          for (int k = 32 - kPolyPairs; k < 32; ++k) asm volatile("" : "+r"(pk[k]));  // done before the turn
-        }
-        FTRACE(3);
         if (n < n_paired && (i == 1 || n > 0)) {
           named_barrier(my_turn, 64);
           asm volatile("" : "+f"(m_use));
         }
-        FTRACE(4);
         const float2 sl2_2 = make_float2(sl2, sl2), nm_2 = make_float2(-m_use, -m_use);
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+        uint32_t pk[32];
         constexpr int kLag = 6;
         float2 xs[32];
-        if (use_poly) {
-          constexpr int kM = 32 - kPolyPairs;
 #pragma unroll
-          for (int k = 0; k < kM; ++k)
-            xs[k] = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
-                                           __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
-                               sl2_2, nm_2);
+        for (int k = 0; k < 32; ++k)
+          xs[k] = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
+                                         __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
+                             sl2_2, nm_2);
 #pragma unroll
-          for (int k = 0; k < kM + kLag; ++k) {
-            if (k < kM) {
-              xs[k].x = ex2_approx(xs[k].x);
-              xs[k].y = ex2_approx(xs[k].y);
-            }
-            if (k >= kLag) {
-              const int d = k - kLag;
-              if (d & 1) lb = __fadd2_rn(lb, xs[d]);
-              else la = __fadd2_rn(la, xs[d]);
-              pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
-            }
+        for (int k = 0; k < 32 + kLag; ++k) {
+          if (k < 32) {
+            xs[k].x = ex2_approx(xs[k].x);
+            xs[k].y = ex2_approx(xs[k].y);
           }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k)
-            xs[k] = __ffma2_rn(make_float2(__uint_as_float(sr[k >> 4][2 * (k & 15)]),
-                                           __uint_as_float(sr[k >> 4][2 * (k & 15) + 1])),
-                               sl2_2, nm_2);
-#pragma unroll
-          for (int k = 0; k < 32 + kLag; ++k) {
-            if (k < 32) {
-              xs[k].x = ex2_approx(xs[k].x);
-              xs[k].y = ex2_approx(xs[k].y);
-            }
-            if (k >= kLag) {
-              const int d = k - kLag;
-              if (d & 1) lb = __fadd2_rn(lb, xs[d]);
-              else la = __fadd2_rn(la, xs[d]);
-              pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
-            }
+          if (k >= kLag) {
+            const int d = k - kLag;
+            if (d & 1) lb = __fadd2_rn(lb, xs[d]);
+            else la = __fadd2_rn(la, xs[d]);
+            pk[d] = Elem<T>::pack(xs[d].x, xs[d].y);
           }
         }
-        (void)mufu_pairs;
         tmem_st32(s_tmem, pk);
         if (n < n_paired && (i == 0 || n + 1 < n_paired)) named_barrier_arrive(other_turn, 64);
         turns_done = n + 1;
         l_run += (la.x + la.y) + (lb.x + lb.y);
-        FTRACE(5);
         requested = false;
         if (n + 1 < nblk) {
           const uint32_t Nn = N + 1;
@@ -723,7 +627,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           }
         }
         tmem_st_wait();
-        FTRACE(6);
         // the first of the tile's two tail commits is observed before the last P
         // (which lets the second happen) is published
         if (n + 1 == nblk && nblk >= 2 && !tail0_seen && !mbar_wait(&tail_done[i], tail_count & 1, p.status)) {
@@ -733,7 +636,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
-        FTRACE(7);
       }
       if (!ok) {
         for (int m = turns_done; m < n_paired; ++m) {
@@ -905,14 +807,6 @@ bool attention_tc_p_covers(const AttnArgs& a) {
   const int64_t items = n_qt * a.heads * a.batch;
   return items > 148 && items < 0x7fffffffLL;
 }
-
-#ifdef FA_TRACE
-}  // namespace svodb
-extern "C" int svodb_debug_read_fa_trace(unsigned int* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, svodb::g_fa_trace, sizeof(unsigned int) * n);
-}
-namespace svodb {
-#endif
 
 int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!attention_tc_p_covers(a)) return 1;

@@ -225,3 +225,35 @@ def test_native_runner_equals_the_python_stack(reference_ops):
     with pytest.raises(ops.OpsError):
         NativeQwen3(m).plan(0, 16)
     runner.close()
+
+
+def test_native_xlm_roberta_and_modernbert_runners_equal_the_python_stacks():
+    """`svodb_xlmr_create` / `svodb_modernbert_create` + `svodb_model_plan` / `svodb_plan_run`: the same
+    ops in the same order issued from compiled code under one captured graph give the same bits as the
+    Python stacks, for host ids and padding masks changed between replays."""
+    from svod_b200.native import NativeModernBert, NativeXlmRoberta
+    rng = np.random.default_rng(12)
+    B, L = 3, 256
+    xc = E.XlmRobertaConfig(vocab_size=600, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                            intermediate_size=512, max_position_embeddings=L + 2)
+    mc = E.ModernBertConfig(vocab_size=600, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                            intermediate_size=384)
+    for model, Runner in ((E.XlmRobertaEncoder.random_init(xc, seed=5), NativeXlmRoberta),
+                          (E.ModernBertEncoder.random_init(mc, seed=6), NativeModernBert)):
+        for lp in model.p["layers"]:  # non-trivial norm weights
+            for name, t in lp.items():
+                if t is not None and t.dim() == 1 and name.endswith("_w"):
+                    t.add_(torch.randn_like(t) * 0.05)
+        runner = Runner(model)
+        for trial in range(2):
+            lens = np.array([L, 40 + trial, 199])
+            mask = np.arange(L)[None, :] < lens[:, None]
+            ids = rng.integers(2, 600, (B, L)).astype(np.int32)
+            ids[~mask] = 1
+            got = runner.run(ids, mask)
+            want = model.forward(torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()).cpu().numpy()
+            assert got.shape == want.shape and np.array_equal(got, want), type(model).__name__
+            assert np.allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-5)
+        runner.replay(B, L)
+        ops.device_status()
+        runner.close()
