@@ -44,6 +44,7 @@ struct FaParams {
   const int32_t* row_map;  // `ops::Cache`: cache row of batch lane b, or null
   float* lse;
   int n_qt;  // query tile pairs per (head, batch)
+  int d_real;  // the tensors' head dim (a multiple of 8, <= D): columns past it are TMA zero fill and never stored
   uint32_t* status;
 };
 

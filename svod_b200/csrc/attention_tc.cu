@@ -41,7 +41,8 @@
 //
 // Every mbarrier wait is bounded; a timeout records a status code and the CTA
 // drains and frees its TMEM. Named barriers have no timeout, so a warp that
-// gave up still walks the rest of its hand-over sequence.
+// gave up never waits on one again: it only arrives, once per remaining turn of
+// its partner, which is thereby released whether or not it gave up too.
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
@@ -539,7 +540,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     }
     if (!ok) {
       for (int m = turns_done; m < n_paired; ++m) {
-        if (i == 1 || m > 0) named_barrier(my_turn, 64);
+        // arrivals only: the partner is released at each of its remaining turns and
+        // this warp never waits on a barrier without a limit again
         if (i == 0 || m + 1 < n_paired) named_barrier_arrive(other_turn, 64);
       }
     }
@@ -570,7 +572,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       }
     } else if (row_ok && ok) {
       // No key block reaches this tile: zeros (attention.rs:971-980).
-      for (int c = 0; c < D; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
+      for (int c = 0; c < p.d_real; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
     }
     if (p.lse != nullptr && row_ok && ok)
       p.lse[(b * p.heads + h) * p.t + row] = l_run == 0.f ? -INFINITY : kLn2F * (m_run + log2f(l_run));
@@ -595,12 +597,12 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   const uint32_t box[4] = {64, 1, 128, 1};     // Q tile rows
   const uint32_t kvbox[4] = {64, 1, kBKV, 1};  // K/V block rows
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
+    const uint64_t dims[4] = {(uint64_t)a.d, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
     const uint64_t st[3] = {(uint64_t)a.q_sh, (uint64_t)a.q_st, (uint64_t)a.q_sb};
     if (!make_tmap(&tq, a.q, a.dtype, 4, dims, st, box)) return -1;
   }
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
+    const uint64_t dims[4] = {(uint64_t)a.d, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
     const uint64_t stk[3] = {(uint64_t)a.k_sh, (uint64_t)a.k_st, (uint64_t)a.k_sb};
     const uint64_t stv[3] = {(uint64_t)a.v_sh, (uint64_t)a.v_st, (uint64_t)a.v_sb};
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
@@ -635,11 +637,12 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.row_map = a.row_map;
   p.lse = a.lse;
   p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
+  p.d_real = a.d;
   p.status = a.status;
   dim3 grid((unsigned)p.n_qt, (unsigned)a.heads, (unsigned)a.batch);
   attention_tc_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p);
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1}", 2 * kBQ, kBKV, D, C::kStages);
+    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1}", 2 * kBQ, kBKV, a.d, C::kStages);
   return 0;
 }
 
@@ -647,11 +650,14 @@ int run(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
 
 bool attention_tc_covers(const AttnArgs& a) {
   // The reference's kernel gate (tk/src/ops/shape.rs:92-99,189-206): one 16-bit
-  // dtype. This kernel tiles head dims 64 and 128, takes no additive bias and no
-  // key splits (the exact kernel serves those), and needs a positive scale
-  // because the running maximum is kept in raw-score units.
+  // dtype. This kernel tiles head dims 64 and 128; every other multiple of 8 up
+  // to 128 (the reference plans 32, 48, 64, 128: website/docs/tile-kernels/op-layer.md)
+  // runs on the next of the two with the missing columns zero-filled by the TMA
+  // loads and never stored. It takes no additive bias and no key splits (the
+  // exact kernel serves those), and needs a positive scale because the running
+  // maximum is kept in raw-score units.
   if (a.dtype != SVODB_BF16 && a.dtype != SVODB_F16) return false;
-  if (a.d != 64 && a.d != 128) return false;
+  if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return false;
   if (a.bias != nullptr || a.splits > 1 || a.n_app > 0) return false;
   if (!(a.scale > 0.f)) return false;
   if (a.batch <= 0 || a.t <= 0 || a.tk <= 0 || a.batch > 65535 || a.heads > 65535) return false;
@@ -669,8 +675,8 @@ bool attention_tc_covers(const AttnArgs& a) {
 int launch_attention_tc(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!attention_tc_covers(a)) return 1;
   if (a.dtype == SVODB_BF16)
-    return a.d == 128 ? run<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
-  return a.d == 128 ? run<__half, 128>(a, s, cfg, cfg_len) : run<__half, 64>(a, s, cfg, cfg_len);
+    return a.d > 64 ? run<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
+  return a.d > 64 ? run<__half, 128>(a, s, cfg, cfg_len) : run<__half, 64>(a, s, cfg, cfg_len);
 }
 
 }  // namespace svodb

@@ -433,13 +433,25 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     uint32_t tail_count = 0;  // tail commits of this tile in all earlier items
     MaskRow mrow{-1, 0, 0};
     // A warp whose bounded wait ran out stops computing but keeps walking the
-    // queue and the hand-over sequence of every later item (`ok` stays false):
-    // its partner on the named barriers, which sees the same items, is never
-    // left waiting. Both leave when the queue ends or stops being fed.
+    // queue and, for every later item, arrives on its partner's barrier at each
+    // turn the partner may take (`ok` stays false): the partner, which sees the
+    // same items, is never left waiting, and the warp that gave up never waits
+    // on a named barrier (they have no limit) again. Both leave when the queue
+    // ends or stops being fed.
     bool ok = true;
     for (uint32_t n_it = 0;; ++n_it) {
       const int slot = (int)(n_it & 1);
-      if (!mbar_wait(&item_full[slot], (n_it >> 1) & 1, p.status)) break;
+      // Both warps of a MUFU pair must take the same items: this wait ignores a
+      // status word that is already set (it would let one partner leave while the
+      // other still receives the item and then waits on a named barrier for good)
+      // and ends only with the item or with its own limit, which both reach together.
+      if (!mbar_wait_patient(&item_full[slot], (n_it >> 1) & 1, p.status)) {
+        // No item within the limit: the queue is dead. Should the partner have
+        // caught an item in the instant between the two limits (the loader can be
+        // at most two items ahead), it is released through every turn it may take.
+        for (int64_t m = 0; m < 2 * (p.tk / kBKV + 2); ++m) named_barrier_arrive(other_turn, 64);
+        break;
+      }
       const Item it = item_ring[slot];
       __syncwarp();
       if (lane == 0) mbar_arrive(&item_empty[slot]);
@@ -448,10 +460,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       const Work w = plan(it, mrow);
       if (!ok) {
         const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
-        for (int m = 0; m < pairs; ++m) {
-          if (i == 1 || m > 0) named_barrier(my_turn, 64);
+        // arrivals only: a partner still computing is released at each of its
+        // turns, and this warp never waits on a barrier without a limit again
+        for (int m = 0; m < pairs; ++m)
           if (i == 0 || m + 1 < pairs) named_barrier_arrive(other_turn, 64);
-        }
         continue;
       }
       const Range r = i == 0 ? w.r0 : w.r1;
@@ -638,10 +650,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         if (lane == 0) mbar_arrive(&p_full[i * 2 + buf]);
       }
       if (!ok) {
-        for (int m = turns_done; m < n_paired; ++m) {
-          if (i == 1 || m > 0) named_barrier(my_turn, 64);
+        for (int m = turns_done; m < n_paired; ++m)
           if (i == 0 || m + 1 < n_paired) named_barrier_arrive(other_turn, 64);
-        }
         continue;
       }
       // ---- epilogue: O / l ----
@@ -663,6 +673,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (row_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
+              if (c + v * 8 >= p.d_real) break;  // padded head dim: nothing past the real columns
               uint32_t wv[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e)
@@ -680,7 +691,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         tail_count += nblk >= 2 ? 2u : 1u;
       } else if (row_ok) {
         // No key block reaches this tile: zeros (attention.rs:971-980).
-        for (int c = 0; c < D; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
+        for (int c = 0; c < p.d_real; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
       }
       if (p.lse != nullptr && row_ok)
         p.lse[(b * p.heads + h) * p.t + row] = l_run == 0.f ? -INFINITY : kLn2F * (m_run + log2f(l_run));
@@ -732,12 +743,12 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   const uint32_t box[4] = {64, 1, 128, 1};
   const uint32_t kvbox[4] = {64, 1, kBKV, 1};
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
+    const uint64_t dims[4] = {(uint64_t)a.d, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
     const uint64_t st[3] = {(uint64_t)a.q_sh, (uint64_t)a.q_st, (uint64_t)a.q_sb};
     if (!make_tmap(&tq, a.q, a.dtype, 4, dims, st, box)) return -1;
   }
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
+    const uint64_t dims[4] = {(uint64_t)a.d, (uint64_t)a.kv_heads, (uint64_t)a.tk, (uint64_t)a.kv_rows};
     const uint64_t stk[3] = {(uint64_t)a.k_sh, (uint64_t)a.k_st, (uint64_t)a.k_sb};
     const uint64_t stv[3] = {(uint64_t)a.v_sh, (uint64_t)a.v_st, (uint64_t)a.v_sb};
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
@@ -774,6 +785,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.row_map = a.row_map;
   p.lse = a.lse;
   p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
+  p.d_real = a.d;
   p.status = a.status;
   const int64_t items = (int64_t)p.n_qt * a.heads * a.batch;
   int sms = 0, dev = 0;
@@ -793,7 +805,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
   attention_tc_p_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, tail_groups, head);
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1,persistent:%d}", 2 * kBQ, kBKV, D, C::kStages, grid);
+    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages, grid);
   return 0;
 }
 
@@ -811,8 +823,8 @@ bool attention_tc_p_covers(const AttnArgs& a) {
 int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!attention_tc_p_covers(a)) return 1;
   if (a.dtype == SVODB_BF16)
-    return a.d == 128 ? run_p<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run_p<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
-  return a.d == 128 ? run_p<__half, 128>(a, s, cfg, cfg_len) : run_p<__half, 64>(a, s, cfg, cfg_len);
+    return a.d > 64 ? run_p<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run_p<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
+  return a.d > 64 ? run_p<__half, 128>(a, s, cfg, cfg_len) : run_p<__half, 64>(a, s, cfg, cfg_len);
 }
 
 }  // namespace svodb

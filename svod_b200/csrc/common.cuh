@@ -196,6 +196,17 @@ __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, ui
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status) {
   return mbar_wait_for(bar, parity, status, kWaitLimit);
 }
+// The same wait without the early exit on a status word that is already set: it
+// gives up only when its own limit runs out. For waits whose outcome two warps
+// must agree on (both poll one barrier phase and then pair up on named
+// barriers): a word left set by an earlier launch, or set by another role a
+// moment ago, must not make one of them leave while the other goes on.
+__device__ __forceinline__ bool mbar_wait_patient(uint64_t* bar, uint32_t parity, uint32_t* status) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicExch(status, (uint32_t)kStatusWaitTimeout);
+  return false;
+}
 
 // ---- TMA (non-multicast only) ----------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

@@ -92,6 +92,12 @@ KERNEL_CASES = [
     ("wide core, d 128", 200, 300, 128, {}),
     ("wide core, d 64, bq 256", 300, 300, 64, {}),
     ("odd keys", 99, 99, 64, dict(lens=[99, 41])),
+    # head dims between the two tiled ones run zero-padded on the next (the reference plans 32 and 48 too:
+    # tk/src/test/unit/attention.rs:349-455 has d 48)
+    ("d 48, causal segments", 96, 96, 48, dict(causal=True, seg="seg")),
+    ("d 32, key lengths", 128, 192, 32, dict(lens=[192, 77])),
+    ("d 96, ragged, key mask", 200, 130, 96, dict(mask="km")),
+    ("d 48, a lane with no keys", 100, 100, 48, dict(lens=[100, 0])),
 ]
 
 
@@ -191,7 +197,7 @@ def test_config_1_f32_attention_with_key_lengths_output_and_logsumexp():
 
 
 GENERIC_CASES = [
-    ("d 48", 2, 96, 96, 2, 2, 48, O.BF16, dict(causal=True, seg=40)),
+    ("d 40 (rows off the 16-byte grid)", 2, 96, 96, 2, 2, 40 + 4, O.BF16, dict(causal=True, seg=40)),
     ("bias per batch", 2, 128, 128, 2, 2, 64, O.BF16, dict(bias=(2, 2, 128, 128))),
     ("shared bias, ragged", 2, 100, 130, 2, 2, 64, O.BF16, dict(bias=(1, 2, 100, 130))),
     ("bias with key lengths", 2, 99, 99, 2, 2, 64, O.BF16, dict(bias=(2, 2, 99, 99), lens=[99, 41])),
