@@ -88,7 +88,8 @@ const char* svodb_last_chosen(void);
  * none did). `svodb_config_set(key, bn)`: later calls with that key use tile
  * width bn (64, 128 or 256 on one CTA, 512 = the CTA-pair kernel; a choice the
  * shape or epilogue cannot take is ignored); bn = 0 forgets the key. The key
- * "attention|one_item" (value 1) keeps attention on the one-item-per-CTA kernel.
+ * "attention|one_item" (value 1) keeps attention on the one-item-per-CTA kernel,
+ * "attention|exact" (value 1) on the exact CUDA-core kernel (for A/B timings).
  * `svodb_config_get` returns 0 when the key is unset. */
 const char* svodb_last_config_key(void);
 int svodb_config_set(const char* key, int32_t value);

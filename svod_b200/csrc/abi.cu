@@ -689,15 +689,28 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
       return fail(SVODB_ERR_GRAPH, "%s: a split attention writes a contiguous output", OP);
   }
   char cfg[128];
-  if (attention_tc_p_covers(a) && config_lookup("attention|one_item") == 0) {
+  auto merge_splits = [&]() {
+    if (a.splits <= 1) return;
+    CombineArgs c{};
+    c.o_part = a.o_part, c.m_part = a.m_part, c.l_part = a.l_part;
+    c.o = o->data;
+    c.rows = B * T * H;
+    c.d = (int)D;
+    c.splits = a.splits;
+    c.dtype = a.dtype;
+    launch_combine(c, s);
+  };
+  const bool exact_only = config_lookup("attention|exact") != 0;
+  if (!exact_only && attention_tc_p_covers(a) && config_lookup("attention|one_item") == 0) {
     int rc = launch_attention_tc_p(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
     if (rc == 0) {
+      merge_splits();
       chose_kernel(OP, packed ? "flash_attention_packed" : "flash_attention", cfg);
       return check_launch(OP);
     }
   }
-  if (attention_tc_covers(a)) {
+  if (!exact_only && attention_tc_covers(a)) {
     int rc = launch_attention_tc(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
     if (rc == 0) {
@@ -709,16 +722,7 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
   const char* why = !is_half(a.dtype) ? "dtype" : "shape";
   int rc = launch_attention_generic(a, s);
   if (rc != 0) return fail(SVODB_ERR_LAUNCH, "%s: kernel attributes were rejected (%d)", OP, rc);
-  if (a.splits > 1) {
-    CombineArgs c{};
-    c.o_part = a.o_part, c.m_part = a.m_part, c.l_part = a.l_part;
-    c.o = o->data;
-    c.rows = B * T * H;
-    c.d = (int)D;
-    c.splits = a.splits;
-    c.dtype = a.dtype;
-    launch_combine(c, s);
-  }
+  merge_splits();
   chose_graph(OP, why);
   return check_launch(OP);
 }

@@ -45,6 +45,20 @@ struct FaParams {
   float* lse;
   int n_qt;  // query tile pairs per (head, batch)
   int d_real;  // the tensors' head dim (a multiple of 8, <= D): columns past it are TMA zero fill and never stored
+  // Key splits (persistent kernel): split s of `splits` takes an equal share of the
+  // key blocks and writes its unnormalised state instead of the output:
+  // o_part [S,B,T,H,d] f32, m_part / l_part [S,B,T,H] (m in scaled log2 units,
+  // -1e30 for a share no key reached: tk/src/kernels/attention.rs:616,910-920).
+  int splits;
+  int64_t batch;
+  float* o_part;
+  float* m_part;
+  float* l_part;
+  // Additive bias [B|1, H, T, Tk] in the stream dtype (persistent kernel), added to
+  // the scaled score before the masks (attention.rs:405-407).
+  const void* bias;
+  int bias_per_batch;
+  float inv_scale;  // 1 / scale: the bias in raw-score units
   uint32_t* status;
 };
 

@@ -560,6 +560,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (row_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
+              if (c + v * 8 >= p.d_real) break;  // padded head dim: nothing past the real columns
               uint32_t w[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e)

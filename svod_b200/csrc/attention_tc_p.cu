@@ -50,6 +50,7 @@ __device__ int g_next_item[kQueueSlots];
 struct Item {
   int qt, h, b, valid;
   int mask_len, mask_general;  // what the loader's scan of a bool key mask row found (see MaskRow)
+  int split;                   // key split of this item (0 without splits)
 };
 
 // Work item w in queue order: batch, KV head, query head of the group, then
@@ -59,9 +60,14 @@ struct Item {
 // tile pair first (heaviest first), then group, then query head. The queue then
 // ends on the lightest items of many groups rather than starting the heaviest
 // items of the last group when everything else is done.
-__device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads, int tail_groups) {
-  Item it{0, 0, 0, 0, 0, 0};
+__device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads, int tail_groups,
+                                            int splits) {
+  Item it{0, 0, 0, 0, 0, 0, 0};
   if (w >= n_items) return it;
+  // the splits of one (tile pair, head, batch) follow one another in the queue
+  it.split = w % splits;
+  w /= splits;
+  n_items /= splits;
   const int group = heads / kv_heads;
   const int per_kv = group * n_qt;
   const int head_groups = n_items / per_kv - tail_groups;
@@ -132,7 +138,9 @@ __device__ __forceinline__ void scan_mask_row(const FaParams& p, int64_t b, int 
   row.general = first_zero < last_set ? 1 : 0;
 }
 
-template <typename T, int D>
+// EXTRAS = key splits and / or an additive bias: a separate instantiation, so that
+// the plain kernel's inner loop carries neither their registers nor their branches.
+template <typename T, int D, bool EXTRAS>
 __global__ void __launch_bounds__(kThreadsFa, 1)
     attention_tc_p_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const int n_items,
@@ -201,7 +209,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
 
   // What every role derives from an item: the key-block ranges of its two tiles.
   struct Work {
-    int h, hk;
+    int h, hk, split;
     int64_t b, i0;
     Ctx ctx;
     Range r0, r1;
@@ -226,6 +234,17 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     }
     w.r0 = tile_range(p, w.ctx, w.b, w.i0);
     w.r1 = tile_range(p, w.ctx, w.b, w.i0 + kBQ);
+    w.split = it.split;
+    if (EXTRAS && p.splits > 1) {
+      // this split's share of the key blocks
+      const int total = (int)((p.tk + kBKV - 1) / kBKV);
+      const int per = (total + p.splits - 1) / p.splits;
+      const int s_lo = it.split * per, s_hi = s_lo + per;
+      w.r0.lo = max(w.r0.lo, s_lo), w.r0.hi = min(w.r0.hi, s_hi);
+      w.r1.lo = max(w.r1.lo, s_lo), w.r1.hi = min(w.r1.hi, s_hi);
+      if (w.r0.hi <= w.r0.lo) w.r0 = Range{0, 0};
+      if (w.r1.hi <= w.r1.lo) w.r1 = Range{0, 0};
+    }
     w.live0 = w.r0.hi > w.r0.lo;
     w.live1 = w.r1.hi > w.r1.lo;
     w.u_lo = 0, w.u_hi = 0;
@@ -258,7 +277,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (lane == 0 && mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) wi = atomicAdd(queue, 1);
           wi = __shfl_sync(0xffffffffu, wi, 0);
           if (wi < 0) break;  // the wait ran out
-          Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups);
+          Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups, EXTRAS ? p.splits : 1);
           // The loader alone scans a bool key mask row (all its lanes, once per change
           // of batch lane, while it runs ahead of the other warps) and hands what it
           // found to them with the item.
@@ -531,6 +550,32 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
         tmem_ld_wait_for(sr[0]);
         tmem_ld_wait_for(sr[1]);
+        if (EXTRAS && p.bias != nullptr && row_ok) {
+          // + bias / scale in raw-score units: (s + bias/scale) * scale = s*scale + bias, before the masks
+          const T* brow = (const T*)p.bias + (((p.bias_per_batch ? b : 0) * p.heads + h) * p.t + row) * p.tk + j0;
+          const bool vec = ((reinterpret_cast<uintptr_t>(brow) & 15) == 0) && j1 < p.tk;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float bv[8];
+            if (vec) {
+              const uint4 u = ldg128(brow + c * 8);
+              const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = Elem<T>::unpack(uu[e]);
+                bv[2 * e] = f.x, bv[2 * e + 1] = f.y;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) bv[e] = j0 + c * 8 + e < p.tk ? Elem<T>::to_f(brow[c * 8 + e]) : 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int k = c * 8 + e;
+              sr[k >> 5][k & 31] = __float_as_uint(fmaf(bv[e], p.inv_scale, __uint_as_float(sr[k >> 5][k & 31])));
+            }
+          }
+        }
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
@@ -654,8 +699,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (i == 0 || m + 1 < n_paired) named_barrier_arrive(other_turn, 64);
         continue;
       }
-      // ---- epilogue: O / l ----
+      // ---- epilogue: O / l, or this split's unnormalised state ----
       T* orow = (T*)p.o + b * p.o_sb + row * p.o_st + (int64_t)h * p.o_sh;
+      const int64_t prow = (((int64_t)w.split * p.batch + b) * p.t + row) * p.heads + h;  // partial-state row
+      float* oprow = EXTRAS && p.splits > 1 ? p.o_part + prow * p.d_real : nullptr;
       if (nblk > 0) {
         // the last P.V: the item's second tail commit (its only one for a one-block tile)
         const uint32_t last = tail_count + (nblk >= 2 ? 1u : 0u);
@@ -670,7 +717,14 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           uint32_t orr[32];
           tmem_ld32(o_tmem + c, orr);
           tmem_ld_wait();
-          if (row_ok) {
+          if (EXTRAS && row_ok && oprow != nullptr) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              if (c + v * 4 >= p.d_real) break;
+              *reinterpret_cast<uint4*>(oprow + c + v * 4) =
+                  make_uint4(orr[v * 4], orr[v * 4 + 1], orr[v * 4 + 2], orr[v * 4 + 3]);
+            }
+          } else if (row_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               if (c + v * 8 >= p.d_real) break;  // padded head dim: nothing past the real columns
@@ -689,9 +743,16 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         if (lane == 0) mbar_arrive(&o_empty[i]);
         my_blocks += (uint32_t)nblk;
         tail_count += nblk >= 2 ? 2u : 1u;
+      } else if (EXTRAS && row_ok && oprow != nullptr) {
+        for (int c = 0; c < p.d_real; c += 4) *reinterpret_cast<uint4*>(oprow + c) = make_uint4(0, 0, 0, 0);
       } else if (row_ok) {
         // No key block reaches this tile: zeros (attention.rs:971-980).
         for (int c = 0; c < p.d_real; c += 8) stg128(orow + c, make_uint4(0, 0, 0, 0));
+      }
+      if (EXTRAS && oprow != nullptr && row_ok) {
+        // an empty share keeps a finite sentinel maximum, so the merge never sees inf - inf
+        p.m_part[prow] = m_run == -INFINITY ? -1e30f : m_run;
+        p.l_part[prow] = l_run;
       }
       if (p.lse != nullptr && row_ok)
         p.lse[(b * p.heads + h) * p.t + row] = l_run == 0.f ? -INFINITY : kLn2F * (m_run + log2f(l_run));
@@ -736,7 +797,7 @@ int* queue_head(cudaStream_t stream) {
   return base[dev] + it->second;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool EXTRAS>
 int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   using C = FaCfg<D>;
   CUtensorMap tq, tk, tv;
@@ -760,7 +821,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   cudaGetDevice(&attr_dev);
   bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attention_tc_p_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attention_tc_p_kernel<T, D, EXTRAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)
       return -1;
     attr_set = true;
@@ -786,8 +847,14 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.lse = a.lse;
   p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
   p.d_real = a.d;
+  p.splits = a.splits > 1 ? a.splits : 1;
+  p.batch = a.batch;
+  p.o_part = a.o_part, p.m_part = a.m_part, p.l_part = a.l_part;
+  p.bias = a.bias;
+  p.bias_per_batch = a.bias_per_batch;
+  p.inv_scale = 1.0f / a.scale;
   p.status = a.status;
-  const int64_t items = (int64_t)p.n_qt * a.heads * a.batch;
+  const int64_t items = (int64_t)p.n_qt * a.heads * a.batch * p.splits;
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -803,28 +870,49 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     tail_groups = (int)(want < groups ? want : groups);
   }
   if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
-  attention_tc_p_kernel<T, D><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, tail_groups, head);
+  attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, tail_groups,
+                                                                               head);
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:1,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages, grid);
+    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages,
+             p.splits, grid);
   return 0;
 }
 
 }  // namespace
 
 // The persistent kernel takes what the one-item kernel takes once there are more
-// items than SMs (otherwise nothing would overlap).
+// items than SMs (otherwise nothing would overlap), and it alone takes key
+// splits and an additive bias, whatever the item count.
 bool attention_tc_p_covers(const AttnArgs& a) {
-  if (!attention_tc_covers(a)) return false;
+  AttnArgs plain = a;
+  plain.splits = 1;
+  plain.bias = nullptr;
+  if (!attention_tc_covers(plain)) return false;
+  const int splits = a.splits > 1 ? a.splits : 1;
   const int64_t n_qt = (a.t + 2 * kBQ - 1) / (2 * kBQ);
-  const int64_t items = n_qt * a.heads * a.batch;
-  return items > 148 && items < 0x7fffffffLL;
+  const int64_t items = n_qt * a.heads * a.batch * splits;
+  if (items >= 0x7fffffffLL) return false;
+  if (a.splits > 1 || a.bias != nullptr) {
+    // partial rows are written 16 bytes at a time; the score rows of the bias are read per thread
+    if (a.splits > 1 && (a.o_part == nullptr || (reinterpret_cast<uintptr_t>(a.o_part) & 15) != 0 || a.d % 4 != 0))
+      return false;
+    return true;
+  }
+  return items > 148;
 }
 
 int launch_attention_tc_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   if (!attention_tc_p_covers(a)) return 1;
-  if (a.dtype == SVODB_BF16)
-    return a.d > 64 ? run_p<__nv_bfloat16, 128>(a, s, cfg, cfg_len) : run_p<__nv_bfloat16, 64>(a, s, cfg, cfg_len);
-  return a.d > 64 ? run_p<__half, 128>(a, s, cfg, cfg_len) : run_p<__half, 64>(a, s, cfg, cfg_len);
+  const bool extras = a.splits > 1 || a.bias != nullptr;
+  if (a.dtype == SVODB_BF16) {
+    if (extras)
+      return a.d > 64 ? run_p<__nv_bfloat16, 128, true>(a, s, cfg, cfg_len)
+                      : run_p<__nv_bfloat16, 64, true>(a, s, cfg, cfg_len);
+    return a.d > 64 ? run_p<__nv_bfloat16, 128, false>(a, s, cfg, cfg_len)
+                    : run_p<__nv_bfloat16, 64, false>(a, s, cfg, cfg_len);
+  }
+  if (extras) return a.d > 64 ? run_p<__half, 128, true>(a, s, cfg, cfg_len) : run_p<__half, 64, true>(a, s, cfg, cfg_len);
+  return a.d > 64 ? run_p<__half, 128, false>(a, s, cfg, cfg_len) : run_p<__half, 64, false>(a, s, cfg, cfg_len);
 }
 
 }  // namespace svodb

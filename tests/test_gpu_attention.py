@@ -196,17 +196,43 @@ def test_config_1_f32_attention_with_key_lengths_output_and_logsumexp():
     assert max_abs(glse, wlse) < 2e-2
 
 
-GENERIC_CASES = [
-    ("d 40 (rows off the 16-byte grid)", 2, 96, 96, 2, 2, 40 + 4, O.BF16, dict(causal=True, seg=40)),
+# Additive bias and key splits run on the persistent tensor-core kernel (partials merged by
+# `combine_splits`); the exact kernel keeps f32, a non-positive scale and rows off the 16-byte grid.
+BIAS_SPLIT_CASES = [
     ("bias per batch", 2, 128, 128, 2, 2, 64, O.BF16, dict(bias=(2, 2, 128, 128))),
     ("shared bias, ragged", 2, 100, 130, 2, 2, 64, O.BF16, dict(bias=(1, 2, 100, 130))),
     ("bias with key lengths", 2, 99, 99, 2, 2, 64, O.BF16, dict(bias=(2, 2, 99, 99), lens=[99, 41])),
+    ("causal bias, d 128, 300 queries", 2, 300, 300, 4, 2, 128, O.BF16, dict(bias=(2, 4, 300, 300), causal=True)),
     ("four splits", 1, 1, 200, 4, 4, 64, O.BF16, dict(lens=[70], splits=4)),
     ("two splits, five queries, d128", 2, 5, 96, 2, 2, 128, O.BF16, dict(lens=[64, 96], splits=2)),
     ("more splits than blocks", 2, 1, 64, 2, 2, 64, O.BF16, dict(lens=[64, 40], splits=4)),
     ("splits, a lane with no keys", 2, 1, 200, 4, 4, 64, O.BF16, dict(lens=[0, 70], splits=4)),
+    ("three splits, causal, 300 queries, gqa", 2, 300, 300, 4, 2, 128, O.BF16, dict(causal=True, splits=3)),
+    ("five splits with a bias, f16", 2, 40, 700, 2, 2, 64, O.F16, dict(bias=(1, 2, 40, 700), splits=5, lens=[700, 333])),
+]
+
+
+@pytest.mark.parametrize("name,B,T,Tk,H,Hkv,D,dt,kw", BIAS_SPLIT_CASES, ids=[c[0] for c in BIAS_SPLIT_CASES])
+def test_bias_and_key_splits_run_on_the_tensor_core_kernel(name, B, T, Tk, H, Hkv, D, dt, kw):
+    kw = dict(kw)
+    q, k, v = recipe(B, T, Tk, H, Hkv, D, dt)
+    if "bias" in kw:
+        kw["bias"] = O.Lcg(99).rounded(dt, int(np.prod(kw["bias"])), lambda x: 2.0 * x).reshape(kw["bias"])
+    got, want = run_case(q, k, v, dt, **kw)
+    ran = min(kw.get("splits", 1), (Tk + 31) // 32)   # a request is capped at the 32-key tile count
+    assert "kernel flash_attention" in ops.chosen() and f"splits:{ran}" in ops.chosen(), ops.chosen()
+    assert max_abs(got, want) < 2e-2
+    if "lens" in kw and 0 in kw["lens"]:
+        assert np.all(got[kw["lens"].index(0)] == 0.0)
+
+
+GENERIC_CASES = [
+    ("d 44 (rows off the 16-byte grid)", 2, 96, 96, 2, 2, 44, O.BF16, dict(causal=True, seg=40)),
     ("negative scale", 2, 128, 128, 2, 2, 64, O.BF16, dict(causal=True, lens=[128, 50], scale=-0.1)),
+    ("negative scale with splits and a bias", 2, 8, 128, 2, 2, 64, O.BF16,
+     dict(lens=[128, 50], scale=-0.1, splits=2, bias=(2, 2, 8, 128))),
     ("f32 causal ragged gqa", 2, 100, 130, 4, 2, 48, O.F32, dict(causal=True)),
+    ("f32 splits", 2, 3, 200, 4, 2, 48, O.F32, dict(lens=[200, 70], splits=4)),
 ]
 
 
