@@ -777,6 +777,34 @@ def sweep(args):
     peaks = measured_peaks()
     g = torch.Generator(device="cuda").manual_seed(2)
     stream = torch.cuda.current_stream()
+    if args.sweep == "decode":
+        # decode-shaped attention: few queries per lane against a long cache, key splits on the
+        # tensor-core kernel against the exact kernel (config key `attention|exact`)
+        from svod_b200 import _lib as L
+        lib = L.load()
+        for (B, T, Tk, H, Hk, D) in [(8, 1, 32768, 16, 8, 128), (8, 16, 32768, 16, 8, 128), (64, 1, 4096, 16, 8, 128)]:
+            q = torch.randn(B, T, H, D, generator=g, device="cuda").to(torch.bfloat16)
+            k = torch.randn(B, Tk, Hk, D, generator=g, device="cuda").to(torch.bfloat16)
+            v = torch.randn(B, Tk, Hk, D, generator=g, device="cuda").to(torch.bfloat16)
+            lens = torch.full((B,), Tk, dtype=torch.int32, device="cuda")
+            kv_bytes = 2 * B * Tk * Hk * D * 2
+            ref = None
+            for splits in (1, 4, 8, 16, 32):
+                row = {}
+                for mode in ("tensor", "exact"):
+                    lib.svodb_config_set(b"attention|exact", 1 if mode == "exact" else 0)
+                    a = ops.Attn(keys=ops.KeyMask.Lens(lens), splits=splits if splits > 1 else None)
+                    out = ops.attention(q, k, v, a)
+                    ch = ops.chosen()
+                    ms = time_graphed(lambda: ops.attention(q, k, v, a), 10)
+                    ref = out.float() if ref is None else ref
+                    row[mode] = {"ms": round(ms, 4), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
+                                 "max_abs_vs_first": float((out.float() - ref).abs().max()),
+                                 "kernel": "flash_attention" if "kernel" in ch else "exact"}
+                lib.svodb_config_set(b"attention|exact", 0)
+                print(json.dumps({"case": f"decode B{B} T{T} Tk{Tk} H{H}/{Hk} D{D}", "splits": splits, **row}), flush=True)
+        ops.device_status()
+        return
     if args.sweep == "attention-f32":
         B, H, T, D = 2, 8, 512, 64
         q, k, v = (torch.randn(B, T, H, D, generator=g, device="cuda") for _ in range(3))
@@ -824,7 +852,7 @@ def main():
     ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "rms_norm", "heads"],
                     help="run a few launches of one kernel on a small case (for profiler captures) and exit")
     ap.add_argument("--case-batch", type=int, default=4)
-    ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32"],
+    ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32", "decode"],
                     help="time the kernel-level baseline configurations (one JSON line per case) and exit")
     args = ap.parse_args()
     if args.kernel_case:
