@@ -582,3 +582,16 @@ def test_persistent_attention_scans_aligned_byte_masks_in_16_byte_pieces(kind):
     finally:
         lib.svodb_config_set(b"attention|one_item", 0)
     assert np.array_equal(got, one)
+
+
+def test_f16_scores_stay_in_f32_on_the_tensor_core_kernel():
+    """tensor/src/test/unit/transformer.rs:170-190 on the GPU: 64 products of
+    100*100 overflow float16; the kernel's f32 accumulator keeps the scores finite
+    and key 0, ahead by 800 in score, takes every query to V[0] = 1."""
+    dt = O.F16
+    q = np.full((1, 2, 1, 64), 100.0)
+    k = np.stack([np.full(64, 100.0), np.full(64, 99.0)]).reshape(1, 2, 1, 64)
+    v = np.repeat(np.array([1.0, 100.0]).reshape(1, 2, 1, 1), 64, axis=-1)
+    got = host(ops.attention(dev(q, dt), dev(k, dt), dev(v, dt)))
+    assert "kernel flash_attention" in ops.chosen()
+    assert np.isfinite(got).all() and np.abs(got - 1.0).max() < 1e-3

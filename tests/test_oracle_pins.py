@@ -402,3 +402,82 @@ def test_oracle_reproduces_the_committed_fixtures():
         a = fresh[key]
         a = (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64) if a.dtype == np.uint16 else a
         assert np.array_equal(a, want[key]), key
+
+
+# --------------------------------------------------------------------------
+# More of the reference's own known-answer tests, replayed on the oracle
+# --------------------------------------------------------------------------
+
+
+def ramp(count):
+    """`ramp` of tensor/src/test/unit/attention_helpers.rs:80-82 (float32 arithmetic)."""
+    i = np.arange(count, dtype=np.float32)
+    return (np.sin(i * np.float32(0.37)) + i * np.float32(0.01)).astype(np.float32)
+
+
+def test_layernorm_known_answer():
+    """tensor/src/test/unit/nn.rs:428-446: rows [1,2,3,4] and [5,6,7,8], eps 1e-5:
+    every row comes out with mean ~0 and variance ~1."""
+    x = np.array([[1.0, 2.0, 3.0, 4.0], [5.0, 6.0, 7.0, 8.0]])
+    y, _ = O.norm_rows("layer", x, np.ones(4), np.zeros(4), eps=1e-5, dtype=O.F32)
+    for row in y:
+        assert abs(row.mean()) < 1e-4 and abs(row.var() - 1.0) < 0.1
+    # closed form: (x - 2.5) / sqrt(1.25 + 1e-5)
+    assert np.allclose(y[0], (x[0] - 2.5) / np.sqrt(1.25 + 1e-5), atol=1e-6)
+
+
+@pytest.mark.parametrize("theta,seq,hd", [(10_000.0, 8, 16), (100_000.0, 6, 8), (1_000_000.0, 5, 8), (64.0, 4, 4)])
+def test_rope_table_matches_the_reference_host_loop(theta, seq, hd):
+    """tensor/src/test/unit/attention_helpers.rs:19-32,88-104: inv_freq = theta^(-2i/d)
+    formed in f64 and cast to f32, angle = s * inv_freq in f32, cos/sin in f32; 1e-5."""
+    half = hd // 2
+    inv = np.array([theta ** (-2.0 * i / hd) for i in range(half)], dtype=np.float32)
+    ang = (np.arange(seq, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    cos, sin = O.rope_table(theta, np.arange(seq), hd, O.F32)
+    assert np.abs(np.asarray(cos).reshape(seq, half) - np.cos(ang)).max() < 1e-5
+    assert np.abs(np.asarray(sin).reshape(seq, half) - np.sin(ang)).max() < 1e-5
+
+
+@pytest.mark.parametrize("mask", [[1, 1, 1, 1, 1, 0], [1, 0, 0, 0, 0, 0], [1, 1, 1, 1, 1, 1], [0, 0, 0, 1, 1, 1]])
+def test_masked_mean_matches_the_reference_host_loop(mask):
+    """tensor/src/test/unit/attention_helpers.rs:66-76,487-505: sum over the masked
+    tokens / max(count, 1e-9) on the `ramp` data, batch 2 x len 3 x depth 4; 1e-5."""
+    data = ramp(2 * 3 * 4).reshape(2, 3, 4)
+    m = np.array(mask, dtype=np.float32).reshape(2, 3)
+    want = np.zeros((2, 4), dtype=np.float32)
+    for b in range(2):
+        count = max(float(m[b].sum()), 1e-9)
+        for d in range(4):
+            want[b, d] = sum(float(data[b, l, d]) * float(m[b, l]) for l in range(3)) / count
+    got = O.pool(data, m > 0.5, "mean", normalize=False)
+    assert np.abs(got - want).max() < 1e-5
+    # cls / last-token pooling of the same tensor (attention_helpers.rs:507-520)
+    assert np.array_equal(O.pool(data, None, "cls", normalize=False), data[:, 0].astype(np.float64))
+    assert np.array_equal(O.pool(data, None, "last", lengths=np.array([3, 3]), normalize=False),
+                          data[:, -1].astype(np.float64))
+
+
+def test_embedding_known_answers():
+    """tensor/src/test/unit/transformer.rs:51-100: rows of the table by index, 1-D,
+    2-D and int64 indices (the oracle's lookup is `table[ids]`)."""
+    w = np.arange(12, dtype=np.float64).reshape(3, 4)
+    got = w[np.array([2, 0])]
+    assert got[0, 0] == 8.0 and got[0, 3] == 11.0 and got[1, 0] == 0.0 and got[1, 3] == 3.0
+    w2 = np.array([[0.0, 1.0], [2.0, 3.0], [4.0, 5.0], [6.0, 7.0]])
+    got = w2[np.array([[0, 1, 2], [3, 2, 1]])]
+    assert got.shape == (2, 3, 2) and got[0, 2, 0] == 4.0 and list(got[1, 0]) == [6.0, 7.0]
+    got = w2[np.array([[3, 0], [1, 3]], dtype=np.int64)]
+    assert list(got.reshape(-1)) == [6.0, 7.0, 0.0, 1.0, 2.0, 3.0, 6.0, 7.0]
+
+
+def test_f16_scores_are_formed_in_wide_precision():
+    """tensor/src/test/unit/transformer.rs:170-190: 64 products of 100*100 pass
+    float16's range; scores formed wide keep the softmax finite and key 0 (ahead
+    by 800 in score) takes every query to V[0] = 1."""
+    q = O.round_to(O.F16, np.full((1, 2, 1, 64), 100.0))
+    k = O.round_to(O.F16, np.stack([np.full(64, 100.0), np.full(64, 99.0)]).reshape(1, 2, 1, 64))
+    v = O.round_to(O.F16, np.array([1.0, 100.0]).reshape(1, 2, 1, 1))
+    # the oracle takes [B,T,H,D]; a 1-wide value head is padded to the key's head dim for the kernels,
+    # the oracle itself has no such limit
+    out = O.attention(q, k, np.repeat(v, 64, axis=-1), dtype=O.F16)
+    assert np.isfinite(out).all() and np.abs(out - 1.0).max() < 1e-3
