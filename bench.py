@@ -724,6 +724,15 @@ def kernel_case(args):
         o = ops.Linear(act=ops.Act.SILU, gated=True)
         fn = lambda: ops.linear(x, w, o)
         flops = 2 * M * 2 * N * K
+    elif args.kernel_case == "gemm_gelu":
+        # XLM-R's FFN-in shape at a reduced row count: bias + erf-GELU, K = 1024
+        M, N, K = B * T, 4096, 1024
+        x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.float16)
+        w = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.float16)
+        bias = (torch.randn(N, generator=g, device="cuda") * 0.02).to(torch.float16)
+        o = ops.Linear(bias=bias, act=ops.Act.GELU)
+        fn = lambda: ops.linear(x, w, o)
+        flops = 2 * M * N * K
     elif args.kernel_case == "rms_norm":
         x = torch.randn(B * T * 4, 1024, generator=g, device="cuda").to(torch.bfloat16)
         w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
@@ -849,7 +858,7 @@ def main():
     ap.add_argument("--reference-ops", action="store_true",
                     help="Qwen3: the reference's op sequence (linear, heads, attention) instead of the "
                          "q/k prologue fused into the projection's store")
-    ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "rms_norm", "heads"],
+    ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "gemm_gelu", "rms_norm", "heads"],
                     help="run a few launches of one kernel on a small case (for profiler captures) and exit")
     ap.add_argument("--case-batch", type=int, default=4)
     ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32", "decode"],
