@@ -79,20 +79,45 @@ __device__ __forceinline__ float silu_f(float x) {
   return x * rcp_ftz(1.0f + ex2_ftz(x * -1.4426950408889634f));
 }
 
-// 0.5*(x + |x|*erf(|x|/sqrt2)), erf by Abramowitz-Stegun 7.1.26 with
-// z = |x|/sqrt2 folded into the constants: t = 1/(1 + p*z), e^(-z^2) =
-// 2^(-x^2 * log2(e)/2). Two MUFU operations and a dozen FMA-pipe ones per value.
+// Exact (erf) GELU as x*Phi(x) = max(x, 0) - |x|*Q(|x|), Q(a) = erfc(a/sqrt2)/2 the
+// Gaussian upper tail. log2 Q is smooth, so Q(a) = 2^P(a) with P a degree-5
+// polynomial (P(0) = -1, fitted on [0, 5.5] with the weight a*Q(a) the error
+// carries into the result; beyond 5.5 the tail term stays at 5.5*Q(5.5) = 1e-7). Absolute
+// error 1e-6 against the erf form, the same as the Abramowitz-Stegun 7.1.26 form
+// the CPU checker pins (tensor/src/activation.rs:233-243), with ONE MUFU operation
+// and 8 FMA-pipe / ALU ones per value instead of two and 12: in a GEMM epilogue
+// the MUFU unit is what four epilogue warps per scheduler queue on.
+constexpr float kGeluClamp = 5.5f;
+constexpr float kGeluP1 = -1.15100054e+00f;
+constexpr float kGeluP2 = -4.59595852e-01f;
+constexpr float kGeluP3 = -5.21466294e-02f;
+constexpr float kGeluP4 = 7.19871996e-03f;
+constexpr float kGeluP5 = -4.88102743e-04f;
+
 __device__ __forceinline__ float gelu_f(float x) {
-  const float ax = fabsf(x);
-  const float t = rcp_ftz(fmaf(ax, 0.3275911f * 0.70710678118654752f, 1.0f));
-  float poly = 1.061405429f;
-  poly = fmaf(poly, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float e = ex2_ftz((x * x) * -0.72134752044448170f);
-  const float erf = fmaf(-(poly * t), e, 1.0f);
-  return 0.5f * fmaf(ax, erf, x);
+  const float a = fminf(fabsf(x), kGeluClamp);
+  float p = kGeluP5;
+  p = fmaf(p, a, kGeluP4);
+  p = fmaf(p, a, kGeluP3);
+  p = fmaf(p, a, kGeluP2);
+  p = fmaf(p, a, kGeluP1);
+  p = fmaf(p, a, -1.0f);
+  return fmaf(-a, ex2_ftz(p), fmaxf(x, 0.0f));
+}
+
+// Two values at once, the same operations in the same order (bit-identical to
+// gelu_f): the polynomial and the last step as packed f32x2 FMAs on n = -a, with
+// the odd coefficients' signs flipped — half the issue slots.
+__device__ __forceinline__ void gelu2_f(float& x0, float& x1) {
+  const float2 n = make_float2(fmaxf(-fabsf(x0), -kGeluClamp), fmaxf(-fabsf(x1), -kGeluClamp));
+  float2 p = __ffma2_rn(make_float2(-kGeluP5, -kGeluP5), n, make_float2(kGeluP4, kGeluP4));
+  p = __ffma2_rn(p, n, make_float2(-kGeluP3, -kGeluP3));
+  p = __ffma2_rn(p, n, make_float2(kGeluP2, kGeluP2));
+  p = __ffma2_rn(p, n, make_float2(-kGeluP1, -kGeluP1));
+  p = __ffma2_rn(p, n, make_float2(-1.0f, -1.0f));
+  const float2 y = __ffma2_rn(n, make_float2(ex2_ftz(p.x), ex2_ftz(p.y)), make_float2(fmaxf(x0, 0.0f), fmaxf(x1, 0.0f)));
+  x0 = y.x;
+  x1 = y.y;
 }
 
 // 0.5*x*(1+tanh(sqrt(2/pi)*(x+0.044715x^3))) (tensor/src/activation.rs:198-230).

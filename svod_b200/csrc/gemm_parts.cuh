@@ -40,7 +40,7 @@ __device__ __forceinline__ void act32(float (&x)[32], int act) {
   switch (act) {
     case kActGelu:
 #pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = gelu_f(x[i]);
+      for (int i = 0; i < 32; i += 2) gelu2_f(x[i], x[i + 1]);
       break;
     case kActSilu:
 #pragma unroll
@@ -60,16 +60,27 @@ template <typename T>
 __device__ __forceinline__ void acc32(uint32_t taddr, const T* bias, int n_at, int n_lim, float (&x)[32]) {
   uint32_t r[32];
   tmem_ld32(taddr, r);
-  tmem_ld_wait();
+  // the bias chunk is requested while the accumulator load is in flight: the two
+  // latencies overlap instead of following one another
+  uint4 bu[4];
+  if (bias != nullptr) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      bu[v] = n_at + v * 8 < n_lim ? ldg128(bias + n_at + v * 8) : make_uint4(0, 0, 0, 0);
+  }
+  tmem_ld_wait_for(r);
 #pragma unroll
   for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
   if (bias != nullptr) {
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
-      float b[8];
-      load8<T>(bias + n_at + v * 8, n_at + v * 8 < n_lim, b);
+      const uint32_t uu[4] = {bu[v].x, bu[v].y, bu[v].z, bu[v].w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[v * 8 + i] += b[i];
+      for (int i = 0; i < 4; ++i) {
+        const float2 b = Elem<T>::unpack(uu[i]);
+        x[v * 8 + 2 * i] += b.x;
+        x[v * 8 + 2 * i + 1] += b.y;
+      }
     }
   }
 }

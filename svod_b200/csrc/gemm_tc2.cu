@@ -49,8 +49,12 @@ struct Cfg2 {
   static constexpr int kThreads = 32 * (2 + EW);
   static constexpr int kStagingBytes = kGroups * kGroupStaging;
   static constexpr int kStages = (HEADS || EW == 16) ? 5 : 6;
+  // sixteen-warp variant: the bias of a group's 64 columns, three tiles deep
+  static constexpr int kBiasBytes = EW == 16 ? 3 * kGroups * 128 : 0;
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kStagingBytes + (HEADS ? kTableBytes : 0) +
-                                       1024 /*align*/ + 256 /*barriers*/ + (HEADS ? 1024 : 0) /*norm weights*/;
+                                       1024 /*align*/ + 256 /*barriers*/ + (HEADS ? 1024 : 0) /*norm weights*/ +
+                                       kBiasBytes;
+  static_assert(kSmemBytes <= 232448, "beyond the 227 KiB a CTA may hold");
 };
 
 struct Params2 {
@@ -246,6 +250,104 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
           aph ^= 1;
         }
       }
+    }
+  } else if constexpr (EW == 16) {
+    // ---------------- epilogue, sixteen warps (both CTAs, each its 128 rows) ----------------
+    // Bias -> activation -> scale, no residual, no gate. Each warp owns 32 rows x 64
+    // columns of the tile and shares nothing with the others but the accumulator:
+    // it reads both 32-column halves from tensor memory at once, hands the
+    // accumulator back to the MMA warp as soon as they are in registers, and stores
+    // its own 32-row slab by TMA, so no warp waits for a slower one.
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int group = ew >> 2;
+    const T* bias = (const T*)p.bias;
+    uint8_t* bias_slots = reinterpret_cast<uint8_t*>(bars) + 256;  // [3 tiles][4 groups][128 B]
+    uint8_t* slab = staging + group * kGroupStaging + quarter * (32 * 128);
+    uint8_t* srow = slab + lane * 128;
+    int as = 0;
+    uint32_t aph = 0;
+    int slot = 0;
+    for (int t = pair; t < num_tiles; t += pairs) {
+      int mt, nt;
+      tile_coords(t, p.tiles_m, p.tiles_n, mt, nt);
+      const int m_at = mt * 2 * BM + (int)rank * BM + quarter * 32;
+      const int n_at = nt * BN + group * 64;
+      const bool live = m_at < p.m && n_at < p.n;
+      // The group's 64 bias values go to shared memory before the accumulator is
+      // waited for (their latency hides behind the wait). The four warps of a
+      // group write the same bytes; a slot is reused every third tile, which the
+      // accumulator hand-over below keeps apart from any warp still reading it.
+      uint8_t* bslot = bias_slots + (slot * 4 + group) * 128;
+      if (bias != nullptr) {
+        const int c = n_at + 2 * lane;
+        *reinterpret_cast<uint32_t*>(bslot + 4 * lane) =
+            (live && c < p.n) ? __ldg(reinterpret_cast<const uint32_t*>(bias + c)) : 0u;
+      }
+      if (!mbar_wait(&acc_full[as], aph, p.status)) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + (uint32_t)(as * BN + group * 64) + ((uint32_t)(quarter * 32) << 16);
+      uint32_t r0[32], r1[32];
+      tmem_ld32(t_acc, r0);
+      tmem_ld32(t_acc + 32u, r1);
+      tmem_ld_wait_for(r0);
+      tmem_ld_wait_for(r1);
+      __syncwarp();  // the slot's bytes are visible to every lane
+      float x0[32], x1[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x0[i] = __uint_as_float(r0[i]), x1[i] = __uint_as_float(r1[i]);
+      if (bias != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 b0 = *reinterpret_cast<const uint4*>(bslot + v * 16);
+          const uint4 b1 = *reinterpret_cast<const uint4*>(bslot + 64 + v * 16);
+          const uint32_t u0[4] = {b0.x, b0.y, b0.z, b0.w};
+          const uint32_t u1[4] = {b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f0 = Elem<T>::unpack(u0[i]);
+            const float2 f1 = Elem<T>::unpack(u1[i]);
+            x0[v * 8 + 2 * i] += f0.x, x0[v * 8 + 2 * i + 1] += f0.y;
+            x1[v * 8 + 2 * i] += f1.x, x1[v * 8 + 2 * i + 1] += f1.y;
+          }
+        }
+      }
+      // This warp has read the accumulator and the bias slot: one arrival on the
+      // even CTA's barrier, from either CTA.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cluster(cluster_map(&acc_empty[as], 0));
+        tma_store_wait_read();  // this warp's previous store has read the slab
+      }
+      __syncwarp();
+#pragma unroll
+      for (int hc = 0; hc < 2; ++hc) {
+        float(&xs)[32] = hc == 0 ? x0 : x1;
+        act32(xs, p.act);
+        if (p.has_scale) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) xs[i] *= p.scale;
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int c = hc * 4 + c4;  // chunk c of row r sits at (c ^ (r & 7))
+          *reinterpret_cast<uint4*>(srow + ((c ^ (lane & 7)) << 4)) =
+              make_uint4(Elem<T>::pack(xs[c4 * 8 + 0], xs[c4 * 8 + 1]), Elem<T>::pack(xs[c4 * 8 + 2], xs[c4 * 8 + 3]),
+                         Elem<T>::pack(xs[c4 * 8 + 4], xs[c4 * 8 + 5]), Elem<T>::pack(xs[c4 * 8 + 6], xs[c4 * 8 + 7]));
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && live) {
+        tma_store_2d(&tmap_r, slab, n_at, m_at);  // the 32-row view of the output
+        tma_store_commit();
+      }
+      if (++as == 2) {
+        as = 0;
+        aph ^= 1;
+      }
+      if (++slot == 3) slot = 0;
     }
   } else {
     // ---------------- epilogue (both CTAs, each its 128 rows) ----------------
@@ -536,7 +638,7 @@ __global__ void __launch_bounds__(32 * (2 + EW), 1)
     }
   }
 
-  if (warp >= 2 && ((warp - 2) & 3) == 0 && lane == 0) tma_store_wait_all();
+  if (warp >= 2 && lane == 0) tma_store_wait_all();  // whoever issued stores; a no-op for the others
   tc_fence_before();
   __syncthreads();
   // Neither CTA may leave while the other can still signal its barriers or the
@@ -565,7 +667,9 @@ int run2(const GemmArgs& a, int sms, cudaStream_t s, char* cfg, size_t cfg_len) 
   if (!make_tmap_2d(&tw, a.w, dt, (uint64_t)a.k, w_rows, (uint64_t)a.ldw, BK, BN / 2)) return -1;
   if (!make_tmap_2d(&tc, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, BM)) return -1;
   tr = tc;
-  if (a.residual != nullptr && !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
+  // sixteen epilogue warps: the residual's slot carries the output again, as 32-row boxes
+  if (EW == 16 && !make_tmap_2d(&tr, a.c, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, 32)) return -1;
+  if (EW != 16 && a.residual != nullptr && !make_tmap_2d(&tr, a.residual, dt, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldr, 64, BM))
     return -1;
   CUtensorMap tcos = tc, tsin = tc;
   if (HEADS) {
@@ -664,7 +768,7 @@ int launch_gemm_tc2(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len
   // sixteen epilogue warps where each output value costs an activation
   // (long k loops hide the epilogue anyway and prefer the deeper ring of the eight-warp variant;
   // measured: a residual alone does not pay for them)
-  const bool wide = !heads && !a.gated && a.act != kActNone && a.k <= 2048;
+  const bool wide = !heads && !a.gated && a.act != kActNone && a.residual == nullptr && a.k <= 2048;
   if (a.dtype == SVODB_BF16)
     return heads  ? run2<__nv_bfloat16, true, 8>(a, sms, s, cfg, cfg_len)
            : wide ? run2<__nv_bfloat16, false, 16>(a, sms, s, cfg, cfg_len)

@@ -126,6 +126,30 @@ def test_in_kernel_gelu_is_within_the_stated_error_of_erf_gelu():
     assert abs(float(O.gelu_tanh(np.array(1.0))) - 0.841192) < 1e-5
 
 
+def test_the_kernels_single_exponential_gelu_stays_within_1e_4_of_the_pinned_form():
+    """The CUDA `gelu_f` evaluates x*Phi(x) as max(x,0) - |x| * 2^P(|x|); its
+    coefficients are read from the kernel header and the form is replayed here in
+    f32 against the pinned Abramowitz-Stegun form and against erf itself."""
+    import pathlib
+    import re
+
+    src = (pathlib.Path(__file__).resolve().parent.parent / "svod_b200" / "csrc" / "common.cuh").read_text()
+    coef = {k: float(v) for k, v in re.findall(r"constexpr float kGelu(\w+) = ([-+0-9.e]+)f;", src)}
+    assert set(coef) == {"Clamp", "P1", "P2", "P3", "P4", "P5"}
+    x = np.concatenate([np.linspace(-12, 12, 400001), [-1e4, 1e4, 0.0]]).astype(np.float32)
+    a = np.minimum(np.abs(x), np.float32(coef["Clamp"]))
+    p = np.full_like(x, np.float32(coef["P5"]))
+    for k in ("P4", "P3", "P2", "P1"):
+        p = (p * a + np.float32(coef[k])).astype(np.float32)
+    p = (p * a - np.float32(1.0)).astype(np.float32)
+    got = (np.maximum(x, 0) - a * np.exp2(p).astype(np.float32)).astype(np.float32)
+    assert np.max(np.abs(got - O.gelu_as(x.astype(np.float64)))) < 1e-4
+    inside = np.abs(x) <= 12
+    assert np.max(np.abs(got - O.gelu_erf(x.astype(np.float64)))[inside]) < 5e-6
+    # far outside the fitted range the result is x or 0 to within 5.5 * Q(5.5)
+    assert abs(got[-3]) < 2e-7 and got[-2] == 1e4 and got[-1] == 0
+
+
 # ---- the GEMM epilogue recipe: tk/src/test/unit/rows.rs:37-104 -------------------------------
 EPILOGUES = [
     dict(bias=True), dict(residual=True), dict(bias=True, act=O.ACT_GELU),
