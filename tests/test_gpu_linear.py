@@ -217,7 +217,9 @@ def test_qkv_prologue_excludes_the_other_epilogues():
     (4964, 1000, 256, dict(bias=True, residual=True, scale=0.5)),  # ragged rows (the odd CTA of the last tile is empty) and columns
     (4864, 512, 256, dict(act=2, gated=True)),                   # SwiGLU: gate rows in the even CTA, up rows in the odd one
     (9728, 512, 192, dict(bias=True, act=2, gated=True, residual=True)),
-    (4964, 1000, 512, dict(bias=True, act=1, residual=True, scale=0.5)),  # sixteen epilogue warps, ragged, residual
+    (4964, 1000, 512, dict(bias=True, act=1, residual=True, scale=0.5)),  # activation with a residual: eight epilogue warps
+    (4964, 1000, 512, dict(bias=True, act=1, scale=0.5)),  # sixteen epilogue warps (per-warp slabs), ragged rows and columns
+    (4900, 1096, 2048, dict(act=1)),                       # sixteen warps without a bias, rows ragged inside a 32-row slab
     (4864, 1024, 512, dict(act=3)),                                        # tanh GELU, four column groups
 ])
 def test_cta_pair_gemm_matches_the_oracle(m, n, k, kw):
