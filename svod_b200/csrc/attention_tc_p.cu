@@ -20,8 +20,10 @@
 //     first P.V may overwrite it): the loader and the issuers run into the next
 //     item while the softmax warps still finish the last one.
 // A bool key mask needs no CTA-wide scan here: the loader warp scans the mask row
-// of its item's batch lane (once per change of lane) and passes the result on
-// with the item; the softmax gathers the bits of a block's keys with a ballot.
+// of its item's batch lane (once per change of lane); the softmax gathers the
+// bits of a block's keys with a ballot. The loader also works out each item's
+// key-block ranges (`Work`) once and publishes them with the item, so that the
+// issuers and the softmax warps start an item by reading 80 bytes.
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
@@ -45,12 +47,16 @@ using namespace fa_parts;
 // Queue heads: items handed out so far by a running launch, one per (device,
 // stream) pair, zeroed on the stream just before each launch.
 constexpr int kQueueSlots = 256;
+template <int D>
+constexpr size_t smem_bytes_p() {
+  using C = FaCfg<D>;
+  return 1024 + (size_t)2 * C::kQTileBytes + (size_t)2 * C::kStages * C::kKvBytes + 512;
+}
 __device__ int g_next_item[kQueueSlots];
 
 struct Item {
   int qt, h, b, valid;
-  int mask_len, mask_general;  // what the loader's scan of a bool key mask row found (see MaskRow)
-  int split;                   // key split of this item (0 without splits)
+  int split;  // key split of this item (0 without splits)
 };
 
 // Work item w in queue order: batch, KV head, query head of the group, then
@@ -62,7 +68,7 @@ struct Item {
 // items of the last group when everything else is done.
 __device__ __forceinline__ Item decode_item(int w, int n_items, int n_qt, int heads, int kv_heads, int tail_groups,
                                             int splits) {
-  Item it{0, 0, 0, 0, 0, 0, 0};
+  Item it{0, 0, 0, 0, 0};
   if (w >= n_items) return it;
   // the splits of one (tile pair, head, batch) follow one another in the queue
   it.split = w % splits;
@@ -138,6 +144,17 @@ __device__ __forceinline__ void scan_mask_row(const FaParams& p, int64_t b, int 
   row.general = first_zero < last_set ? 1 : 0;
 }
 
+// What every role derives from an item: the key-block ranges of its two tiles.
+// The loader works it out once per item and publishes it with the item.
+struct Work {
+  int valid;
+  int h, hk, split;
+  int b, i0;         // batch lane, first query row of the pair of tiles (both below 2^31)
+  int len, general;  // the mask context (`Ctx`): visible key bound, whether to consult the bitmask
+  Range r0, r1;
+  int u_lo, u_hi;    // the union of the two ranges: the blocks the loader brings
+};
+
 // EXTRAS = key splits and / or an additive bias: a separate instantiation, so that
 // the plain kernel's inner loop carries neither their registers nor their branches.
 template <typename T, int D, bool EXTRAS>
@@ -169,7 +186,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   uint64_t* item_full = o_empty + 2;           // [2 slots]
   uint64_t* item_empty = item_full + 2;        // [2 slots]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_empty + 2);
-  Item* item_ring = reinterpret_cast<Item*>(tmem_slot + 4);  // [2]
+  Work* item_ring = reinterpret_cast<Work*>(tmem_slot + 4);  // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -207,33 +224,28 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // What every role derives from an item: the key-block ranges of its two tiles.
-  struct Work {
-    int h, hk, split;
-    int64_t b, i0;
-    Ctx ctx;
-    Range r0, r1;
-    bool live0, live1;
-    int u_lo, u_hi;
-  };
   auto plan = [&](const Item& it, const MaskRow& mrow) -> Work {
     Work w;
+    w.valid = it.valid;
     w.h = it.h;
     w.hk = it.h / (p.heads / p.kv_heads);
     w.b = it.b;
-    w.i0 = (int64_t)it.qt * 2 * kBQ;
-    w.ctx.len = p.tk;
-    w.ctx.general_mask = 0;
+    w.i0 = it.qt * 2 * kBQ;
+    Ctx ctx;
+    ctx.len = p.tk;
+    ctx.general_mask = 0;
     if (p.key_lens != nullptr) {
       const int64_t kl = p.key_lens[it.b];
-      w.ctx.len = kl < 0 ? 0 : (kl < w.ctx.len ? kl : w.ctx.len);
+      ctx.len = kl < 0 ? 0 : (kl < ctx.len ? kl : ctx.len);
     }
     if (p.key_mask != nullptr) {
-      w.ctx.general_mask = mrow.general;
-      if (mrow.len < w.ctx.len) w.ctx.len = mrow.len;
+      ctx.general_mask = mrow.general;
+      if (mrow.len < ctx.len) ctx.len = mrow.len;
     }
-    w.r0 = tile_range(p, w.ctx, w.b, w.i0);
-    w.r1 = tile_range(p, w.ctx, w.b, w.i0 + kBQ);
+    w.len = (int)ctx.len;
+    w.general = ctx.general_mask;
+    w.r0 = tile_range(p, ctx, w.b, w.i0);
+    w.r1 = tile_range(p, ctx, w.b, (int64_t)w.i0 + kBQ);
     w.split = it.split;
     if (EXTRAS && p.splits > 1) {
       // this split's share of the key blocks
@@ -245,22 +257,24 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       if (w.r0.hi <= w.r0.lo) w.r0 = Range{0, 0};
       if (w.r1.hi <= w.r1.lo) w.r1 = Range{0, 0};
     }
-    w.live0 = w.r0.hi > w.r0.lo;
-    w.live1 = w.r1.hi > w.r1.lo;
+    const bool live0 = w.r0.hi > w.r0.lo, live1 = w.r1.hi > w.r1.lo;
     w.u_lo = 0, w.u_hi = 0;
-    if (w.live0 && w.live1) {
+    if (live0 && live1) {
       w.u_lo = w.r0.lo < w.r1.lo ? w.r0.lo : w.r1.lo;
       w.u_hi = w.r0.hi > w.r1.hi ? w.r0.hi : w.r1.hi;
-    } else if (w.live0) {
+    } else if (live0) {
       w.u_lo = w.r0.lo, w.u_hi = w.r0.hi;
-    } else if (w.live1) {
+    } else if (live1) {
       w.u_lo = w.r1.lo, w.u_hi = w.r1.hi;
     }
     return w;
   };
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    // 4 warps x 72 + 8 warps x 216 registers = the 384 x 168 the CTA was launched
+    // with: a larger request here would leave the softmax warps' increase waiting
+    // for registers that never come.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0) {
       // ---------------- scheduler + TMA loader ----------------
       // The whole warp walks the queue (a key mask row is scanned by all lanes);
@@ -281,22 +295,19 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           // The loader alone scans a bool key mask row (all its lanes, once per change
           // of batch lane, while it runs ahead of the other warps) and hands what it
           // found to them with the item.
-          if (it.valid && p.key_mask != nullptr) {
-            scan_mask_row(p, it.b, lane, mrow);
-            it.mask_len = mrow.len;
-            it.mask_general = mrow.general;
-          }
+          if (it.valid && p.key_mask != nullptr) scan_mask_row(p, it.b, lane, mrow);
+          Work w{};
+          if (it.valid) w = plan(it, mrow);
           if (lane == 0) {
-            item_ring[slot] = it;
+            item_ring[slot] = w;
             __threadfence_block();
             mbar_arrive(&item_full[slot]);
           }
           if (!it.valid) break;
-          const Work w = plan(it, mrow);
           if (w.u_hi <= w.u_lo) continue;
           if (lane == 0) {
           for (int i = 0; i < 2; ++i) {
-            if (i == 0 ? w.live0 : w.live1) {
+            if (i == 0 ? w.r0.hi > w.r0.lo : w.r1.hi > w.r1.lo) {
               // the issuer's last QK of the tile's previous live item has read this Q tile
               if (!mbar_wait(&q_empty[i], (q_items[i] & 1) ^ 1, p.status)) {
                 ok = false;
@@ -305,11 +316,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
               ++q_items[i];
               mbar_expect_tx(&q_full[i], QB);
               for (int c = 0; c < D / 64; ++c)
-                tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, w.h, (int)(w.i0 + i * kBQ),
-                            (int)w.b);
+                tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, w.h, w.i0 + i * kBQ, w.b);
             }
           }
-          const int kv_b = p.row_map != nullptr ? p.row_map[w.b] : (int)w.b;
+          const int kv_b = p.row_map != nullptr ? p.row_map[w.b] : w.b;
           for (int j = w.u_lo; j < w.u_hi && ok; ++j) {
             if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) {
               ok = false;
@@ -350,17 +360,14 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       uint32_t kv_blocks = 0;  // K/V blocks of all earlier items (ring position)
       uint32_t my_blocks = 0;  // blocks of this tile in all earlier items (S/P buffer and phase)
       uint32_t my_items = 0;   // live items of this tile so far
-      MaskRow mrow{-1, 0, 0};
       bool ok = true;
       for (uint32_t n_it = 0; ok; ++n_it) {
         const int slot = (int)(n_it & 1);
         if (!mbar_wait(&item_full[slot], (n_it >> 1) & 1, p.status)) break;
-        const Item it = item_ring[slot];
+        const Work w = item_ring[slot];
         __syncwarp();
         if (lane == 0) mbar_arrive(&item_empty[slot]);
-        if (!it.valid) break;
-        mrow.len = it.mask_len, mrow.general = it.mask_general;
-        const Work w = plan(it, mrow);
+        if (!w.valid) break;
         if (w.u_hi <= w.u_lo) continue;
         const Range r = i == 0 ? w.r0 : w.r1;
         const int nblk = r.hi - r.lo;
@@ -450,7 +457,6 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     const int other_turn = 1 + (1 - i) * 4 + quarter;
     uint32_t my_blocks = 0;   // blocks of this tile in all earlier items
     uint32_t tail_count = 0;  // tail commits of this tile in all earlier items
-    MaskRow mrow{-1, 0, 0};
     // A warp whose bounded wait ran out stops computing but keeps walking the
     // queue and, for every later item, arrives on its partner's barrier at each
     // turn the partner may take (`ok` stays false): the partner, which sees the
@@ -471,12 +477,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         for (int64_t m = 0; m < 2 * (p.tk / kBKV + 2); ++m) named_barrier_arrive(other_turn, 64);
         break;
       }
-      const Item it = item_ring[slot];
+      const Work w = item_ring[slot];
       __syncwarp();
       if (lane == 0) mbar_arrive(&item_empty[slot]);
-      if (!it.valid) break;
-      mrow.len = it.mask_len, mrow.general = it.mask_general;
-      const Work w = plan(it, mrow);
+      if (!w.valid) break;
       if (!ok) {
         const int pairs = min(w.r0.hi - w.r0.lo, w.r1.hi - w.r1.lo);
         // arrivals only: a partner still computing is released at each of its
@@ -488,7 +492,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       const Range r = i == 0 ? w.r0 : w.r1;
       const int h = w.h;
       const int64_t b = w.b;
-      const int64_t i_first = w.i0 + (int64_t)i * kBQ;
+      const int64_t i_first = (int64_t)w.i0 + (int64_t)i * kBQ;
       const int64_t row = i_first + quarter * 32 + lane;
       const bool row_ok = row < p.t;
       const int64_t i_last = (i_first + kBQ - 1 < p.t - 1) ? i_first + kBQ - 1 : p.t - 1;
@@ -497,7 +501,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         seg_me = p.seg_start[b * p.t + (row_ok ? row : i_last)];
         seg_last = p.seg_start[b * p.t + i_last];
       }
-      int64_t vis_lo64 = 0, vis_hi64 = w.ctx.len;
+      int64_t vis_lo64 = 0, vis_hi64 = w.len;
       if (p.causal && row + 1 < vis_hi64) vis_hi64 = row + 1;
       if (p.has_window) {
         if (row - p.win_left > vis_lo64) vis_lo64 = row - p.win_left;
@@ -544,7 +548,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           tmem_ld32(s_tmem + 32, sr[1]);
         }
         const int64_t j0 = (int64_t)j * kBKV, j1 = j0 + kBKV - 1;
-        bool need_mask = j1 >= w.ctx.len || p.has_chunk || w.ctx.general_mask;
+        bool need_mask = j1 >= w.len || p.has_chunk || w.general;
         if (p.causal && j1 > i_first) need_mask = true;
         if (p.has_window && (j0 + p.win_left < i_last || j1 > i_first + p.win_right)) need_mask = true;
         if (p.seg_start != nullptr && j0 < seg_last) need_mask = true;
@@ -580,7 +584,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t vw = vis_word((int)j0 + 32 * c);
-            if (w.ctx.general_mask) {
+            if (w.general) {
               // the mask bits of these 32 keys: one key per lane, gathered by a ballot
               const int64_t jk = j0 + 32 * c + lane;
               int m = 0;
@@ -822,7 +826,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   bool& attr_set = attr_seen[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(attention_tc_p_kernel<T, D, EXTRAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)C::kSmemBytes) != cudaSuccess)
+                             (int)smem_bytes_p<D>()) != cudaSuccess)
       return -1;
     attr_set = true;
   }
@@ -870,8 +874,8 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     tail_groups = (int)(want < groups ? want : groups);
   }
   if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
-  attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, C::kSmemBytes, s>>>(tq, tk, tv, p, (int)items, tail_groups,
-                                                                               head);
+  attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, smem_bytes_p<D>(), s>>>(tq, tk, tv, p, (int)items,
+                                                                                  tail_groups, head);
   if (cfg != nullptr)
     snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages,
              p.splits, grid);
