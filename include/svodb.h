@@ -48,7 +48,9 @@ enum {
 enum { SVODB_F32 = 0, SVODB_F16 = 1, SVODB_BF16 = 2, SVODB_I32 = 3, SVODB_I64 = 4, SVODB_U8 = 5 };
 
 /* ---- `kernels::Act` (tk/src/kernels/mod.rs:272-280); GELU_TANH is the extra
- * `Tensor::gelu` form (tensor/src/activation.rs:198-230) ---- */
+ * `Tensor::gelu` form (tensor/src/activation.rs:198-230). GELU is the exact (erf)
+ * form: the reference evaluates erf by Abramowitz-Stegun 7.1.26 (mod.rs:304-335),
+ * this library as x*Phi(x) = max(x,0) - a*2^P(a); both sit within 1e-6 of erf. ---- */
 enum { SVODB_ACT_NONE = 0, SVODB_ACT_GELU = 1, SVODB_ACT_SILU = 2, SVODB_ACT_GELU_TANH = 3 };
 
 #define SVODB_MAX_RANK 5
