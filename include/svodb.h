@@ -143,7 +143,20 @@ typedef struct svodb_linear_opts {
    * packed [B,T,N] projection that `svodb_attention_packed` reads in place.
    * Excludes rope_*, gated, act, scale and residual. NULL = off. */
   const struct svodb_qkv_opts* qkv;
+  /* Split-K (the reference's `gemm_tail` + `split_merge`, tk/src/kernels/gemm.rs:454-466,
+   * 750-808: f32 partials of a k loop cut into pieces, merged by one pass that applies the
+   * epilogue once; never with a gate or a rotation). 0 or 1 = the k loop in one piece;
+   * > 1 = that many pieces on the CTA-pair kernel, for problems of few 256 x 256 tiles and
+   * a long k loop, with `workspace` of `svodb_linear_workspace_bytes` bytes (256-byte
+   * aligned). Here the CTA that brings a tile's last piece merges them in piece order
+   * inside the same launch. A call the split kernel does not cover runs unsplit. */
+  int32_t k_splits;
+  void* workspace;
+  size_t workspace_bytes;
 } svodb_linear_opts;
+
+/* Bytes of `workspace` a split-K linear of m rows, n columns needs (0 for k_splits <= 1). */
+size_t svodb_linear_workspace_bytes(int64_t m, int64_t n, int32_t k_splits);
 
 /* `ops::linear(x, w, opts)` (tk/src/ops/linear.rs:63-191):
  * y[lead..., N] = scale*act(x[lead..., K] . w[N,K]^T + bias) + residual. */

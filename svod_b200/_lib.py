@@ -51,6 +51,9 @@ class LinearOpts(C.Structure):
         ("rope_head_dim", C.c_int32),
         ("into_at", C.c_int64),
         ("qkv", C.c_void_p),  # const svodb_qkv_opts* (QkvOpts is declared below)
+        ("k_splits", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -172,6 +175,7 @@ SYMBOLS = [
     ("svodb_plan_free", None, [C.c_void_p]),
     ("svodb_linear", C.c_int, [TensorP, TensorP, C.POINTER(LinearOpts), TensorP, C.c_void_p]),
     ("svodb_attention_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    ("svodb_linear_workspace_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int32]),
     ("svodb_attention", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
     ("svodb_attention_splits_noalloc", C.c_int, [TensorP, TensorP, TensorP, C.POINTER(AttnOpts), TensorP, C.c_void_p]),
     ("svodb_attention_packed", C.c_int, [TensorP, C.c_int32, C.c_int32, C.POINTER(AttnOpts), TensorP, C.c_void_p]),

@@ -493,6 +493,25 @@ int svodb_linear(const svodb_tensor* x, const svodb_tensor* w, const svodb_linea
     if (any && !contiguous(y))
       return fail(SVODB_ERR_GRAPH, "%s: the qkv prologue outside the kernel needs a contiguous y", OP);
   }
+  if (qo == nullptr && opts->k_splits > 1) {
+    // split-K where the caller asked for it and the split kernel covers the call;
+    // everything else runs its k loop in one piece
+    GemmArgs sk = a;
+    sk.k_splits = opts->k_splits;
+    sk.workspace = opts->workspace;
+    sk.workspace_bytes = opts->workspace_bytes;
+    const size_t need = gemm_splitk_workspace_bytes(a.m, a.n, opts->k_splits);
+    if (opts->workspace == nullptr || opts->workspace_bytes < need)
+      return fail(SVODB_ERR_WORKSPACE, "%s: %d k splits need %zu workspace bytes", OP, opts->k_splits, need);
+    if (gemm_tc2_splitk_covers(sk)) {
+      int rc = launch_gemm_tc2_splitk(sk, s, cfg, sizeof cfg);
+      if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
+      if (rc == 0) {
+        chose_kernel(OP, "gemm", cfg);
+        return check_launch(OP);
+      }
+    }
+  }
   if (a.force_bn == 512 ? gemm_tc2_covers(a) : (a.force_bn == 0 && gemm_tc2_preferred(a))) {
     int rc = launch_gemm_tc2(a, s, cfg, sizeof cfg);
     if (rc < 0) return fail(SVODB_ERR_LAUNCH, "%s: the tensor map or kernel attributes were rejected", OP);
@@ -728,6 +747,10 @@ int attend(const char* OP, const svodb_tensor* q, const svodb_tensor* k, const s
 }
 
 }  // namespace
+
+size_t svodb_linear_workspace_bytes(int64_t m, int64_t n, int32_t k_splits) {
+  return gemm_splitk_workspace_bytes(m, n, k_splits);
+}
 
 size_t svodb_attention_workspace_bytes(int64_t batch, int64_t t, int64_t heads, int64_t d, int32_t splits) {
   if (splits <= 1) return 0;

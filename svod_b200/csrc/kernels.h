@@ -193,7 +193,18 @@ struct GemmArgs {
   int dtype;
   uint32_t* status;
   int force_bn;  // 0 = the launcher's choice; 64/128/256 = that tile width on one CTA; 512 = the CTA-pair kernel
+  // Split-K on the CTA-pair kernel (tk/src/kernels/gemm.rs:454-466,750-808): > 1 =
+  // that many splits of the k loop, f32 blocks and tile counters in `workspace`.
+  int k_splits;
+  void* workspace;
+  size_t workspace_bytes;
 };
+// Workspace bytes of a split-K GEMM: [tiles][2] counters, then [tiles][splits][2][128][256] f32.
+size_t gemm_splitk_workspace_bytes(int64_t m, int64_t n, int k_splits);
+// Whether the split-K instantiation takes the call (plain epilogue: bias, activation,
+// scale, residual; no gate, no rotation, no per-head store), workspace included.
+bool gemm_tc2_splitk_covers(const GemmArgs& a);
+int launch_gemm_tc2_splitk(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 int launch_gemm_generic(const GemmArgs& a, cudaStream_t s);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t s, char* cfg, size_t cfg_len);
 bool gemm_tc_covers(const GemmArgs& a);

@@ -68,6 +68,10 @@ class Linear:
     # of q and k, rotation) applied in this projection's store; the result stays
     # the packed `[B, T, (H + 2*Hkv)*D]` projection for `attention_packed`.
     qkv: Optional["Qkv"] = None
+    # Split-K (the reference's tail split + merge, tk/src/kernels/gemm.rs:454-466,750-808):
+    # None = this module's choice (`auto_k_splits`: one piece), 0 / 1 = the k loop in one
+    # piece, > 1 = that many pieces on the CTA-pair kernel. The f32 workspace is allocated here.
+    k_splits: Optional[int] = None
 
 
 @dataclass
@@ -201,6 +205,16 @@ def device_status() -> None:
 
 
 # --------------------------------------------------------------------------- linear
+def auto_k_splits(m: int, n: int, k: int, opts: "Linear", dtype) -> int:
+    """Pieces of the k loop when the caller leaves the choice here: always one.
+    Measured on every one-wave shape of the GEMM sweep, the split kernel is slower
+    than the unsplit one (512 x 4096 x 4096: 29 us in two pieces against 21 us;
+    512 x 1024 x 4096: 25 us in four against 19 us): what a piece saves in its k
+    loop, the f32 blocks' trip through L2 and the merge cost again. A caller (or a
+    tuned config) that knows better passes `k_splits`."""
+    return 1
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, opts: Optional[Linear] = None) -> torch.Tensor:
     """`ops::linear` (tk/src/ops/linear.rs:63-191): `x [lead..., K] . w [N, K]^T`
     with the epilogue `opts`."""
@@ -236,6 +250,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, opts: Optional[Linear] = None) -> t
         qo = _qkv_opts(opts.qkv, keep)
         keep.append(qo)
         o.qkv = C.cast(C.pointer(qo), C.c_void_p)
+    m = x.numel() // max(1, x.shape[-1])
+    splits = opts.k_splits if opts.k_splits is not None else auto_k_splits(m, n, x.shape[-1], opts, x.dtype)
+    if splits and splits > 1:
+        need = lib.svodb_linear_workspace_bytes(m, n, splits)
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=x.device)
+        keep.append(ws)
+        o.k_splits, o.workspace, o.workspace_bytes = splits, ws.data_ptr(), need
     xd, wd, yd = _desc(x), _desc(w), _desc(y)
     _check(lib.svodb_linear(_p(xd), _p(wd), C.byref(o), _p(yd), _stream()))
     return opts.into[0] if opts.into is not None else y

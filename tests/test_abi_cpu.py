@@ -34,6 +34,10 @@ def test_version_and_status_strings_without_a_device():
     assert lib.svodb_last_error() is not None
     assert lib.svodb_attention_workspace_bytes(2, 5, 4, 64, 3) == 4 * 3 * 2 * 5 * 4 * (64 + 2)
     assert lib.svodb_attention_workspace_bytes(2, 5, 4, 64, 1) == 0
+    # split-K: [tiles][2] counters rounded up to 256 bytes, then [tiles][splits][2][128][256] f32
+    assert lib.svodb_linear_workspace_bytes(512, 4096, 2) == 256 + 32 * 2 * 2 * 128 * 256 * 4
+    assert lib.svodb_linear_workspace_bytes(700, 1000, 3) == 256 + 12 * 3 * 2 * 128 * 256 * 4
+    assert lib.svodb_linear_workspace_bytes(512, 4096, 1) == 0
 
 
 def test_struct_layouts_match_the_header():

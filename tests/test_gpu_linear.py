@@ -341,3 +341,63 @@ def test_rope_of_64_wide_heads_on_the_cta_pair_kernel(dt, B, T, k, heads, extra)
     finally:
         lib.svodb_config_set(key, 0)
     assert max_abs(got, one) == 0.0
+
+
+SPLIT_K_CASES = [
+    # (m, n, k, dtype, k_splits (None = the op layer's choice), epilogue)
+    (512, 4096, 4096, O.BF16, 2, dict(bias=True, act=1)),               # the sweep's one-wave shape: 32 tiles x 2 pieces
+    (512, 1024, 2048, O.BF16, 4, dict(bias=True, residual=True, scale=0.5)),
+    (700, 1000, 2240, O.BF16, 3, dict(bias=True, act=3, residual=True)),  # ragged rows and columns, 35 k-blocks in 3 uneven pieces
+    (256, 512, 4096, O.F16, 8, dict()),                                   # one pair tile a column block, 8 pieces
+    (1024, 768, 3072, O.F16, 6, dict(act=2, residual=True)),              # 4 x 3 tiles x 6 pieces = 72 items on 74 pairs
+]
+
+
+@pytest.mark.parametrize("m,n,k,dt,splits,kw", SPLIT_K_CASES)
+def test_split_k_matches_the_oracle_and_the_unsplit_kernel(m, n, k, dt, splits, kw):
+    """The reference's tail split + merge (tk/src/kernels/gemm.rs:454-466,750-808):
+    f32 partials of pieces of the k loop, merged in piece order with the epilogue
+    applied once. Same tolerance as the unsplit GEMM; two runs are bit-equal."""
+    rng = np.random.default_rng(m + n + k)
+    x = O.round_to(dt, rng.standard_normal((m, k)))
+    w = O.round_to(dt, rng.standard_normal((n, k)) / np.sqrt(k))
+    b = O.round_to(dt, rng.standard_normal(n)) if kw.get("bias") else None
+    r = O.round_to(dt, rng.standard_normal((m, n))) if kw.get("residual") else None
+    want = O.linear(x, w, b, act=kw.get("act", 0), residual=r, scale=kw.get("scale"), dtype=dt)
+
+    def run(k_splits):
+        o = ops.Linear(bias=dev(b, dt) if b is not None else None, act=ops.Act(kw.get("act", 0)),
+                       residual=dev(r, dt) if r is not None else None, scale=kw.get("scale"), k_splits=k_splits)
+        return host(ops.linear(dev(x, dt), dev(w, dt), o))
+
+    got = run(splits)
+    chosen = ops.chosen()
+    assert f"k_splits:{splits}" in chosen, chosen
+    assert rel_close(got, want, 1.6e-2)
+    assert mean_rel(got, want) < 5e-3
+    assert max_abs(run(splits), got) == 0.0          # the merge order does not depend on who came last
+    one = run(1)
+    assert "k_splits" not in ops.chosen()
+    assert rel_close(got, one, 1.6e-2)
+
+
+def test_split_k_is_the_callers_choice_and_never_splits_a_gated_projection():
+    dt = torch.bfloat16
+    # left to the op layer, the k loop stays in one piece (the split kernel measured slower)
+    assert ops.auto_k_splits(512, 4096, 4096, ops.Linear(), dt) == 1
+    x = torch.randn(512, 2048, device="cuda").to(dt)
+    w = (torch.randn(1024, 2048, device="cuda") * 0.02).to(dt)
+    ops.linear(x, w, ops.Linear())
+    assert "k_splits" not in ops.chosen()
+    # asked for on a gated projection: the call runs unsplit (tk/src/kernels/gemm.rs:459-462)
+    ops.linear(x, w, ops.Linear(gated=True, act=ops.Act.SILU, k_splits=4))
+    assert "k_splits" not in ops.chosen()
+    # asked for without a workspace through the C ABI: refused, not run
+    from svod_b200 import _lib as L
+    import ctypes as C
+    y = torch.empty(512, 1024, device="cuda", dtype=dt)
+    o = L.LinearOpts()
+    o.k_splits = 2
+    xd, wd, yd = ops._desc(x), ops._desc(w), ops._desc(y)
+    rc = L.load().svodb_linear(ops._p(xd), ops._p(wd), C.byref(o), ops._p(yd), ops._stream())
+    assert rc == L.ERR_WORKSPACE
