@@ -814,6 +814,25 @@ def sweep(args):
                 print(json.dumps({"case": f"decode B{B} T{T} Tk{Tk} H{H}/{Hk} D{D}", "splits": splits, **row}), flush=True)
         ops.device_status()
         return
+    if args.sweep == "split-k":
+        # the one-wave shapes with a long k loop: the k loop in one piece (the default) against 2 / 4 / 8 pieces
+        for (m, n, k) in [(512, 4096, 4096), (512, 1024, 4096), (1024, 4096, 4096), (2048, 1024, 3072)]:
+            x = (torch.randn(m, k, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+            w = (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+            b = (torch.randn(n, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+            ref = None
+            for pieces in (1, 2, 4, 8):
+                o = ops.Linear(bias=b, act=ops.Act.GELU, k_splits=pieces)
+                out = ops.linear(x, w, o)
+                ch = ops.chosen()
+                ref = out.float() if ref is None else ref
+                ms = time_graphed(lambda: ops.linear(x, w, o), 10)
+                print(json.dumps({"case": f"gemm bias+gelu M{m} N{n} K{k}", "k_splits": pieces, "us": round(ms * 1e3, 1),
+                                  "tflops": round(2 * m * n * k / ms / 1e9, 1),
+                                  "max_abs_vs_unsplit": float((out.float() - ref).abs().max()),
+                                  "chosen": ch.split("kernel gemm ")[-1]}), flush=True)
+        ops.device_status()
+        return
     if args.sweep == "attention-f32":
         B, H, T, D = 2, 8, 512, 64
         q, k, v = (torch.randn(B, T, H, D, generator=g, device="cuda") for _ in range(3))
@@ -861,7 +880,7 @@ def main():
     ap.add_argument("--kernel-case", default=None, choices=["flash_attention", "gemm", "gemm_gelu", "rms_norm", "heads"],
                     help="run a few launches of one kernel on a small case (for profiler captures) and exit")
     ap.add_argument("--case-batch", type=int, default=4)
-    ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32", "decode"],
+    ap.add_argument("--sweep", default=None, choices=["gemm", "attention-f32", "decode", "split-k"],
                     help="time the kernel-level baseline configurations (one JSON line per case) and exit")
     args = ap.parse_args()
     if args.kernel_case:
