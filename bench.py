@@ -568,7 +568,8 @@ def gpu_arm(args):
                   "global_batch": batch, "e2e_tokens_per_s": batch * seq / (sm["e2e_ms"] * 1e-3),
                   "n1_ms_per_step": ms_step, "speedup_vs_n1": ms_step / s_ms, "efficiency_vs_n1": ms_step / s_ms / world,
                   "note": ("one batch of ragged rows dealt longest-first round-robin (shard_rows); n1 = this run's "
-                           "own full-batch step on one GPU (the weak pass); all-gather inside the captured graph")}
+                           "own full-batch step on one GPU (the weak pass: the same work, since a Qwen3 row's length "
+                           "only moves its pooled position); all-gather inside the captured graph")}
         if rank == 0:
             undone = E.unshard_rows(srun.gathered, shards)   # back to the batch's own row order
             strong["matches_one_gpu_rows"] = bool(torch.equal(undone, full_rows))
