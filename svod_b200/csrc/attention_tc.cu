@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     u_lo = r1.lo, u_hi = r1.hi;
   }
 
-  // Register budget: the loader / MMA / mask warpgroup gives registers back to
+  // Registers: the loader / MMA / mask warpgroup gives registers back to
   // the two softmax warpgroups.
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
