@@ -401,3 +401,22 @@ def test_split_k_is_the_callers_choice_and_never_splits_a_gated_projection():
     xd, wd, yd = ops._desc(x), ops._desc(w), ops._desc(y)
     rc = L.load().svodb_linear(ops._p(xd), ops._p(wd), C.byref(o), ops._p(yd), ops._stream())
     assert rc == L.ERR_WORKSPACE
+
+
+def test_device_gelu_is_within_5e_6_of_erf_gelu_on_a_dense_grid():
+    """The device's erf-GELU (`max(x,0) - a*2^P(a)`, one exponential) seen at f32
+    precision: an f32 linear with an identity weight returns gelu(x) unrounded
+    (the exact generic kernel shares `gelu_f` with the tile kernels' epilogues)."""
+    n = 256
+    x = np.linspace(-9.0, 9.0, 64 * n, dtype=np.float32).reshape(64, n)
+    w = np.eye(n, dtype=np.float32)
+    got = ops.linear(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), ops.Linear(act=ops.Act.GELU))
+    assert "graph" in ops.chosen()
+    err = np.abs(got.cpu().numpy().astype(np.float64) - O.gelu_erf(x.astype(np.float64)))
+    assert err.max() < 5e-6
+    # and the tile kernel's epilogue, through bf16 rounding: within half a bf16 step of the pinned form
+    xb = O.round_to(O.BF16, x)
+    gb = host(ops.linear(dev(xb, O.BF16), dev(w, O.BF16), ops.Linear(act=ops.Act.GELU)))
+    assert "kernel gemm" in ops.chosen()
+    want = O.round_to(O.BF16, O.gelu_as(xb))
+    assert np.max(np.abs(gb - want) / np.maximum(np.abs(want), 1e-2)) < 2.0 ** -7
