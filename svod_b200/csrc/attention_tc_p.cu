@@ -47,10 +47,12 @@ using namespace fa_parts;
 // Queue heads: items handed out so far by a running launch, one per (device,
 // stream) pair, zeroed on the stream just before each launch.
 constexpr int kQueueSlots = 256;
+// Output staging of the softmax warps: a 32-row x 64-column slab each, stored by TMA.
+constexpr int kOutStageBytes = 8 * 32 * 128;
 template <int D>
 constexpr size_t smem_bytes_p() {
   using C = FaCfg<D>;
-  return 1024 + (size_t)2 * C::kQTileBytes + (size_t)2 * C::kStages * C::kKvBytes + 512;
+  return 1024 + (size_t)2 * C::kQTileBytes + (size_t)2 * C::kStages * C::kKvBytes + kOutStageBytes + 512;
 }
 __device__ int g_next_item[kQueueSlots];
 
@@ -155,12 +157,52 @@ struct Work {
   int u_lo, u_hi;    // the union of the two ranges: the blocks the loader brings
 };
 
+// The read-out of one tile's O by one softmax warp (32 rows): 64 columns at a time
+// through the warp's slab — both 32-column halves read from tensor memory at once,
+// scaled by 1/l, packed into the swizzled rows (16-byte chunk c of row r at
+// c ^ (r & 7)) — and one TMA store per 64 columns, which writes whole 128-byte
+// lines and cuts rows past T and columns past the real head dim by itself. Not
+// inlined: the block loop's registers and schedule stay what they are without it.
+template <typename T, int D>
+__device__ __noinline__ void store_o_slab(uint32_t o_tmem, float inv, uint8_t* slab, int lane, const CUtensorMap* tmap_o,
+                                          int h, int row0, int b, int d_real, bool rows_live) {
+  uint8_t* srow = slab + lane * 128;
+#pragma unroll 1
+  for (int c = 0; c < D; c += 64) {
+    uint32_t oa[32], ob[32];
+    tmem_ld32(o_tmem + c, oa);
+    tmem_ld32(o_tmem + c + 32, ob);
+    if (lane == 0) tma_store_wait_read();  // the slab's previous store has read it
+    __syncwarp();
+    tmem_ld_wait_for(oa);
+    tmem_ld_wait_for(ob);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      uint32_t wv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = (v & 3) * 8 + 2 * e;
+        wv[e] = v < 4 ? Elem<T>::pack(__uint_as_float(oa[k]) * inv, __uint_as_float(oa[k + 1]) * inv)
+                      : Elem<T>::pack(__uint_as_float(ob[k]) * inv, __uint_as_float(ob[k + 1]) * inv);
+      }
+      *reinterpret_cast<uint4*>(srow + ((v ^ (lane & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && rows_live && c < d_real) {
+      tma_store_4d(tmap_o, slab, c, h, row0, b);
+      tma_store_commit();
+    }
+  }
+}
+
 // EXTRAS = key splits and / or an additive bias: a separate instantiation, so that
 // the plain kernel's inner loop carries neither their registers nor their branches.
 template <typename T, int D, bool EXTRAS>
 __global__ void __launch_bounds__(kThreadsFa, 1)
     attention_tc_p_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                          const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const int n_items,
+                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                          const FaParams p, const int n_items,
                           const int tail_groups, int* const queue) {
   using C = FaCfg<D>;
   constexpr int S = C::kStages;
@@ -172,7 +214,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   uint8_t* q_s = smem;                         // [2][QB]
   uint8_t* k_s = q_s + 2 * QB;                 // [S][KB]
   uint8_t* v_s = k_s + S * KB;                 // [S][KB]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + S * KB);
+  uint8_t* o_stage = v_s + S * KB;             // [8 softmax warps][32 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(o_stage + kOutStageBytes);
   uint64_t* q_full = bars;                     // [2]
   uint64_t* q_empty = bars + 2;                // [2]
   uint64_t* k_full = bars + 4;                 // [S]
@@ -716,30 +759,25 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         }
         tc_fence_after();
         const float inv = l_run == 0.f ? 0.f : 1.0f / l_run;
+        if (EXTRAS && oprow != nullptr) {
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
-          uint32_t orr[32];
-          tmem_ld32(o_tmem + c, orr);
-          tmem_ld_wait();
-          if (EXTRAS && row_ok && oprow != nullptr) {
+          for (int c = 0; c < D; c += 32) {
+            uint32_t orr[32];
+            tmem_ld32(o_tmem + c, orr);
+            tmem_ld_wait();
+            if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              if (c + v * 4 >= p.d_real) break;
-              *reinterpret_cast<uint4*>(oprow + c + v * 4) =
-                  make_uint4(orr[v * 4], orr[v * 4 + 1], orr[v * 4 + 2], orr[v * 4 + 3]);
-            }
-          } else if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (c + v * 8 >= p.d_real) break;  // padded head dim: nothing past the real columns
-              uint32_t wv[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                wv[e] = Elem<T>::pack(__uint_as_float(orr[v * 8 + 2 * e]) * inv,
-                                      __uint_as_float(orr[v * 8 + 2 * e + 1]) * inv);
-              stg128(orow + c + v * 8, make_uint4(wv[0], wv[1], wv[2], wv[3]));
+              for (int v = 0; v < 8; ++v) {
+                if (c + v * 4 >= p.d_real) break;
+                *reinterpret_cast<uint4*>(oprow + c + v * 4) =
+                    make_uint4(orr[v * 4], orr[v * 4 + 1], orr[v * 4 + 2], orr[v * 4 + 3]);
+              }
             }
           }
+        } else {
+          const int64_t row0 = i_first + quarter * 32;
+          store_o_slab<T, D>(o_tmem, inv, o_stage + (warp - 4) * (32 * 128), lane, &tmap_o, h, (int)row0, (int)b,
+                             p.d_real, row0 < p.t);
         }
         // O is read out: the next live item's first P.V may overwrite it
         tc_fence_before();
@@ -761,6 +799,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
       if (p.lse != nullptr && row_ok)
         p.lse[(b * p.heads + h) * p.t + row] = l_run == 0.f ? -INFINITY : kLn2F * (m_run + log2f(l_run));
     }
+    if (lane == 0) tma_store_wait_all();  // the slab stays put until its last store has read it
   }
 
   tc_fence_before();
@@ -819,6 +858,14 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     if (!make_tmap(&tk, a.k, a.dtype, 4, dims, stk, kvbox)) return -1;
     if (!make_tmap(&tv, a.v, a.dtype, 4, dims, stv, kvbox)) return -1;
   }
+  CUtensorMap to = tq;
+  if (a.o != nullptr) {
+    // the output as 32-row x 64-column boxes, one per softmax warp and store
+    const uint32_t obox[4] = {64, 1, 32, 1};
+    const uint64_t dims[4] = {(uint64_t)a.d, (uint64_t)a.heads, (uint64_t)a.t, (uint64_t)a.batch};
+    const uint64_t st[3] = {(uint64_t)a.o_sh, (uint64_t)a.o_st, (uint64_t)a.o_sb};
+    if (!make_tmap(&to, a.o, a.dtype, 4, dims, st, obox)) return -1;
+  }
   // the attribute belongs to the device's copy of the kernel: once per device
   static bool attr_seen[64] = {};
   int attr_dev = 0;
@@ -874,7 +921,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
     tail_groups = (int)(want < groups ? want : groups);
   }
   if (cudaMemsetAsync(head, 0, sizeof(int), s) != cudaSuccess) return -1;
-  attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, smem_bytes_p<D>(), s>>>(tq, tk, tv, p, (int)items,
+  attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, smem_bytes_p<D>(), s>>>(tq, tk, tv, to, p, (int)items,
                                                                                   tail_groups, head);
   if (cfg != nullptr)
     snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages,
