@@ -43,7 +43,12 @@ struct FaParams {
   const int32_t* seg_start;
   const int32_t* row_map;  // `ops::Cache`: cache row of batch lane b, or null
   float* lse;
-  int n_qt;  // query tile pairs per (head, batch)
+  int n_qt;  // work items per (head or head pair, batch): pairs of 128-row tiles, or 128-row tiles when pair_heads
+  // How an item's two query tiles are chosen (persistent kernel): 0 = two consecutive
+  // 128-row tiles of one head; 1 = the SAME 128-row tile of two consecutive query
+  // heads that share a KV head (grouped-query attention with an even group), so that
+  // under a causal mask or a window both tiles walk the same key blocks and end together.
+  int pair_heads;
   int d_real;  // the tensors' head dim (a multiple of 8, <= D): columns past it are TMA zero fill and never stored
   // Key splits (persistent kernel): split s of `splits` takes an equal share of the
   // key blocks and writes its unnormalised state instead of the output:

@@ -61,7 +61,8 @@ struct Item {
   int split;  // key split of this item (0 without splits)
 };
 
-// Work item w in queue order: batch, KV head, query head of the group, then
+// Work item w in queue order: batch, KV head, query head of the group (or head
+// pair, when an item is one tile of two heads: `heads` then counts pairs), then
 // query tile pairs from the last (the heaviest under a causal mask) to the first,
 // so that the items in flight at one time share few KV heads and their keys stay
 // in L2. The last `tail_groups` (batch, KV head) groups are interleaved instead:
@@ -151,7 +152,8 @@ __device__ __forceinline__ void scan_mask_row(const FaParams& p, int64_t b, int 
 struct Work {
   int valid;
   int h, hk, split;
-  int b, i0;         // batch lane, first query row of the pair of tiles (both below 2^31)
+  int b, i0;         // batch lane, first query row of the item (both below 2^31); tile i covers rows
+                     // i0 + i*128 of head h, or with paired heads rows i0 of head h + i
   int len, general;  // the mask context (`Ctx`): visible key bound, whether to consult the bitmask
   Range r0, r1;
   int u_lo, u_hi;    // the union of the two ranges: the blocks the loader brings
@@ -270,10 +272,10 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
   auto plan = [&](const Item& it, const MaskRow& mrow) -> Work {
     Work w;
     w.valid = it.valid;
-    w.h = it.h;
-    w.hk = it.h / (p.heads / p.kv_heads);
+    w.h = p.pair_heads ? 2 * it.h : it.h;
+    w.hk = w.h / (p.heads / p.kv_heads);
     w.b = it.b;
-    w.i0 = it.qt * 2 * kBQ;
+    w.i0 = it.qt * (p.pair_heads ? kBQ : 2 * kBQ);
     Ctx ctx;
     ctx.len = p.tk;
     ctx.general_mask = 0;
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
     w.len = (int)ctx.len;
     w.general = ctx.general_mask;
     w.r0 = tile_range(p, ctx, w.b, w.i0);
-    w.r1 = tile_range(p, ctx, w.b, (int64_t)w.i0 + kBQ);
+    w.r1 = tile_range(p, ctx, w.b, (int64_t)w.i0 + (p.pair_heads ? 0 : kBQ));
     w.split = it.split;
     if (EXTRAS && p.splits > 1) {
       // this split's share of the key blocks
@@ -334,7 +336,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
           if (lane == 0 && mbar_wait(&item_empty[slot], ((n_it >> 1) & 1) ^ 1, p.status)) wi = atomicAdd(queue, 1);
           wi = __shfl_sync(0xffffffffu, wi, 0);
           if (wi < 0) break;  // the wait ran out
-          Item it = decode_item(wi, n_items, p.n_qt, p.heads, p.kv_heads, tail_groups, EXTRAS ? p.splits : 1);
+          Item it = decode_item(wi, n_items, p.n_qt, p.pair_heads ? p.heads / 2 : p.heads, p.kv_heads, tail_groups,
+                                EXTRAS ? p.splits : 1);
           // The loader alone scans a bool key mask row (all its lanes, once per change
           // of batch lane, while it runs ahead of the other warps) and hands what it
           // found to them with the item.
@@ -359,7 +362,8 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
               ++q_items[i];
               mbar_expect_tx(&q_full[i], QB);
               for (int c = 0; c < D / 64; ++c)
-                tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, w.h, w.i0 + i * kBQ, w.b);
+                tma_load_4d(q_s + i * QB + c * (128 * 128), &tmap_q, &q_full[i], c * 64, w.h + (p.pair_heads ? i : 0),
+                            w.i0 + (p.pair_heads ? 0 : i * kBQ), w.b);
             }
           }
           const int kv_b = p.row_map != nullptr ? p.row_map[w.b] : w.b;
@@ -533,9 +537,9 @@ __global__ void __launch_bounds__(kThreadsFa, 1)
         continue;
       }
       const Range r = i == 0 ? w.r0 : w.r1;
-      const int h = w.h;
+      const int h = w.h + (p.pair_heads ? i : 0);
       const int64_t b = w.b;
-      const int64_t i_first = (int64_t)w.i0 + (int64_t)i * kBQ;
+      const int64_t i_first = (int64_t)w.i0 + (p.pair_heads ? 0 : (int64_t)i * kBQ);
       const int64_t row = i_first + quarter * 32 + lane;
       const bool row_ok = row < p.t;
       const int64_t i_last = (i_first + kBQ - 1 < p.t - 1) ? i_first + kBQ - 1 : p.t - 1;
@@ -840,6 +844,18 @@ int* queue_head(cudaStream_t stream) {
   return base[dev] + it->second;
 }
 
+// An item is one 128-row tile of two query heads (instead of two tiles of one head)
+// whenever grouped-query attention gives every KV head an even number of query heads.
+bool pairs_heads(const AttnArgs& a) {
+  const int group = a.kv_heads > 0 ? a.heads / a.kv_heads : 0;
+  return group >= 2 && group % 2 == 0;
+}
+
+int64_t item_count(const AttnArgs& a, int splits) {
+  if (pairs_heads(a)) return ((a.t + kBQ - 1) / kBQ) * (int64_t)(a.heads / 2) * a.batch * splits;
+  return ((a.t + 2 * kBQ - 1) / (2 * kBQ)) * (int64_t)a.heads * a.batch * splits;
+}
+
 template <typename T, int D, bool EXTRAS>
 int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   using C = FaCfg<D>;
@@ -896,7 +912,8 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.seg_start = a.seg_start;
   p.row_map = a.row_map;
   p.lse = a.lse;
-  p.n_qt = (int)((a.t + 2 * kBQ - 1) / (2 * kBQ));
+  p.pair_heads = pairs_heads(a) ? 1 : 0;
+  p.n_qt = (int)(p.pair_heads ? (a.t + kBQ - 1) / kBQ : (a.t + 2 * kBQ - 1) / (2 * kBQ));
   p.d_real = a.d;
   p.splits = a.splits > 1 ? a.splits : 1;
   p.batch = a.batch;
@@ -905,7 +922,8 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   p.bias_per_batch = a.bias_per_batch;
   p.inv_scale = 1.0f / a.scale;
   p.status = a.status;
-  const int64_t items = (int64_t)p.n_qt * a.heads * a.batch * p.splits;
+  const int item_heads = p.pair_heads ? a.heads / 2 : a.heads;
+  const int64_t items = (int64_t)p.n_qt * item_heads * a.batch * p.splits;
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -916,7 +934,7 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   int tail_groups = 0;
   if (a.causal) {
     const int64_t groups = (int64_t)a.batch * a.kv_heads;
-    const int64_t per_kv = (int64_t)(a.heads / a.kv_heads) * p.n_qt;
+    const int64_t per_kv = (int64_t)(item_heads / a.kv_heads) * p.n_qt;
     const int64_t want = (6 * (int64_t)sms + per_kv - 1) / per_kv;
     tail_groups = (int)(want < groups ? want : groups);
   }
@@ -924,7 +942,9 @@ int run_p(const AttnArgs& a, cudaStream_t s, char* cfg, size_t cfg_len) {
   attention_tc_p_kernel<T, D, EXTRAS><<<grid, kThreadsFa, smem_bytes_p<D>(), s>>>(tq, tk, tv, to, p, (int)items,
                                                                                   tail_groups, head);
   if (cfg != nullptr)
-    snprintf(cfg, cfg_len, "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d}", 2 * kBQ, kBKV, a.d, C::kStages,
+    snprintf(cfg, cfg_len, p.pair_heads ? "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d,head_pairs:1}"
+                                        : "{bq:%d,bkv:%d,d:%d,stages:%d,splits:%d,persistent:%d}",
+             2 * kBQ, kBKV, a.d, C::kStages,
              p.splits, grid);
   return 0;
 }
@@ -940,8 +960,7 @@ bool attention_tc_p_covers(const AttnArgs& a) {
   plain.bias = nullptr;
   if (!attention_tc_covers(plain)) return false;
   const int splits = a.splits > 1 ? a.splits : 1;
-  const int64_t n_qt = (a.t + 2 * kBQ - 1) / (2 * kBQ);
-  const int64_t items = n_qt * a.heads * a.batch * splits;
+  const int64_t items = item_count(a, splits);
   if (items >= 0x7fffffffLL) return false;
   if (a.splits > 1 || a.bias != nullptr) {
     // partial rows are written 16 bytes at a time; the score rows of the bias are read per thread
