@@ -415,8 +415,9 @@ PERSISTENT_CASES = [
 
 @pytest.mark.parametrize("name,D,kw", PERSISTENT_CASES, ids=[c[0] for c in PERSISTENT_CASES])
 def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D, kw):
-    """192 work items (B4 x H8 x 6 tile pairs of a ragged T = 1300) on 148 SMs run
-    the persistent kernel: same numbers as the oracle within tolerance and as the
+    """176 work items (B4 x 4 head pairs x 11 tiles of a ragged T = 1300: with two
+    query heads a KV head an item is one 128-row tile of both) on 148 SMs run the
+    persistent kernel: same numbers as the oracle within tolerance and as the
     one-item kernel bit for bit."""
     from svod_b200 import _lib as L
     dt, B, T, H, Hkv = O.BF16, 4, 1300, 8, 4
@@ -440,7 +441,7 @@ def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D
     want = O.attention(q, k, v, dtype=dt, **okw)
     Q, K, V = dev(q, dt), dev(k, dt), dev(v, dt)
     got = host(ops.attention(Q, K, V, a))
-    assert "persistent" in ops.chosen(), ops.chosen()
+    assert "persistent" in ops.chosen() and "head_pairs:1" in ops.chosen(), ops.chosen()
     ops.device_status()
     assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
     lib = L.load()
@@ -453,6 +454,30 @@ def test_persistent_attention_matches_the_oracle_and_the_one_item_kernel(name, D
     assert np.array_equal(got, one)
     again = host(ops.attention(Q, K, V, a))  # a second launch takes another queue slot
     assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("H,Hkv,pairs", [(6, 6, False), (6, 2, False), (8, 2, True)])
+def test_persistent_attention_pairs_rows_or_heads(H, Hkv, pairs):
+    """An item's two query tiles are consecutive tiles of one head, or — when every
+    KV head serves an even number of query heads — the same tile of two heads.
+    Either way the rows come out as the one-item kernel computes them."""
+    from svod_b200 import _lib as L
+    dt, B, T, D = O.BF16, 6, 1100, 64
+    rng = np.random.default_rng(H * 10 + Hkv)
+    q, k, v = normal(rng, (B, T, H, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt), normal(rng, (B, T, Hkv, D), 1.0, dt)
+    a = ops.Attn(causal=True, window=(300, 0))
+    Q, K, V = dev(q, dt), dev(k, dt), dev(v, dt)
+    got = host(ops.attention(Q, K, V, a))
+    assert "persistent" in ops.chosen() and ("head_pairs:1" in ops.chosen()) == pairs, ops.chosen()
+    want = O.attention(q, k, v, dtype=dt, causal=True, window=(300, 0))
+    assert max_abs(got, want) < 2e-2 and mean_rel(got, want) < 5e-3
+    lib = L.load()
+    lib.svodb_config_set(b"attention|one_item", 1)
+    try:
+        one = host(ops.attention(Q, K, V, a))
+    finally:
+        lib.svodb_config_set(b"attention|one_item", 0)
+    assert np.array_equal(got, one)
 
 
 def test_persistent_attention_launches_overlapping_on_two_streams_keep_their_own_queues():
