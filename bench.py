@@ -54,7 +54,8 @@ WORKLOADS = {
 # under a profiler), and the traffic of both kernels grows in proportion to the
 # rows (every CTA works on one batch row's tiles).
 NCU_DRAM_BYTES_PER_ROW = {
-    ("qwen3", "flash_attention"): 196.7e6 / 4,   # algorithmic 100.7 MB at batch 4 (the interleaved queue tail re-reads some K/V)
+    ("qwen3", "flash_attention"): 803.5e6 / 16,  # batch 16: 562.0 MB read + 241.4 MB written against 402.7 MB algorithmic
+                                                 # (batch 4: 203.1 MB, the same 50 MB a row; K/V fetched again, L2 hit rate 73-78 %)
     ("qwen3", "gemm"): 101.7e6 / 4,              # algorithmic 96.5 MB at batch 4 (M = 16384)
 }
 
@@ -639,7 +640,7 @@ def gpu_arm(args):
             "kernel": top, "bound": "tensor", "achieved": ks[top]["tflops"], "peak": peaks["burst"],
             "unit": "TFLOP/s", "frac": ks[top]["tflops"] / peaks["burst"],
             "traffic": NCU_DRAM_BYTES_PER_ROW.get((kind, top), 0) * batch or None,
-            "traffic_note": "dram read+write bytes of one ncu capture at batch 4, scaled by rows (profiles/)",
+            "traffic_note": "dram read+write bytes of one ncu capture of the kernel at batch 16, scaled by rows (profiles/)",
             "peak_source": f"{peaks['source']} bf16 burst: the kernel is timed alone (20 launches in one graph)",
         }
         if attn_ms:
