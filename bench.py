@@ -394,7 +394,7 @@ class StackRun:
     """One plan of one stack on this rank: rows x seq, pooled rows written into this
     rank's slot of `gathered`, the all-gather captured inside the plan's graph."""
 
-    def __init__(self, model, aux_kind, rows, seq, world, rank, device):
+    def __init__(self, model, aux_kind, rows, seq, world, rank, device, gather="nccl"):
         import torch
         from svod_b200 import encoders as E
         from svod_b200 import ops
@@ -403,7 +403,14 @@ class StackRun:
         self.gathered = torch.zeros(world * rows, D, dtype=torch.float32, device=device)
         self.mine = self.gathered[rank * rows:(rank + 1) * rows]
         self.out_host = torch.empty(rows, D, dtype=torch.float32).pin_memory()
-        epilogue = (lambda: E.gather_pooled(self.mine, self.gathered)) if world > 1 else None
+        epilogue = None
+        if world > 1 and gather == "peer":
+            # the library's own all-gather: plain stores into the peers' staging buffers over NVLink
+            from svod_b200.peer import PeerGather
+            self.peer = PeerGather(rows, D)
+            epilogue = lambda: self.peer.all_gather(self.mine, self.gathered)
+        elif world > 1:
+            epilogue = lambda: E.gather_pooled(self.mine, self.gathered)
         before = ops.launches
         self.plan = E.Plan(model, rows, seq, aux_kind, out=self.mine, device=device, epilogue=epilogue)
         self._capture = lambda: self.plan.capture()
@@ -493,7 +500,8 @@ def measure_stack(kind, model, aux_kind, rows, seq, world, rank, device, args, i
     import torch
     from svod_b200 import ops
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    run = StackRun(model, aux_kind, rows, seq, world, rank, device).load(ids_host, aux_host)
+    run = StackRun(model, aux_kind, rows, seq, world, rank, device, getattr(args, "gather", "nccl")).load(ids_host,
+                                                                                                        aux_host)
     for _ in range(max(3, args.warmup)):
         run.step_resident()
     run.plan.check()
@@ -616,7 +624,9 @@ def gpu_arm(args):
                        "seq_len": seq, "parallelism": f"dp{world}",
                        "l2": "activations per step (GBs) exceed the 126 MB L2; no explicit flush",
                        "real_tokens_per_step": real_tokens * world,
-                       "collective": "all-gather of pooled rows, captured inside the step's CUDA graph" if world > 1
+                       "collective": ("all-gather of pooled rows by the library's own kernels (peer stores over NVLink), "
+                                      "captured inside the step's CUDA graph") if world > 1 and args.gather == "peer"
+                       else "NCCL all-gather of pooled rows, captured inside the step's CUDA graph" if world > 1
                        else "none at one GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -874,6 +884,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b-embed", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
+                    help="the all-gather of pooled rows at N > 1: NCCL, or the library's own peer-memory kernels")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the short XLM-RoBERTa-large and ModernBERT-base runs of the default one-GPU line")
     ap.add_argument("--reference-ops", action="store_true",

@@ -452,6 +452,39 @@ int svodb_free(void* ptr, int32_t kind);
 int svodb_copy_h2d(void* dst, const void* src, size_t bytes, void* stream);
 int svodb_copy_d2h(void* dst, const void* src, size_t bytes, void* stream);
 int svodb_stream_sync(void* stream);
+int svodb_memset(void* ptr, int32_t value, size_t bytes, void* stream);
+
+/* ---- the path's one collective over NVLink peer memory ----
+ * No counterpart in the reference (it runs on one GPU): the all-gather of pooled
+ * rows that follows `svodb_norm_pool` when the batch is dealt over several GPUs,
+ * as kernels of this library instead of a collective library's. One process per
+ * GPU. Every rank allocates (`svodb_alloc`, zeroed) a stage of
+ * `svodb_peer_stage_bytes` bytes, 256 bytes of flags and 256 bytes of local
+ * counters, exports stage and flags (`svodb_ipc_export`), the host exchanges the
+ * 64-byte handles by whatever channel it has, and each rank maps the others'
+ * (`svodb_ipc_open`; its own pointers go in at its own index). `svodb_peer_all_gather`
+ * then puts rank r's `[rows, d]` f32 block into slot r of every rank's `gathered`
+ * [world*rows, d]: a push kernel (plain stores into the peers' stages, a
+ * system-scope fence, a flag per peer) and an unstage kernel that waits for each
+ * peer's flag — `wait_polls` polls of about 256 ns (0 = a few seconds), after which
+ * the step reports SVODB_ERR_TIMEOUT through `svodb_device_status` — and copies
+ * its rows in. `mine` is normally slot `rank` of `gathered`. Both launches can be
+ * captured in a CUDA graph; ranks must reach the same step count. */
+typedef struct svodb_peer_gather {
+  int32_t world, rank;  /* world <= 8 */
+  void* stage[8];       /* rank p's stage as mapped in this process */
+  void* flags[8];       /* rank p's flags as mapped in this process */
+  void* local;          /* this rank's private counters (256 bytes, zeroed) */
+  uint32_t wait_polls;
+  int32_t phases;       /* 0 = the whole step; 1 = the push alone, 2 = the unstage alone (a host may put
+                           other work between them; every step needs both, in this order) */
+} svodb_peer_gather;
+size_t svodb_peer_stage_bytes(int32_t world, int64_t rows, int64_t d);
+int svodb_ipc_export(const void* dev_ptr, uint8_t handle[64]);
+int svodb_ipc_open(const uint8_t handle[64], void** out);
+int svodb_ipc_close(void* ptr);
+int svodb_peer_all_gather(const svodb_peer_gather* pg, const float* mine, float* gathered, int64_t rows, int64_t d,
+                          void* stream);
 
 #ifdef __cplusplus
 }

@@ -57,6 +57,18 @@ class LinearOpts(C.Structure):
     ]
 
 
+class PeerGather(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("stage", C.c_void_p * 8),
+        ("flags", C.c_void_p * 8),
+        ("local", C.c_void_p),
+        ("wait_polls", C.c_uint32),
+        ("phases", C.c_int32),
+    ]
+
+
 class AttnOpts(C.Structure):
     _fields_ = [
         ("causal", C.c_int32),
@@ -207,6 +219,12 @@ SYMBOLS = [
     ("svodb_copy_h2d", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("svodb_copy_d2h", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("svodb_stream_sync", C.c_int, [C.c_void_p]),
+    ("svodb_memset", C.c_int, [C.c_void_p, C.c_int32, C.c_size_t, C.c_void_p]),
+    ("svodb_peer_stage_bytes", C.c_size_t, [C.c_int32, C.c_int64, C.c_int64]),
+    ("svodb_ipc_export", C.c_int, [C.c_void_p, C.c_void_p]),
+    ("svodb_ipc_open", C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    ("svodb_ipc_close", C.c_int, [C.c_void_p]),
+    ("svodb_peer_all_gather", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
 ]
 
 _lib = None
