@@ -404,13 +404,20 @@ class StackRun:
         self.mine = self.gathered[rank * rows:(rank + 1) * rows]
         self.out_host = torch.empty(rows, D, dtype=torch.float32).pin_memory()
         epilogue = None
+        self.collective = "none"
         if world > 1 and gather == "peer":
-            # the library's own all-gather: plain stores into the peers' staging buffers over NVLink
+            # the library's own all-gather: plain stores into the peers' staging buffers over NVLink;
+            # if the peers' memory cannot be mapped here, every rank hears of it and all take NCCL
             from svod_b200.peer import PeerGather
-            self.peer = PeerGather(rows, D)
-            epilogue = lambda: self.peer.all_gather(self.mine, self.gathered)
-        elif world > 1:
+            try:
+                self.peer = PeerGather(rows, D)
+                epilogue = lambda: self.peer.all_gather(self.mine, self.gathered)
+                self.collective = "peer"
+            except ops.OpsError as e:
+                sys.stderr.write(f"peer gather unavailable ({e}); using NCCL\n")
+        if world > 1 and epilogue is None:
             epilogue = lambda: E.gather_pooled(self.mine, self.gathered)
+            self.collective = "nccl"
         before = ops.launches
         self.plan = E.Plan(model, rows, seq, aux_kind, out=self.mine, device=device, epilogue=epilogue)
         self._capture = lambda: self.plan.capture()
@@ -550,6 +557,7 @@ def gpu_arm(args):
     e2e_value = tokens_step / (e2e_ms * 1e-3)
     real_tokens = int(lens.sum())
     launches_per_step = run.launches_per_step
+    run_collective = run.collective
     h2d, d2h = run.h2d_bytes(), run.out_host.numel() * 4
     attn_ms, attn_launches, attn_ms_max = attention_in_step_ms(model, run) if rank == 0 else (None, 0, None)
     ops.device_status()
@@ -625,7 +633,7 @@ def gpu_arm(args):
                        "l2": "activations per step (GBs) exceed the 126 MB L2; no explicit flush",
                        "real_tokens_per_step": real_tokens * world,
                        "collective": ("all-gather of pooled rows by the library's own kernels (peer stores over NVLink), "
-                                      "captured inside the step's CUDA graph") if world > 1 and args.gather == "peer"
+                                      "captured inside the step's CUDA graph") if world > 1 and run_collective == "peer"
                        else "NCCL all-gather of pooled rows, captured inside the step's CUDA graph" if world > 1
                        else "none at one GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
@@ -884,8 +892,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b-embed", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
-                    help="the all-gather of pooled rows at N > 1: NCCL, or the library's own peer-memory kernels")
+    ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
+                    help="the all-gather of pooled rows at N > 1: the library's own peer-memory kernels (NCCL if the "
+                         "peers' memory cannot be mapped), or NCCL")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the short XLM-RoBERTa-large and ModernBERT-base runs of the default one-GPU line")
     ap.add_argument("--reference-ops", action="store_true",

@@ -45,31 +45,50 @@ class PeerGather:
         if self.world == 1:
             return
         lib = L.load()
-        stage = _alloc_zeroed(lib.svodb_peer_stage_bytes(self.world, rows, d))
-        flags = _alloc_zeroed(256)
-        local = _alloc_zeroed(256)
-        self._owned = [stage, flags, local]
-        torch.cuda.current_stream().synchronize()
-        handles = []
-        for ptr in (stage, flags):
-            h = (C.c_uint8 * 64)()
-            ops._check(lib.svodb_ipc_export(ptr, h), 0)
-            handles.append(bytes(h))
+        # Every rank must come out of this constructor the same way (with the mappings, or with
+        # an error): what can fail on one rank alone is tried first and the outcome is exchanged
+        # with the handles, so that nobody is left waiting for a rank that gave up.
+        handles, err = None, None
+        try:
+            stage = _alloc_zeroed(lib.svodb_peer_stage_bytes(self.world, rows, d))
+            flags = _alloc_zeroed(256)
+            local = _alloc_zeroed(256)
+            self._owned = [stage, flags, local]
+            torch.cuda.current_stream().synchronize()
+            handles = []
+            for ptr in (stage, flags):
+                h = (C.c_uint8 * 64)()
+                ops._check(lib.svodb_ipc_export(ptr, h), 0)
+                handles.append(bytes(h))
+        except ops.OpsError as e:
+            err = str(e)
         everyone: List[Optional[tuple]] = [None] * self.world
-        dist.all_gather_object(everyone, tuple(handles), group=group)
-        for r in range(self.world):
-            if r == self.rank:
-                self.ctx.stage[r], self.ctx.flags[r] = stage, flags
-                continue
-            for k, field in enumerate((self.ctx.stage, self.ctx.flags)):
-                out = C.c_void_p()
-                buf = (C.c_uint8 * 64).from_buffer_copy(everyone[r][k])
-                ops._check(lib.svodb_ipc_open(buf, C.byref(out)), 0)
-                self._opened.append(out.value)
-                field[r] = out.value
-        self.ctx.local = local
-        # nobody pushes into a stage before every rank has mapped and zeroed its own
-        dist.barrier(group=group)
+        dist.all_gather_object(everyone, tuple(handles) if err is None else None, group=group)
+        if err is None and all(h is not None for h in everyone):
+            try:
+                for r in range(self.world):
+                    if r == self.rank:
+                        self.ctx.stage[r], self.ctx.flags[r] = stage, flags
+                        continue
+                    for k, field in enumerate((self.ctx.stage, self.ctx.flags)):
+                        out = C.c_void_p()
+                        buf = (C.c_uint8 * 64).from_buffer_copy(everyone[r][k])
+                        ops._check(lib.svodb_ipc_open(buf, C.byref(out)), 0)
+                        self._opened.append(out.value)
+                        field[r] = out.value
+                self.ctx.local = local
+            except ops.OpsError as e:
+                err = str(e)
+        elif err is None:
+            err = "a peer could not export its buffers"
+        # the second exchange doubles as the barrier: nobody pushes into a stage before every
+        # rank has mapped and zeroed its own
+        outcomes: List[Optional[str]] = [None] * self.world
+        dist.all_gather_object(outcomes, err, group=group)
+        failed = [f"rank {r}: {o}" for r, o in enumerate(outcomes) if o is not None]
+        if failed:
+            self.close()
+            raise ops.OpsError(L.ERR_LAUNCH, "peer gather: " + "; ".join(failed))
 
     def all_gather(self, local: torch.Tensor, gathered: torch.Tensor) -> torch.Tensor:
         """`local` `[rows, d]` f32 (normally slot `rank` of `gathered`) into slot `rank`
