@@ -66,6 +66,33 @@ def test_the_protocol_with_every_rank_in_one_process(world, rows, d):
         lib.svodb_free(p, 0)
 
 
+def test_a_peer_that_never_delivers_ends_in_a_reported_timeout():
+    """The unstage of a step whose peer never pushed: the bounded wait (a flag nothing
+    sets, two thousand polls) runs out, the status word says so once, nothing is
+    copied, and the context goes on working."""
+    lib = L.load()
+    world, rows, d = 2, 4, 256
+    stage = [_alloc(lib.svodb_peer_stage_bytes(world, rows, d)) for _ in range(world)]
+    flags = [_alloc(256) for _ in range(world)]
+    local = _alloc(256)
+    c = L.PeerGather()
+    c.world, c.rank, c.wait_polls, c.phases = world, 0, 2000, 2
+    for q in range(world):
+        c.stage[q], c.flags[q] = stage[q], flags[q]
+    c.local = local
+    gathered = torch.full((world * rows, d), 5.0, device="cuda")
+    assert lib.svodb_peer_all_gather(C.byref(c), gathered.data_ptr(), gathered.data_ptr(), rows, d, ops._stream()) == L.OK
+    torch.cuda.synchronize()
+    assert lib.svodb_device_status(None) == L.ERR_TIMEOUT
+    assert lib.svodb_device_status(None) == L.OK
+    assert bool((gathered == 5.0).all())
+    x = torch.randn(8, 256, device="cuda").to(torch.bfloat16)
+    w = torch.ones(256, device="cuda", dtype=torch.bfloat16)
+    assert torch.isfinite(ops.rms_norm(x, w).float()).all()
+    for p in stage + flags + [local]:
+        lib.svodb_free(p, 0)
+
+
 WORKER = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["REPO"])
