@@ -404,22 +404,23 @@ class StackRun:
         self.mine = self.gathered[rank * rows:(rank + 1) * rows]
         self.out_host = torch.empty(rows, D, dtype=torch.float32).pin_memory()
         epilogue = None
+        self.peer = None
         self.collective = "none"
         if world > 1 and gather == "peer":
             # the library's own all-gather: plain stores into the peers' staging buffers over NVLink;
             # if the peers' memory cannot be mapped here, every rank hears of it and all take NCCL
             from svod_b200.peer import PeerGather
             try:
-                self.peer = PeerGather(rows, D)
-                epilogue = lambda: self.peer.all_gather(self.mine, self.gathered)
+                self.peer = PeerGather(rows, D).bind(self.gathered)
                 self.collective = "peer"
             except ops.OpsError as e:
                 sys.stderr.write(f"peer gather unavailable ({e}); using NCCL\n")
-        if world > 1 and epilogue is None:
+        if world > 1 and self.collective != "peer":
             epilogue = lambda: E.gather_pooled(self.mine, self.gathered)
             self.collective = "nccl"
         before = ops.launches
-        self.plan = E.Plan(model, rows, seq, aux_kind, out=self.mine, device=device, epilogue=epilogue)
+        self.plan = E.Plan(model, rows, seq, aux_kind, out=self.mine, device=device, epilogue=epilogue,
+                           gather=self.peer if self.collective == "peer" else None)
         self._capture = lambda: self.plan.capture()
         self._before = before
 
@@ -632,8 +633,9 @@ def gpu_arm(args):
                        "seq_len": seq, "parallelism": f"dp{world}",
                        "l2": "activations per step (GBs) exceed the 126 MB L2; no explicit flush",
                        "real_tokens_per_step": real_tokens * world,
-                       "collective": ("all-gather of pooled rows by the library's own kernels (peer stores over NVLink), "
-                                      "captured inside the step's CUDA graph") if world > 1 and run_collective == "peer"
+                       "collective": ("all-gather of pooled rows by the library's own kernels: the pooling kernel stores "
+                                      "its rows into the peers' staging buffers over NVLink, an unstage kernel "
+                                      "follows; both inside the step's CUDA graph") if world > 1 and run_collective == "peer"
                        else "NCCL all-gather of pooled rows, captured inside the step's CUDA graph" if world > 1
                        else "none at one GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,

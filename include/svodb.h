@@ -485,6 +485,13 @@ int svodb_ipc_open(const uint8_t handle[64], void** out);
 int svodb_ipc_close(void* ptr);
 int svodb_peer_all_gather(const svodb_peer_gather* pg, const float* mine, float* gathered, int64_t rows, int64_t d,
                           void* stream);
+/* `svodb_norm_pool` writing this rank's rows into slot `rank` of `gathered` [world*rows, D] f32
+ * and gathering the others': where the fused norm + pool kernel takes the call, that kernel
+ * itself stores each pooled row into every peer's stage and raises the flags (compute and send
+ * in one launch), and only the unstage follows; otherwise the whole gather follows. */
+int svodb_norm_pool_gather(const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b, double eps,
+                           int32_t layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
+                           int32_t normalize, const svodb_peer_gather* pg, svodb_tensor* gathered, void* stream);
 
 #ifdef __cplusplus
 }

@@ -225,6 +225,8 @@ SYMBOLS = [
     ("svodb_ipc_open", C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     ("svodb_ipc_close", C.c_int, [C.c_void_p]),
     ("svodb_peer_all_gather", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    ("svodb_norm_pool_gather", C.c_int, [TensorP, TensorP, TensorP, C.c_double, C.c_int32, TensorP, TensorP, C.c_int32,
+                                        C.c_int32, C.c_void_p, TensorP, C.c_void_p]),
 ]
 
 _lib = None

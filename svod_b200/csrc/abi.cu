@@ -1061,7 +1061,8 @@ int svodb_embed_norm(const svodb_tensor* ids, const svodb_tensor* table, const s
 namespace {
 int pool_impl(const char* OP, const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b,
               double eps, int layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
-              int32_t normalize, svodb_tensor* out, void* stream, bool fused) {
+              int32_t normalize, svodb_tensor* out, void* stream, bool fused, const PeerPush* push = nullptr,
+              bool* pushed = nullptr) {
   GUARD(OP);
   TRY(realized(OP, "hidden", hidden));
   TRY(realized(OP, "out", out));
@@ -1090,6 +1091,7 @@ int pool_impl(const char* OP, const svodb_tensor* hidden, const svodb_tensor* no
   }
   if (L == 0) return shape_err(OP, "hidden", hidden, "[B, L >= 1, D]");
   PoolArgs a{};
+  a.push = push;
   a.hidden = hidden->data;
   a.aux = aux ? aux->data : nullptr;
   a.aux_i32 = aux ? aux->dtype == SVODB_I32 : 0;
@@ -1108,9 +1110,12 @@ int pool_impl(const char* OP, const svodb_tensor* hidden, const svodb_tensor* no
   if (norm_w != nullptr) TRY(norm_operands(OP, norm_w, norm_b, D, hidden->dtype));
   EmbedNormArgs n{norm_w ? norm_w->data : nullptr, norm_b ? norm_b->data : nullptr, (float)eps, layer};
   if (launch_norm_pool(a, n, (cudaStream_t)stream)) {
-    chose_kernel(OP, "norm_pool", norm_w ? "{norm:fused}" : "{norm:none}");
+    if (pushed != nullptr) *pushed = push != nullptr && push->world > 1;
+    chose_kernel(OP, "norm_pool", norm_w ? (push != nullptr && push->world > 1 ? "{norm:fused,push:peers}" : "{norm:fused}")
+                                         : (push != nullptr && push->world > 1 ? "{norm:none,push:peers}" : "{norm:none}"));
     return check_launch(OP);
   }
+  a.push = nullptr;  // the unfused kernels below do not send
   // outside the fused kernel's rows: the norm into the caller's scratch, then the two pooling kernels
   if (norm_w != nullptr) {
     if (scratch == nullptr || scratch->data == nullptr || !same_shape(scratch, hidden) || !contiguous(scratch) ||
@@ -1140,6 +1145,43 @@ int svodb_norm_pool(const svodb_tensor* hidden, const svodb_tensor* norm_w, cons
                     int32_t normalize, svodb_tensor* out, void* stream) {
   return pool_impl("norm_pool", hidden, norm_w, norm_b, eps, layer ? 1 : 0, scratch, mask_or_lengths, mode, normalize,
                    out, stream, true);
+}
+
+int svodb_norm_pool_gather(const svodb_tensor* hidden, const svodb_tensor* norm_w, const svodb_tensor* norm_b, double eps,
+                           int32_t layer, svodb_tensor* scratch, const svodb_tensor* mask_or_lengths, int32_t mode,
+                           int32_t normalize, const svodb_peer_gather* pg, svodb_tensor* gathered, void* stream) {
+  static const char* OP = "norm_pool_gather";
+  if (pg == nullptr || gathered == nullptr || gathered->data == nullptr)
+    return fail(SVODB_ERR_SHAPE, "%s: no peer context or gathered buffer", OP);
+  if (pg->world < 1 || pg->world > 8 || pg->rank < 0 || pg->rank >= pg->world)
+    return fail(SVODB_ERR_SHAPE, "%s: world %d rank %d", OP, pg->world, pg->rank);
+  if (gathered->rank != 2 || gathered->dtype != SVODB_F32 || !contiguous(gathered) || gathered->shape[0] % pg->world != 0)
+    return shape_err(OP, "gathered", gathered, "[world * rows, D] f32");
+  const int64_t rows = gathered->shape[0] / pg->world, D = gathered->shape[1];
+  // this rank's slot of the gathered buffer is the pooling's output
+  svodb_tensor mine = *gathered;
+  mine.data = (float*)gathered->data + (int64_t)pg->rank * rows * D;
+  mine.shape[0] = rows;
+  PeerPush push{};
+  push.world = pg->world, push.rank = pg->rank;
+  if (pg->world > 1) {
+    for (int i = 0; i < pg->world; ++i) {
+      if (pg->stage[i] == nullptr || pg->flags[i] == nullptr)
+        return fail(SVODB_ERR_SHAPE, "%s: rank %d's buffers are not mapped", OP, i);
+      push.stage[i] = (float*)pg->stage[i];
+      push.flags[i] = (uint32_t*)pg->flags[i];
+    }
+    if (pg->local == nullptr) return fail(SVODB_ERR_SHAPE, "%s: no local counters", OP);
+    push.local = (uint32_t*)pg->local;
+  }
+  bool pushed = false;
+  const int rc = pool_impl(OP, hidden, norm_w, norm_b, eps, layer ? 1 : 0, scratch, mask_or_lengths, mode, normalize,
+                           &mine, stream, true, &push, &pushed);
+  if (rc != SVODB_OK || pg->world == 1) return rc;
+  // the rows are on their way (sent by the pooling kernel itself), or still to be sent
+  svodb_peer_gather step = *pg;
+  step.phases = pushed ? 2 : 0;
+  return svodb_peer_all_gather(&step, (const float*)mine.data, (float*)gathered->data, rows, D, stream);
 }
 
 int svodb_rope_table(double theta, const svodb_tensor* positions, int32_t head_dim, svodb_tensor* cos,

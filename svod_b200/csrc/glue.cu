@@ -190,7 +190,7 @@ template <typename T, int SPANS>
 __global__ void __launch_bounds__(256)
     norm_pool_kernel(const T* __restrict__ hidden, const T* __restrict__ w, const T* __restrict__ b, float eps,
                      int layer, const void* __restrict__ aux, int aux_i32, int mode, int slots, int normalize,
-                     float* __restrict__ out, int64_t out_row_stride, int64_t l_len) {
+                     float* __restrict__ out, int64_t out_row_stride, int64_t l_len, const PeerPush pp) {
   constexpr int D = SPANS * 256;
   __shared__ float part[8192];  // [warps][D], warps * D <= 8192
   __shared__ float cnts[8];
@@ -284,6 +284,30 @@ __global__ void __launch_bounds__(256)
     float4* d4 = reinterpret_cast<float4*>(dst + s * 256 + lane * 8);
     d4[0] = make_float4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]);
     d4[1] = make_float4(acc[s][4], acc[s][5], acc[s][6], acc[s][7]);
+  }
+  // Several GPUs: the row also goes straight into every peer's staging buffer (plain
+  // stores over NVLink) — the send half of the all-gather, in the kernel that made the row.
+  if (pp.world > 1) {
+    const uint32_t step = *reinterpret_cast<volatile uint32_t*>(pp.local);
+    const size_t slot = (((size_t)(step & 1u) * pp.world + pp.rank) * gridDim.x + blockIdx.x) * D;
+    for (int p = 0; p < pp.world; ++p) {
+      if (p == pp.rank) continue;
+      float* pd = pp.stage[p] + slot;
+#pragma unroll
+      for (int s = 0; s < SPANS; ++s) {
+        float4* d4 = reinterpret_cast<float4*>(pd + s * 256 + lane * 8);
+        d4[0] = make_float4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]);
+        d4[1] = make_float4(acc[s][4], acc[s][5], acc[s][6], acc[s][7]);
+      }
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0 && atomicAdd(&pp.local[1], 1u) == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < pp.world; ++p)
+        if (p != pp.rank) *reinterpret_cast<volatile uint32_t*>(pp.flags[p] + pp.rank) = step + 1u;
+      pp.local[1] = 0u;
+    }
   }
 }
 
@@ -406,12 +430,13 @@ bool norm_pool_dispatch(const PoolArgs& a, const EmbedNormArgs& n, cudaStream_t 
   const int spans = a.d / 256;
   int warps = 1;
   if (a.mode == 1) warps = spans <= 4 ? 8 : (spans <= 8 ? 4 : 1);
+  const PeerPush pp = a.push != nullptr ? *a.push : PeerPush{};
 #define SVODB_NP(SP)                                                                                               \
   case SP:                                                                                                         \
     norm_pool_kernel<T, SP><<<(unsigned)out_rows, warps * 32, 0, s>>>((const T*)a.hidden, (const T*)n.w,           \
                                                                       (const T*)n.b, n.eps, n.layer, a.aux,         \
                                                                       a.aux_i32, a.mode, a.slots, a.normalize,      \
-                                                                      a.out, a.out_row_stride, a.l);                \
+                                                                      a.out, a.out_row_stride, a.l, pp);            \
     return true
   switch (spans) {
     SVODB_NP(1); SVODB_NP(2); SVODB_NP(3); SVODB_NP(4); SVODB_NP(5); SVODB_NP(6); SVODB_NP(7); SVODB_NP(8);

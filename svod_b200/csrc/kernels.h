@@ -60,7 +60,19 @@ struct EmbedArgs {
 };
 void launch_embed(const EmbedArgs& a, cudaStream_t s);
 
+// The send half of the peer-memory all-gather (peer.cu) for a kernel that produces
+// the rows itself: block r stores its row into stage[step & 1][rank][r] of every
+// peer, fences at system scope and counts itself; the block that counts last writes
+// step + 1 into flags[rank] of every peer. world <= 1: nothing to send.
+struct PeerPush {
+  int world, rank;
+  float* stage[8];
+  uint32_t* flags[8];
+  uint32_t* local;  // {steps completed, rows pushed, peers unstaged}
+};
+
 struct PoolArgs {
+  const PeerPush* push;  // nullable: the rows also go to the peers' stages (fused norm + pool kernel only)
   const void* hidden;
   const void* aux;  // mask [B,L] (u8 or i32) or lengths [B] i32
   int aux_i32;

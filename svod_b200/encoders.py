@@ -128,11 +128,11 @@ class XlmRobertaEncoder:
             x = ops.layer_norm(y, lp["ln2_w"], lp["ln2_b"], c.layer_norm_eps)
         return x
 
-    def forward(self, ids, mask, out=None):
+    def forward(self, ids, mask, out=None, gather=None):
         h = self.hidden(ids, mask)
         mode = ops.POOL_CLS if self.cfg.pooling == "cls" else ops.POOL_MEAN
         # post-LN stack: the last layer's norm is the final one; pooling + L2 in one kernel
-        return ops.norm_pool(h, aux=mask if mode == ops.POOL_MEAN else None, mode=mode, out=out)
+        return ops.norm_pool(h, aux=mask if mode == ops.POOL_MEAN else None, mode=mode, out=out, gather=gather)
 
 
 # --------------------------------------------------------------------------- Qwen3
@@ -194,11 +194,11 @@ class Qwen3Embedder:
             x = ops.linear(g, lp["down_w"], Linear(residual=h))
         return x
 
-    def forward(self, ids, lengths, out=None):
+    def forward(self, ids, lengths, out=None, gather=None):
         # final RMSNorm of the pooled (last real) tokens alone, pooling and L2: one kernel
         x = self.run_layers(ops.embed(ids, self.p["embed"]))
         return ops.norm_pool(x, self.p["norm_w"], None, self.cfg.rms_norm_eps, layer=False, aux=lengths,
-                             mode=ops.POOL_LAST, out=out)
+                             mode=ops.POOL_LAST, out=out, gather=gather)
 
 
 # --------------------------------------------------------------------------- ModernBERT
@@ -264,7 +264,7 @@ class ModernBertEncoder:
         mode = ops.POOL_CLS if c.pooling == "cls" else ops.POOL_MEAN
         # final LayerNorm (of the tokens that are pooled), pooling and L2: one kernel
         return ops.norm_pool(x, p["final_ln_w"], None, c.norm_eps, aux=mask if mode == ops.POOL_MEAN else None,
-                             mode=mode, out=out)
+                             mode=mode, out=out, gather=gather)
 
 
 # --------------------------------------------------------------------------- plan replay
@@ -278,13 +278,16 @@ class Plan:
     whichever the model's `forward` takes. `out` may be this rank's slice of a
     gather buffer; `epilogue` (no arguments) is issued on the plan's stream right
     after the stack and becomes part of the captured graph: the all-gather of the
-    pooled rows on several GPUs, so that a replay is the whole step.
+    pooled rows on several GPUs, so that a replay is the whole step. `gather` (a
+    `peer.PeerGather` bound to the gather buffer) instead makes the stack's pooling
+    kernel send its rows to the other GPUs itself, with the unstage kernel behind it.
     """
 
     def __init__(self, model, rows: int, length: int, aux_kind: str, out: Optional[torch.Tensor] = None,
-                 ids_dtype=torch.int32, device="cuda", epilogue=None):
+                 ids_dtype=torch.int32, device="cuda", epilogue=None, gather=None):
         self.model = model
         self.epilogue = epilogue
+        self.gather = gather
         self.ids = torch.zeros(rows, length, dtype=ids_dtype, device=device)
         self.aux = (torch.ones(rows, length, dtype=torch.bool, device=device) if aux_kind == "mask"
                     else torch.full((rows,), length, dtype=torch.int32, device=device))
@@ -297,20 +300,24 @@ class Plan:
         # One eager run first: first-use work (kernel attributes, RoPE tables)
         # happens outside the capture.
         with torch.cuda.stream(self.stream):
-            self.model.forward(self.ids, self.aux, self.out)
-            if self.epilogue is not None:
-                self.epilogue()
+            self._step()
         self.stream.synchronize()
         ops.device_status()
         g = torch.cuda.CUDAGraph()
         # thread-local capture mode: helper threads of the process (a collective
         # library's watchdog) may query events while this thread captures
         with torch.cuda.graph(g, stream=self.stream, capture_error_mode="thread_local"):
-            self.model.forward(self.ids, self.aux, self.out)
-            if self.epilogue is not None:
-                self.epilogue()
+            self._step()
         self.graph = g
         return self
+
+    def _step(self):
+        if self.gather is not None:
+            self.model.forward(self.ids, self.aux, self.out, gather=self.gather)
+        else:
+            self.model.forward(self.ids, self.aux, self.out)
+        if self.epilogue is not None:
+            self.epilogue()
 
     def run(self, ids_host: torch.Tensor, aux_host: torch.Tensor, out_host: Optional[torch.Tensor] = None):
         """Host (pinned) inputs -> device, replay, pooled output -> host."""

@@ -469,29 +469,42 @@ POOL_CLS, POOL_MEAN, POOL_LAST, POOL_GATHER = 0, 1, 2, 3
 
 
 def norm_pool(hidden, norm_w=None, norm_b=None, eps: float = 1e-5, layer: bool = True, aux=None, mode: int = POOL_CLS,
-              normalize: bool = True, out=None):
+              normalize: bool = True, out=None, gather=None):
     """The stack's final norm (none when `norm_w` is None), the pooling and the
     L2 normalisation in one kernel (model/src/encoder_head.rs:280-286;
     model/src/qwen3/model.rs:77-99): `hidden [B,L,D]` before its final norm ->
     f32 `[B,D]`. Only the pooled tokens are normalised (every real token for the
-    masked mean)."""
+    masked mean).
+
+    `gather` (a `peer.PeerGather` bound to a gather buffer): the rows are written
+    into this rank's slot of that buffer and gathered from the other GPUs — the
+    pooling kernel itself stores each row into the peers' staging buffers, then the
+    unstage kernel follows (`svodb_norm_pool_gather`). Returns the whole buffer."""
     B, _, D = hidden.shape
-    if out is None:
+    if gather is not None:
+        out = gather.gathered
+    elif out is None:
         rows = B * aux.shape[1] if mode == POOL_GATHER else B
         out = torch.empty(rows, D, dtype=torch.float32, device=hidden.device)
     if aux is not None and aux.dtype not in (torch.bool, torch.uint8, torch.int32):
         aux = aux.to(torch.int32)
     a, b, c, w, bb = _desc(hidden), _desc(aux), _desc(out), _desc(norm_w), _desc(norm_b)
     lib = L.load()
-    rc = lib.svodb_norm_pool(_p(a), _p(w), _p(bb), float(eps), int(layer), None, _p(b), int(mode), int(normalize), _p(c),
-                             _stream())
+
+    def call(scratch):
+        if gather is not None:
+            return lib.svodb_norm_pool_gather(_p(a), _p(w), _p(bb), float(eps), int(layer), scratch, _p(b), int(mode),
+                                              int(normalize), C.byref(gather.ctx), _p(c), _stream())
+        return lib.svodb_norm_pool(_p(a), _p(w), _p(bb), float(eps), int(layer), scratch, _p(b), int(mode), int(normalize),
+                                   _p(c), _stream())
+
+    rc = call(None)
     if rc == L.ERR_WORKSPACE:
         # rows outside the fused kernel: the unfused sequence wants room for the normalised hidden states
         scratch = torch.empty_like(hidden)
         sd = _desc(scratch)
-        rc = lib.svodb_norm_pool(_p(a), _p(w), _p(bb), float(eps), int(layer), _p(sd), _p(b), int(mode), int(normalize),
-                                 _p(c), _stream())
-    _check(rc, 1)
+        rc = call(_p(sd))
+    _check(rc, 1 if gather is None or gather.world == 1 else 2)
     return out
 
 

@@ -90,6 +90,18 @@ class PeerGather:
             self.close()
             raise ops.OpsError(L.ERR_LAUNCH, "peer gather: " + "; ".join(failed))
 
+    def bind(self, gathered: torch.Tensor) -> "PeerGather":
+        """Names the `[world*rows, d]` f32 buffer the gathers fill: `ops.norm_pool(...,
+        gather=self)` then pools into this rank's slot of it and sends the rows from the
+        pooling kernel itself."""
+        if tuple(gathered.shape) != (self.world * self.rows, self.d) or gathered.dtype != torch.float32 \
+                or not gathered.is_contiguous():
+            raise ops.OpsError(L.ERR_SHAPE, f"peer gather: gathered {list(gathered.shape)}, expected contiguous f32 "
+                                            f"[{self.world * self.rows}, {self.d}]")
+        self.gathered = gathered
+        self.mine = gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
+        return self
+
     def all_gather(self, local: torch.Tensor, gathered: torch.Tensor) -> torch.Tensor:
         """`local` `[rows, d]` f32 (normally slot `rank` of `gathered`) into slot `rank`
         of every rank's `gathered` `[world*rows, d]`, on torch's current stream."""

@@ -130,6 +130,24 @@ with torch.cuda.stream(s):
         want = torch.cat([torch.full((rows, d), 10.0 * k + r, device="cuda") for r in range(world)])
         ok = ok and torch.equal(a, want)
 ops.device_status()
+# the send half inside the pooling kernel (`svodb_norm_pool_gather`), eagerly and from a graph
+L_, D_ = 40, 1024
+fused = PeerGather(rows, D_)
+gbuf = torch.zeros(world * rows, D_, device="cuda")
+fused.bind(gbuf)
+wn = torch.ones(D_, device="cuda", dtype=torch.bfloat16)
+for step in range(3):
+    g = torch.Generator(device="cuda").manual_seed(7 * step + rank)
+    hid = torch.randn(rows, L_, D_, generator=g, device="cuda").to(torch.bfloat16)
+    lens = torch.randint(1, L_ + 1, (rows,), generator=g, device="cuda", dtype=torch.int32)
+    mine = ops.norm_pool(hid, wn, None, 1e-6, layer=False, aux=lens, mode=ops.POOL_LAST)
+    want = torch.zeros_like(gbuf)
+    dist.all_gather_into_tensor(want, mine)
+    got = ops.norm_pool(hid, wn, None, 1e-6, layer=False, aux=lens, mode=ops.POOL_LAST, gather=fused)
+    ok = ok and "push:peers" in ops.chosen()
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(got, want)
+ops.device_status()
 dist.barrier()
 print("PEER_OK" if ok else "PEER_MISMATCH", flush=True)
 pg.close()
