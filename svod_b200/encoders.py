@@ -258,7 +258,7 @@ class ModernBertEncoder:
             x = ops.linear(g, lp["wo_w"], Linear(residual=h))
         return x
 
-    def forward(self, ids, mask, out=None):
+    def forward(self, ids, mask, out=None, gather=None):
         c, p = self.cfg, self.p
         x = self.run_layers(ops.embed_norm(ids, p["embed"], p["emb_ln_w"], None, c.norm_eps), mask)
         mode = ops.POOL_CLS if c.pooling == "cls" else ops.POOL_MEAN
